@@ -1,0 +1,141 @@
+// Host-side launch API of the sm_100a kernels (plain C++; no torch headers).
+// bindings.cpp wraps these as torch custom ops; every function enqueues on `stream` and returns
+// the CUDA error of the launch, never synchronising the device.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace stb {
+
+// ------------------------------------------------------------------ GEMM (gemm_sm100.cu)
+struct GemmCall {
+  const void* a;      // bf16; K-major: [M, lda] ; MN-major: [K, lda]
+  const void* b;      // bf16; K-major: [N, ldb] ; MN-major: [K, ldb]
+  void* out;          // bf16 or fp32 [M, ldo]
+  const float* bias;  // optional fp32 [N]
+  const void* residual;  // optional, dtype/ld of out
+  int M, N, K;
+  int64_t lda, ldb, ldo;
+  bool a_mn, b_mn;
+  bool out_fp32;
+  bool accumulate;
+  float alpha;
+  int force_bn;  // 0 = heuristic, else 128 or 256
+};
+cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream);
+
+// ------------------------------------------------------------------ elementwise (elementwise.cu)
+cudaError_t launch_rmsnorm_fwd(const float* x, const float* w, void* y, float* inv, int rows,
+                               int cols, float eps, bool y_fp32, cudaStream_t s);
+// dx_out = dres_in (optional) + rmsnorm backward of dy ; dw_partial [blocks, cols]
+cudaError_t launch_rmsnorm_bwd(const float* dy, const float* x, const float* w, const float* inv,
+                               const float* dres_in, float* dx_out, float* dw_partial,
+                               int partial_rows, int rows, int cols, cudaStream_t s);
+cudaError_t launch_colsum_f32(const float* partial, float* out, int rows, int cols,
+                              bool accumulate, cudaStream_t s);
+cudaError_t launch_colsum_bf16(const void* x, int64_t ldx, float* out, int rows, int cols,
+                               bool accumulate, float* scratch, int scratch_rows, cudaStream_t s);
+// In-place rotary embedding on the q and k heads of a packed [rows, (hq + 2 hkv) * d] bf16 buffer.
+cudaError_t launch_rope(void* qkv, const float* cos, const float* sin, const int* positions,
+                        int rows, int seq, int hq, int hkv, int d, bool inverse, cudaStream_t s);
+cudaError_t launch_swiglu_fwd(const void* gu, void* h, int rows, int inter, cudaStream_t s);
+cudaError_t launch_swiglu_bwd(const void* dh, const void* gu, void* dgu, int rows, int inter,
+                              cudaStream_t s);
+cudaError_t launch_ce_fwd(const void* logits, int64_t ld, const int64_t* labels, float* lse,
+                          float* loss_rows, int rows, int vocab, cudaStream_t s);
+cudaError_t launch_ce_bwd(void* logits, int64_t ld, const int64_t* labels, const float* lse,
+                          const float* scale, int rows, int vocab, cudaStream_t s);
+cudaError_t launch_sum_f32(const float* x, float* out, int n, bool accumulate, cudaStream_t s);
+cudaError_t launch_embedding_scatter_add(const float* dx, const int64_t* ids, float* dw, int rows,
+                                         int cols, int64_t vocab, int64_t pad_id, cudaStream_t s);
+cudaError_t launch_cast_f32_to_bf16(const float* x, void* y, int64_t n, cudaStream_t s);
+cudaError_t launch_add_f32(const float* a, const float* b, float* out, int64_t n, cudaStream_t s);
+
+// Optimiser over a flat fp32 arena (one launch for every shard leaf).
+struct AdamWArgs {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias_correction1, bias_correction2;  // 1 - beta^t
+  float grad_scale;                          // multiplies the gradient first (1/F etc.)
+};
+cudaError_t launch_adamw(float* p, const float* g, float* m, float* v, int64_t n, AdamWArgs a,
+                         cudaStream_t s);
+cudaError_t launch_sgd(float* p, const float* g, int64_t n, float lr, cudaStream_t s);
+// flags[0] |= any non-finite in g[0,n) ; flags[1] |= any non-zero in the listed padding ranges.
+cudaError_t launch_grad_check(const float* g, int64_t n, const int64_t* pad_ranges, int n_ranges,
+                              int* flags, cudaStream_t s);
+
+// ------------------------------------------------------------------ shard <-> full (peer.cu)
+// One entry per parameter of a unit.  The FSDP shard of parameter j on rank r is elements
+// [r*q, min((r+1)*q, numel)) of the TP-local flattened tensor, stored at shard_off in every
+// rank's shard arena (zero padded to q).
+struct SegmentDesc {
+  int64_t shard_off;  // element offset inside the unit's shard arena (same on all ranks)
+  int64_t q;          // shard length ceil(numel / F)
+  int64_t numel;      // TP-local numel
+  int64_t full_off;   // element offset inside the unit's full buffers
+  int32_t keep_fp32;  // materialise as fp32 into the small fp32 buffer instead of bf16
+  int32_t pad;
+};
+constexpr int kMaxPeers = 8;
+struct PeerPtrs {
+  const float* p[kMaxPeers];
+};
+struct PeerPtrsMut {
+  float* p[kMaxPeers];
+};
+// All-gather fused with the fp32 -> bf16 cast: every rank pulls the peers' fp32 shards over
+// NVLink with plain loads and lands the compute-dtype full parameters locally.
+cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc* segs, int n_segs,
+                                 void* full_bf16, float* full_fp32, int64_t total_full,
+                                 cudaStream_t s);
+// Reduce-scatter fused with the fp32 accumulate into the persistent gradient shard: rank r pulls
+// its slice of every peer's full fp32 gradient, sums, scales and adds (or stores).
+cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
+                                        const SegmentDesc* segs, int n_segs, float* grad_shard,
+                                        int64_t shard_total, float scale, bool accumulate,
+                                        cudaStream_t s);
+// Same, and applies AdamW to the owned shard in the same pass (last micro-step only).
+cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int rank,
+                                        const SegmentDesc* segs, int n_segs, float* grad_shard,
+                                        float* p, float* m, float* v, int64_t shard_total,
+                                        float scale, bool accumulate, AdamWArgs a, cudaStream_t s);
+// Embedding lookup straight from the (possibly remote) fp32 shards: no all-gather of the table.
+cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t q,
+                                            const int64_t* ids, float* out, int rows, int cols,
+                                            cudaStream_t s);
+// Sequence all-gather of an activation: out[b, r*sl + s, :] = peer r's x[b, s, :].
+cudaError_t launch_seq_gather(const void* const* peers, int degree, void* out, int batch,
+                              int seq_local, int64_t row_bytes, cudaStream_t s);
+// Sequence reduce-scatter: out[b, s, :] = sum_r peer r's partial[b, rank*sl + s, :] (+ residual).
+cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree, int rank,
+                                          const float* residual, float* out, int batch,
+                                          int seq_local, int cols, cudaStream_t s);
+// Cross-GPU barrier over flag words in peer memory; bounded spin, status word on expiry.
+cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank, uint32_t epoch,
+                                int slot, int* status, uint32_t max_spin, cudaStream_t s);
+
+// ------------------------------------------------------------------ attention (attention_sm100.cu)
+struct AttnCall {
+  const void* qkv;   // bf16 [B*S, (hq + 2 hkv) * 128], rope already applied
+  void* out;         // bf16 [B*S, hq*128]
+  float* lse;        // fp32 [B, hq, S]
+  const uint8_t* key_mask;  // optional [B, S] (1 = attend)
+  int batch, seq, hq, hkv;
+  float scale;
+};
+cudaError_t launch_attention_fwd(const AttnCall& c, int* status, cudaStream_t s);
+struct AttnBwdCall {
+  const void* qkv;
+  const void* out;
+  const void* dout;  // bf16 [B*S, hq*128]
+  const float* lse;
+  float* delta;      // fp32 [B, hq, S] scratch
+  void* dqkv;        // bf16 [B*S, (hq + 2 hkv) * 128]
+  float* dkv_accum;  // fp32 scratch [B*S, 2*hkv*128] for GQA accumulation
+  const uint8_t* key_mask;
+  int batch, seq, hq, hkv;
+  float scale;
+};
+cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t s);
+
+}  // namespace stb

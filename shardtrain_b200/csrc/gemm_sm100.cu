@@ -1,0 +1,117 @@
+// Host launcher of the tcgen05 GEMM: builds the TMA tensor maps and picks the tile width.
+#include <mutex>
+
+#include "api.h"
+#include "gemm_sm100.cuh"
+
+namespace stb {
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+// Row-major bf16 matrix [rows, cols] with leading dimension ld -> 2-D tensor map whose box is
+// box_cols x box_rows with 128-byte swizzle (box_cols * 2 bytes must be 128).
+bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
+                          int64_t ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+namespace {
+
+template <int BN, bool A_MN, bool B_MN>
+cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!A_MN)
+    ok = make_bf16_tensor_map(&ta, c.a, c.M, c.K, c.lda, 64, kGemmBM);
+  else
+    ok = make_bf16_tensor_map(&ta, c.a, c.K, c.M, c.lda, 64, 64);
+  if (!B_MN)
+    ok = ok && make_bf16_tensor_map(&tb, c.b, c.N, c.K, c.ldb, 64, BN);
+  else
+    ok = ok && make_bf16_tensor_map(&tb, c.b, c.K, c.N, c.ldb, 64, 64);
+  if (!ok) return cudaErrorInvalidValue;
+
+  GemmEpilogue ep;
+  ep.out = c.out;
+  ep.bias = c.bias;
+  ep.residual = c.residual;
+  ep.mul = nullptr;
+  ep.ldo = c.ldo;
+  ep.out_fp32 = c.out_fp32 ? 1 : 0;
+  ep.accumulate = c.accumulate ? 1 : 0;
+  ep.alpha = c.alpha;
+
+  auto kernel = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  constexpr int smem = GemmSmem<BN>::kTotal;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
+  const int n_tiles = (c.N + BN - 1) / BN;
+  kernel<<<m_tiles * n_tiles, kGemmThreads, smem, stream>>>(ta, tb, ep, c.M, c.N, c.K, status);
+  return cudaGetLastError();
+}
+
+template <int BN>
+cudaError_t dispatch_major(const GemmCall& c, int* status, cudaStream_t stream) {
+  if (!c.a_mn && !c.b_mn) return launch_variant<BN, false, false>(c, status, stream);
+  if (!c.a_mn && c.b_mn) return launch_variant<BN, false, true>(c, status, stream);
+  if (c.a_mn && c.b_mn) return launch_variant<BN, true, true>(c, status, stream);
+  return launch_variant<BN, true, false>(c, status, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream) {
+  if (c.M <= 0 || c.N <= 0 || c.K <= 0) return cudaErrorInvalidValue;
+  // TMA needs 16-byte aligned bases and strides; the vectorised epilogue needs N % 8 == 0.
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!aligned16(c.a) || !aligned16(c.b) || !aligned16(c.out) || (c.lda % 8) || (c.ldb % 8) ||
+      (c.N % 8) || (c.ldo % (c.out_fp32 ? 4 : 8)))
+    return cudaErrorInvalidValue;
+  if (c.residual != nullptr && !aligned16(c.residual)) return cudaErrorInvalidValue;
+  if (c.accumulate && !c.out_fp32) return cudaErrorInvalidValue;
+  int bn = c.force_bn;
+  if (bn == 0) {
+    const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
+    const int ctas256 = m_tiles * ((c.N + 255) / 256);
+    bn = (ctas256 >= 120) ? 256 : 128;
+  }
+  if (bn == 256) return dispatch_major<256>(c, status, stream);
+  if (bn == 128) return dispatch_major<128>(c, status, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace stb

@@ -1,0 +1,336 @@
+// Collectives written as kernels over NVLink peer memory (plain P2P loads through NVSwitch), each
+// fused with the compute that follows it in the reference's NCCL pipeline:
+//   * parameter all-gather + copy-out + fp32->bf16 cast  (src/sharded_runtime/runtime/materializer.py:31-114,
+//     src/sharded_runtime/runtime/layout.py:77-90)
+//   * gradient pack + reduce-scatter + 1/F scale + accumulate (+ AdamW)  (materializer.py:116-192,
+//     layout.py:93-106, src/sharded_runtime/training/qwen2_trainer.py:48)
+//   * sequence-parallel activation gather / reduce-scatter (src/sharded_runtime/runtime/comm.py:781-884)
+//   * embedding rows fetched from the owning shard without gathering the table.
+// With degree 1 the same kernels read only local memory.  No kernel here waits on another GPU
+// except peer_barrier_kernel, whose spin is bounded.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace stb {
+
+namespace {
+
+constexpr int kMaxSegs = 32;
+struct SegTable {
+  SegmentDesc s[kMaxSegs];
+  int n;
+};
+
+__device__ __forceinline__ uint32_t pk2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Work is tiled in chunks of kChunk elements of one segment; blockIdx.y = segment.
+constexpr int kChunk = 4096;
+
+__global__ void gather_params_kernel(PeerPtrs shards, int degree, SegTable tab,
+                                     __nv_bfloat16* __restrict__ full_bf16,
+                                     float* __restrict__ full_fp32) {
+  const SegmentDesc sg = tab.s[blockIdx.y];
+  const bool vec = (sg.q % 4 == 0) && (sg.shard_off % 4 == 0) && (sg.full_off % 4 == 0);
+  for (int64_t chunk = blockIdx.x; chunk * kChunk < sg.numel; chunk += gridDim.x) {
+    const int64_t base = chunk * kChunk;
+    if (vec) {
+      for (int64_t i = base + threadIdx.x * 4; i < min(base + kChunk, sg.numel);
+           i += blockDim.x * 4) {
+        const int r = static_cast<int>(i / sg.q);  // q % 4 == 0: the 4 elements share a rank
+        const int64_t off = i - r * sg.q;
+        const float* src = shards.p[r] + sg.shard_off + off;
+        if (i + 3 < sg.numel) {
+          const float4 v = *reinterpret_cast<const float4*>(src);
+          if (sg.keep_fp32) {
+            *reinterpret_cast<float4*>(full_fp32 + sg.full_off + i) = v;
+          } else {
+            uint2 o;
+            o.x = pk2(v.x, v.y);
+            o.y = pk2(v.z, v.w);
+            *reinterpret_cast<uint2*>(full_bf16 + sg.full_off + i) = o;
+          }
+        } else {
+          for (int64_t j = i; j < sg.numel; ++j) {
+            const float v = src[j - i];
+            if (sg.keep_fp32)
+              full_fp32[sg.full_off + j] = v;
+            else
+              full_bf16[sg.full_off + j] = __float2bfloat16(v);
+          }
+        }
+      }
+    } else {
+      for (int64_t i = base + threadIdx.x; i < min(base + kChunk, sg.numel); i += blockDim.x) {
+        const int r = static_cast<int>(i / sg.q);
+        const float v = shards.p[r][sg.shard_off + (i - r * sg.q)];
+        if (sg.keep_fp32)
+          full_fp32[sg.full_off + i] = v;
+        else
+          full_bf16[sg.full_off + i] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+// Rank `rank` owns elements [rank*q, rank*q + q) of each segment (zero beyond numel).
+template <bool ADAMW>
+__global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTable tab,
+                                      float* __restrict__ gshard, float* __restrict__ p,
+                                      float* __restrict__ m, float* __restrict__ v, float scale,
+                                      int accumulate, AdamWArgs a) {
+  const SegmentDesc sg = tab.s[blockIdx.y];
+  const int64_t lo = static_cast<int64_t>(rank) * sg.q;
+  const int64_t valid = max(static_cast<int64_t>(0), min(sg.q, sg.numel - lo));
+  const bool vec = (sg.q % 4 == 0) && (sg.shard_off % 4 == 0) && (sg.full_off % 4 == 0);
+  const float step_size = ADAMW ? a.lr / a.bias_correction1 : 0.f;
+  const float inv_bc2_sqrt = ADAMW ? rsqrtf(a.bias_correction2) : 0.f;
+  for (int64_t chunk = blockIdx.x; chunk * kChunk < sg.q; chunk += gridDim.x) {
+    const int64_t base = chunk * kChunk;
+    const int64_t end = min(base + kChunk, sg.q);
+    const int step = vec ? 4 : 1;
+    for (int64_t i = base + threadIdx.x * step; i < end; i += blockDim.x * step) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const int cnt = vec ? 4 : 1;
+      if (vec && i + 3 < valid) {
+        // rotate the peer order by rank so the ranks do not all hit one peer at once
+        for (int d = 0; d < degree; ++d) {
+          const int src = (rank + d) % degree;
+          const float4 t =
+              *reinterpret_cast<const float4*>(full.p[src] + sg.full_off + lo + i);
+          acc[0] += t.x; acc[1] += t.y; acc[2] += t.z; acc[3] += t.w;
+        }
+      } else {
+        for (int j = 0; j < cnt; ++j) {
+          if (i + j < valid) {
+            for (int d = 0; d < degree; ++d) {
+              const int src = (rank + d) % degree;
+              acc[j] += full.p[src][sg.full_off + lo + i + j];
+            }
+          }
+        }
+      }
+      for (int j = 0; j < cnt; ++j) {
+        const int64_t e = sg.shard_off + i + j;
+        if (i + j >= sg.q) break;
+        float g = acc[j] * scale;  // padding stays exactly zero: acc is 0 there
+        if (accumulate) g += gshard[e];
+        gshard[e] = g;
+        if (ADAMW) {
+          float pj = p[e] * (1.f - a.lr * a.weight_decay);
+          const float gr = g * a.grad_scale;
+          const float mj = a.beta1 * m[e] + (1.f - a.beta1) * gr;
+          const float vj = a.beta2 * v[e] + (1.f - a.beta2) * gr * gr;
+          pj -= step_size * mj / (sqrtf(vj) * inv_bc2_sqrt + a.eps);
+          // padding elements have p = g = m = v = 0 and stay 0
+          p[e] = pj;
+          m[e] = mj;
+          v[e] = vj;
+        }
+      }
+    }
+  }
+}
+
+__global__ void embedding_gather_sharded_kernel(PeerPtrs shards, int degree, int64_t q,
+                                                const int64_t* __restrict__ ids,
+                                                float* __restrict__ out, int cols) {
+  const int64_t row = blockIdx.x;
+  const int64_t id = ids[row];
+  const int64_t base = id * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const int64_t g = base + c;
+    const int r = static_cast<int>(g / q);
+    out[row * cols + c] = shards.p[r][g - r * q];
+  }
+}
+
+struct VoidPeers {
+  const void* p[kMaxPeers];
+};
+
+// out[b, r*sl + s, :] = peer r's x[b, s, :]   (16-byte vectors)
+__global__ void seq_gather_kernel(VoidPeers peers, int degree, uint4* __restrict__ out, int batch,
+                                  int seq_local, int64_t row_vec) {
+  const int64_t per_peer = static_cast<int64_t>(batch) * seq_local * row_vec;
+  const int64_t total = per_peer * degree;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / per_peer);
+    const int64_t j = i - r * per_peer;
+    const int64_t b = j / (seq_local * row_vec);
+    const int64_t rest = j - b * seq_local * row_vec;
+    const uint4 v = reinterpret_cast<const uint4*>(peers.p[r])[j];
+    out[(b * degree + r) * seq_local * row_vec + rest] = v;
+  }
+}
+
+struct FloatPeers {
+  const float* p[kMaxPeers];
+};
+
+// out[b, s, :] = residual[b, s, :] + sum_r partial_r[b, rank*sl + s, :]
+__global__ void seq_reduce_scatter_kernel(FloatPeers peers, int degree, int rank,
+                                          const float* __restrict__ residual,
+                                          float* __restrict__ out, int batch, int seq_local,
+                                          int cols) {
+  const int64_t cv = cols / 4;
+  const int64_t total = static_cast<int64_t>(batch) * seq_local * cv;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = i / (seq_local * cv);
+    const int64_t rest = i - b * seq_local * cv;
+    const int64_t src = (b * degree + rank) * seq_local * cv + rest;
+    float4 acc = residual ? reinterpret_cast<const float4*>(residual)[i]
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int d = 0; d < degree; ++d) {
+      const int r = (rank + d) % degree;
+      const float4 t = reinterpret_cast<const float4*>(peers.p[r])[src];
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+  }
+}
+
+struct FlagPeers {
+  uint32_t* p[kMaxPeers];
+};
+
+// Thread t tells peer t "rank `rank` reached `epoch`" and then waits until peer t says the same.
+// Pad layout: pad[slot * kMaxPeers + source_rank].  The spin is bounded; on expiry the status
+// word is set and the kernel returns.
+__global__ void peer_barrier_kernel(FlagPeers pads, int degree, int rank, uint32_t epoch, int slot,
+                                    int* status, uint32_t max_spin) {
+  const int t = threadIdx.x;
+  if (t >= degree) return;
+  __threadfence_system();
+  uint32_t* remote = pads.p[t] + slot * kMaxPeers + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const uint32_t* mine = pads.p[rank] + slot * kMaxPeers + t;
+  bool seen = false;
+  for (uint32_t i = 0; i < max_spin; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    // epochs only grow; signed distance tolerates wrap-around
+    if (static_cast<int32_t>(v - epoch) >= 0) {
+      seen = true;
+      break;
+    }
+    __nanosleep(64);
+  }
+  if (!seen && status != nullptr) atomicCAS(status, kOk, kErrPeerFlagWait);
+  __threadfence_system();
+}
+
+bool fill_table(SegTable* t, const SegmentDesc* segs, int n) {
+  if (n < 1 || n > kMaxSegs) return false;
+  for (int i = 0; i < n; ++i) t->s[i] = segs[i];
+  t->n = n;
+  return true;
+}
+
+int chunks_for(const SegmentDesc* segs, int n, bool per_shard) {
+  int64_t most = 1;
+  for (int i = 0; i < n; ++i) {
+    const int64_t len = per_shard ? segs[i].q : segs[i].numel;
+    most = std::max<int64_t>(most, (len + kChunk - 1) / kChunk);
+  }
+  return static_cast<int>(std::min<int64_t>(most, 148 * 4));
+}
+
+}  // namespace
+
+cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc* segs, int n_segs,
+                                 void* full_bf16, float* full_fp32, int64_t total_full,
+                                 cudaStream_t s) {
+  (void)total_full;
+  SegTable tab;
+  if (degree < 1 || degree > kMaxPeers || !fill_table(&tab, segs, n_segs))
+    return cudaErrorInvalidValue;
+  dim3 grid(chunks_for(segs, n_segs, false), n_segs);
+  gather_params_kernel<<<grid, 256, 0, s>>>(shards, degree, tab,
+                                            reinterpret_cast<__nv_bfloat16*>(full_bf16), full_fp32);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
+                                        const SegmentDesc* segs, int n_segs, float* grad_shard,
+                                        int64_t shard_total, float scale, bool accumulate,
+                                        cudaStream_t s) {
+  (void)shard_total;
+  SegTable tab;
+  if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree ||
+      !fill_table(&tab, segs, n_segs))
+    return cudaErrorInvalidValue;
+  dim3 grid(chunks_for(segs, n_segs, true), n_segs);
+  reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(full_grads, degree, rank, tab, grad_shard,
+                                                    nullptr, nullptr, nullptr, scale,
+                                                    accumulate ? 1 : 0, AdamWArgs{});
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int rank,
+                                        const SegmentDesc* segs, int n_segs, float* grad_shard,
+                                        float* p, float* m, float* v, int64_t shard_total,
+                                        float scale, bool accumulate, AdamWArgs a, cudaStream_t s) {
+  (void)shard_total;
+  SegTable tab;
+  if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree ||
+      !fill_table(&tab, segs, n_segs))
+    return cudaErrorInvalidValue;
+  dim3 grid(chunks_for(segs, n_segs, true), n_segs);
+  reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(full_grads, degree, rank, tab, grad_shard, p, m,
+                                                   v, scale, accumulate ? 1 : 0, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t q,
+                                            const int64_t* ids, float* out, int rows, int cols,
+                                            cudaStream_t s) {
+  if (degree < 1 || degree > kMaxPeers || q < 1) return cudaErrorInvalidValue;
+  embedding_gather_sharded_kernel<<<rows, 256, 0, s>>>(shards, degree, q, ids, out, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_seq_gather(const void* const* peers, int degree, void* out, int batch,
+                              int seq_local, int64_t row_bytes, cudaStream_t s) {
+  if (degree < 1 || degree > kMaxPeers || row_bytes % 16) return cudaErrorInvalidValue;
+  VoidPeers vp;
+  for (int i = 0; i < degree; ++i) vp.p[i] = peers[i];
+  const int64_t total = static_cast<int64_t>(batch) * seq_local * (row_bytes / 16) * degree;
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 8));
+  seq_gather_kernel<<<grid, 256, 0, s>>>(vp, degree, reinterpret_cast<uint4*>(out), batch,
+                                         seq_local, row_bytes / 16);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree, int rank,
+                                          const float* residual, float* out, int batch,
+                                          int seq_local, int cols, cudaStream_t s) {
+  if (degree < 1 || degree > kMaxPeers || cols % 4) return cudaErrorInvalidValue;
+  FloatPeers fp;
+  for (int i = 0; i < degree; ++i) fp.p[i] = peers[i];
+  const int64_t total = static_cast<int64_t>(batch) * seq_local * (cols / 4);
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 8));
+  seq_reduce_scatter_kernel<<<grid, 256, 0, s>>>(fp, degree, rank, residual, out, batch, seq_local,
+                                                 cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank, uint32_t epoch,
+                                int slot, int* status, uint32_t max_spin, cudaStream_t s) {
+  if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree)
+    return cudaErrorInvalidValue;
+  FlagPeers fp;
+  for (int i = 0; i < degree; ++i) fp.p[i] = flag_pads[i];
+  peer_barrier_kernel<<<1, 32, 0, s>>>(fp, degree, rank, epoch, slot, status, max_spin);
+  return cudaGetLastError();
+}
+
+}  // namespace stb
