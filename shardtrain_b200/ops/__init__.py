@@ -1,0 +1,54 @@
+"""Python side of the sm_100a extension.
+
+`load()` returns `torch.ops.stb` after loading the in-tree `_C.so`.  On a machine with a GPU the
+extension is mandatory: a missing or unloadable library raises instead of falling back to
+PyTorch ops.  On a machine without CUDA `available()` is False and the portable (CPU/gloo)
+executor is used.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+_LIB = Path(__file__).resolve().parent.parent / "_C.so"
+_loaded = False
+
+
+def extension_path() -> str | None:
+    return str(_LIB) if _LIB.exists() else None
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def load():
+    global _loaded
+    if not _loaded:
+        if not _LIB.exists():
+            raise RuntimeError(
+                f"{_LIB} is missing: build it with `python -m shardtrain_b200.build_ext` "
+                "(the CUDA path has no PyTorch fallback)"
+            )
+        torch.ops.load_library(str(_LIB))
+        _loaded = True
+    return torch.ops.stb
+
+
+def check_status(where: str = "") -> None:
+    """Synchronise and raise if any kernel recorded a bounded-wait expiry or a bad argument."""
+    code = int(load().status_read())
+    if code != 0:
+        load().status_reset()
+        names = {
+            1: "TMA producer gave up waiting for a free pipeline stage",
+            2: "MMA issuer gave up waiting for operand tiles",
+            3: "epilogue gave up waiting for the accumulator",
+            4: "drain wait expired",
+            5: "peer flag wait expired (a peer never signalled)",
+            6: "attention pipeline wait expired",
+            7: "kernel rejected its arguments",
+        }
+        raise RuntimeError(f"sm_100a kernel status {code} ({names.get(code, 'unknown')}) {where}")
