@@ -689,3 +689,17 @@ class ShardedRuntime:
             flat = torch.cat([p[: handle.spec.valid_len(r)] for r, p in enumerate(parts)])
             full[name] = flat.view(handle.spec.tp_local_shape)
         return full
+
+
+def _attach_qwen_api():
+    """Qwen-specific methods live in qwen2_adapter; expose them as runtime methods."""
+    from shardtrain_b200.runtime import qwen2_adapter as qa
+
+    ShardedRuntime.model_forward = lambda self, model, ids, **kw: qa.model_forward(self, model, ids, **kw)
+    ShardedRuntime.prepare_qwen_input = lambda self, ids, embeds: (qa.prepare_input(self, ids, embeds), None)
+    ShardedRuntime.qwen_loss = lambda self, logits, labels: qa.qwen_loss(self, logits, labels)
+    ShardedRuntime.qwen_reported_loss = lambda self: qa.reported_loss(self)
+    ShardedRuntime.sequence_input = lambda self, t: qa.sequence_input(self, t)
+
+
+_attach_qwen_api()

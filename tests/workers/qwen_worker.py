@@ -1,0 +1,91 @@
+"""torchrun worker: train the tiny Qwen2 for a few steps on an F x T mesh and compare losses,
+reconstructed parameters and event counts against an unsharded single-process model."""
+import argparse
+import json
+import logging
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from shardtrain_b200.config import ParallelConfig
+from shardtrain_b200.distributed.context import DistributedContext, WorkerEnvironment
+from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+from shardtrain_b200.runtime.engine import ShardedRuntime
+from shardtrain_b200.training.qwen2_trainer import QwenTrainer
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--fsdp", type=int, default=1)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--sp", type=int, default=0)
+    ap.add_argument("--flags", default="000")
+    ap.add_argument("--policy", default="conservative")
+    ap.add_argument("--reshard", type=int, default=1)
+    ap.add_argument("--accum", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--tied", type=int, default=1)
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--mismatch", type=int, default=0)
+    a = ap.parse_args()
+    worker = WorkerEnvironment.read()
+    out = Path(a.out)
+    out.mkdir(parents=True, exist_ok=True)
+    logger = logging.getLogger(f"w{worker.rank}")
+    backend = "gloo" if a.device == "cpu" else "nccl"
+    par = ParallelConfig(a.fsdp, a.tp, bool(a.sp), a.device, backend)
+    with DistributedContext(par, worker, 60, logger) as ctx:
+        cfg = Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128,
+                               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                               tie_word_embeddings=bool(a.tied))
+        torch.manual_seed(7 + (worker.rank if a.mismatch else 0))
+        dense = Qwen2CausalLM(cfg)
+        import copy
+        model = copy.deepcopy(dense)
+        fp, bp, ar = (c == "1" for c in a.flags)
+        rt = ShardedRuntime(device=ctx.device, reshard_after_forward=bool(a.reshard),
+                            forward_prefetch=fp, backward_prefetch=bp, async_grad_rs=ar,
+                            communication_policy=a.policy, directory=out)
+        rt.register(model, ctx, sp=bool(a.sp))
+        tr = QwenTrainer(model, rt, lr=1e-3, optimizer="adamw", accumulation_steps=a.accum)
+        opt = torch.optim.AdamW(dense.parameters(), lr=1e-3)
+        batch = 2 * a.accum
+        rows = []
+        for step in range(a.steps):
+            gen = torch.Generator().manual_seed(100 + step)
+            # every FSDP coordinate trains on its own batch; TP ranks of a replica share it
+            all_ids = torch.randint(0, 1024, (a.fsdp, batch, 64), generator=gen)
+            ids = all_ids[ctx.coordinate.fsdp].to(ctx.device)
+            res = tr.train_step(ids)
+            opt.zero_grad()
+            flat = all_ids.reshape(-1, 64)
+            ref = dense(flat, labels=flat)
+            ref.loss.backward()
+            opt.step()
+            rows.append(dict(step=step, loss=res.loss, ref=ref.loss.item(), valid=res.valid_tokens))
+        full = rt.reconstruct_tp_local()
+        err, errs = 0.0, {}
+        for name, p in dense.named_parameters():
+            part = rt.qwen_partitions[name].local_slice(p.detach())
+            e = (full[name].cpu() - part).abs().max().item()
+            errs[name] = e
+            err = max(err, e)
+        events = {}
+        for e in rt.comm.events:
+            events[e["event_type"]] = events.get(e["event_type"], 0) + 1
+        kinds = {}
+        for t in rt.comm.tickets:
+            kinds[t.kind] = kinds.get(t.kind, 0) + 1
+        seq = [(t.pg_id, t.kind) for t in rt.comm.tickets]
+        shard_ok = all(p.ndim == 1 and p.dtype == torch.float32 for p in model.parameters())
+        (out / f"result.rank{worker.rank}.json").write_text(json.dumps(dict(
+            rows=rows, param_err=err, events=events, kinds=kinds, seq=seq, shard_ok=shard_ok,
+            live=len(rt.comm.live_buffers), names=[n for n, _ in model.named_parameters()][:4],
+            units=len(rt.units), leaves=len(rt.registry), errs=errs)))
+        rt.comm.flush_diagnostics()
+
+
+if __name__ == "__main__":
+    main()
