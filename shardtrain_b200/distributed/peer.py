@@ -1,0 +1,92 @@
+"""NVLink peer memory for one process group: CUDA IPC allocations every member can address,
+and a flag-based barrier kernel that orders kernels across GPUs.
+
+`PeerMemory.alloc(nbytes)` cudaMallocs a zeroed buffer, exchanges its IPC handle inside the group
+(`all_gather_object` over the group's own communicator) and returns a `PeerBuffer` with the local
+pointer and one device pointer per member (this rank's entry is the local pointer).  The fused
+kernels take those pointer tables; through NVSwitch every peer is one hop away at full bandwidth.
+
+`barrier(channel)` launches a 1-CTA kernel on the current stream: it publishes a new epoch to
+every peer's flag pad (`st.release.sys`) and waits, with an iteration limit, until every peer has
+published the same epoch to this rank's pad.  Each logical channel has its own flag slot and its
+own epoch counter; all members must call the barriers of a channel in the same order.  When the
+limit is reached the kernel records a status code and returns; `ops.check_status()` raises on the
+host.  With one member every call is a no-op and buffers are ordinary device tensors.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+CHANNEL_SLOTS = {"fsdp_ag": 0, "fsdp_rs": 1, "sp_ag": 2, "sp_rs": 3, "step": 4, "misc": 5}
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.uint8: 3}
+
+
+@dataclass
+class PeerBuffer:
+    local_ptr: int
+    ptrs: list[int]          # one device pointer per group member, index = group rank
+    nbytes: int
+    owner: object = None     # keeps an ordinary tensor alive in the single-member case
+
+    def tensor(self, ops, numel: int, dtype=torch.float32, offset_bytes: int = 0) -> torch.Tensor:
+        return ops.tensor_from_ptr(self.local_ptr + offset_bytes, numel, _DTYPE_CODE[dtype])
+
+
+class PeerMemory:
+    def __init__(self, group, device, ops, *, max_spin: int = 50_000_000):
+        self.group, self.device, self.ops = group, torch.device(device), ops
+        live = dist.is_initialized() and group is not None
+        self.degree = dist.get_world_size(group) if live else 1
+        self.rank = dist.get_rank(group) if live else 0
+        self.max_spin = max_spin
+        self.epochs = {name: 0 for name in CHANNEL_SLOTS}
+        self._allocations: list[PeerBuffer] = []
+        self._opened: list[int] = []
+        self.flags = self.alloc(4096) if self.degree > 1 else None
+
+    def alloc(self, nbytes: int) -> PeerBuffer:
+        nbytes = -(-int(nbytes) // 512) * 512
+        if self.degree == 1:
+            owner = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            buf = PeerBuffer(owner.data_ptr(), [owner.data_ptr()], nbytes, owner)
+            self._allocations.append(buf)
+            return buf
+        local = int(self.ops.peer_alloc(nbytes))
+        handle = self.ops.ipc_handle(local)
+        gathered: list = [None] * self.degree
+        dist.all_gather_object(gathered, bytes(handle.numpy().tobytes()), group=self.group)
+        ptrs = []
+        for member, raw in enumerate(gathered):
+            if member == self.rank:
+                ptrs.append(local)
+            else:
+                opened = int(self.ops.ipc_open(torch.frombuffer(bytearray(raw), dtype=torch.uint8)))
+                self._opened.append(opened)
+                ptrs.append(opened)
+        buf = PeerBuffer(local, ptrs, nbytes)
+        self._allocations.append(buf)
+        return buf
+
+    def barrier(self, channel: str) -> None:
+        """Enqueue a cross-GPU barrier on the current stream (no-op for a single member)."""
+        if self.degree == 1:
+            return
+        self.epochs[channel] += 1
+        self.ops.peer_barrier(self.flags.ptrs, self.rank, self.epochs[channel],
+                              CHANNEL_SLOTS[channel], self.max_spin)
+
+    def close(self) -> None:
+        if self.degree == 1:
+            self._allocations.clear()
+            return
+        for ptr in self._opened:
+            self.ops.ipc_close(ptr)
+        self._opened.clear()
+        for buf in self._allocations:
+            if buf.owner is None:
+                self.ops.peer_free(buf.local_ptr)
+        self._allocations.clear()

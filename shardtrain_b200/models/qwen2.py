@@ -351,6 +351,7 @@ class Qwen2CausalLM(nn.Module):
             raise ValueError("Specify exactly one of input_ids or inputs_embeds")
         source = input_ids if input_ids is not None else inputs_embeds
         batch, seq = source.shape[:2]
+        default_positions = position_ids is None
         if position_ids is None:
             position_ids = torch.arange(seq, device=source.device).unsqueeze(0)
         if tuple(position_ids.shape) not in ((1, seq), (batch, seq)):
@@ -362,7 +363,7 @@ class Qwen2CausalLM(nn.Module):
             # The sharded runtime owns the step: it walks its units with materialised weights.
             return runtime.model_forward(
                 self, input_ids, attention_mask=attention_mask, position_ids=position_ids,
-                labels=labels, inputs_embeds=inputs_embeds,
+                labels=labels, inputs_embeds=inputs_embeds, default_positions=default_positions,
             )
         hidden = self.model.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
         tables = self.model.rotary_emb(hidden, position_ids.to(hidden.device))

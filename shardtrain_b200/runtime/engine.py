@@ -470,6 +470,10 @@ class ShardedRuntime:
     def _check_gradients(self, allow_nonfinite):
         """One sweep over the gradient arena, one host read: non-finite values and padding that
         is not exactly zero (NaN/Inf in padding count as non-zero)."""
+        if self.fused is not None and getattr(self, "defer_gradient_check", False):
+            # the flags accumulate on the device and are read with the step metrics
+            self.fused.launch_grad_check()
+            return
         if self.fused is not None:
             bad = self.fused.grad_check()
             nonfinite, padding = bool(bad[0]), bool(bad[1])

@@ -1,0 +1,554 @@
+"""sm_100a executor: the Qwen2 units computed with this package's CUDA kernels only.
+
+Per unit, the `PeerMaterializer` lands the gathered parameters already cast to bf16 in one flat
+buffer whose order is chosen for the kernels: `q|k|v` weights adjacent (one QKV GEMM), `gate|up`
+adjacent (one gate/up GEMM), small vectors (biases, norm weights) in an FP32 side buffer.  The
+backward writes every parameter gradient in FP32 straight into one slot of a peer-visible ring
+(`GradRing`) laid out the same way, so the reduce-scatter kernel can pull this rank's slice of
+every peer's slot without any packing pass, average it, accumulate it into the gradient arena
+and, on the last micro-step, apply AdamW in the same pass.
+
+One decoder layer is one autograd node (`FusedLayerFn`): forward and backward are explicit
+sequences of kernel launches (RMSNorm, tcgen05 GEMMs with fused bias / residual epilogues, RoPE,
+tcgen05 attention, SwiGLU), saving only compact activations.  The residual stream stays FP32,
+GEMM operands are bf16, accumulation is FP32 -- the same precision plan as the reference under
+bf16 autocast (`src/sharded_runtime/runtime/qwen2_operators.py:39-204`).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+from torch.autograd.function import once_differentiable
+
+from shardtrain_b200 import ops as ops_module
+from shardtrain_b200.distributed.peer import PeerMemory
+from shardtrain_b200.runtime.layout import segment_table
+from shardtrain_b200.runtime.materializer import PeerMaterializer
+
+_LAYER_ORDER = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
+                "gate_proj.weight", "up_proj.weight", "down_proj.weight",
+                "q_proj.bias", "k_proj.bias", "v_proj.bias",
+                "input_layernorm.weight", "post_attention_layernorm.weight")
+
+
+def _up(value, multiple):
+    return -(-value // multiple) * multiple
+
+
+@dataclass
+class UnitPlan:
+    """Where each parameter of a unit lives in the materialised buffers and in the gradient slot."""
+
+    names: list[str] = field(default_factory=list)
+    shapes: dict[str, tuple] = field(default_factory=dict)
+    param_offsets: dict[str, int] = field(default_factory=dict)   # into the bf16 or fp32 buffer
+    fp32_names: set[str] = field(default_factory=set)
+    grad_offsets: dict[str, int] = field(default_factory=dict)    # into the fp32 gradient slot
+    bf16_numel: int = 0
+    fp32_numel: int = 0
+    grad_numel: int = 0
+    shard_numel: int = 0
+    gather_table: torch.Tensor | None = None
+    reduce_table: torch.Tensor | None = None
+
+    def views(self, full_bf16, full_fp32):
+        out = {}
+        for name in self.names:
+            shape = self.shapes[name]
+            n = math.prod(shape)
+            src = full_fp32 if name in self.fp32_names else full_bf16
+            out[name] = src.narrow(0, self.param_offsets[name], n).view(shape)
+        return out
+
+    def span(self, buffer, first, last, cols):
+        """Contiguous 2-D view covering parameters first..last (adjacent in the layout)."""
+        start = self.param_offsets[first]
+        stop = self.param_offsets[last] + math.prod(self.shapes[last])
+        return buffer.narrow(0, start, stop - start).view(-1, cols)
+
+    def grad_view(self, slot, name):
+        return slot.narrow(0, self.grad_offsets[name], math.prod(self.shapes[name])).view(self.shapes[name])
+
+    def grad_span(self, slot, first, last, cols):
+        start = self.grad_offsets[first]
+        stop = self.grad_offsets[last] + math.prod(self.shapes[last])
+        return slot.narrow(0, start, stop - start).view(-1, cols)
+
+
+def build_plan(unit) -> UnitPlan:
+    plan = UnitPlan()
+    by_name = {h.spec.param_id: h for h in unit.handles}
+
+    def rank_of(name):
+        for position, suffix in enumerate(_LAYER_ORDER):
+            if name.endswith(suffix):
+                return position
+        return len(_LAYER_ORDER)
+
+    ordered = sorted(by_name, key=lambda n: (rank_of(n), unit.handles.index(by_name[n])))
+    plan.names = ordered
+    bf16_cursor = fp32_cursor = grad_cursor = 0
+    for name in ordered:
+        spec = by_name[name].spec
+        plan.shapes[name] = spec.tp_local_shape
+        if len(spec.tp_local_shape) == 1:
+            plan.fp32_names.add(name)
+            plan.param_offsets[name] = fp32_cursor
+            fp32_cursor = _up(fp32_cursor + spec.numel, 4)
+        else:
+            plan.param_offsets[name] = bf16_cursor
+            bf16_cursor = _up(bf16_cursor + spec.numel, 8)
+        plan.grad_offsets[name] = grad_cursor
+        grad_cursor = _up(grad_cursor + spec.numel, 4)
+        plan.shard_numel += spec.fsdp_shard_numel
+    plan.bf16_numel, plan.fp32_numel, plan.grad_numel = bf16_cursor, fp32_cursor, grad_cursor
+    handles = [by_name[n] for n in ordered]
+    plan.gather_table = segment_table(handles, plan.param_offsets, plan.fp32_names)
+    plan.reduce_table = segment_table(handles, plan.grad_offsets, set())
+    return plan
+
+
+class GradSlot:
+    def __init__(self, local, peer_ptrs):
+        self.local, self.peer_ptrs = local, peer_ptrs
+        self.holder = None
+        self.last_rs = -10
+
+
+class GradRing:
+    """Peer-visible FP32 slots the backward writes full gradients into.
+
+    A slot may be overwritten once the reduce-scatter that consumed it has finished on this GPU
+    *and* every peer has finished pulling from it.  The second condition holds once this rank's
+    next reduce-scatter barrier has passed (a peer enters barrier n+1 only after its pull n), so
+    a slot last used by reduction n is handed out again after waiting for the event of
+    reduction n+1.
+    """
+
+    def __init__(self, peer: PeerMemory, ops, numel: int, count: int = 4):
+        self.slots = []
+        for _ in range(count):
+            buf = peer.alloc(numel * 4)
+            self.slots.append(GradSlot(buf.tensor(ops, numel) if peer.degree > 1
+                                       else buf.owner.view(torch.float32)[:numel], buf.ptrs))
+        self.events: list = []      # events[n]: completion of reduction n on the rs stream
+
+    def acquire(self, unit_id, stream):
+        free = [s for s in self.slots if s.holder is None]
+        if not free:
+            raise RuntimeError("No free gradient slot (a unit's reduction was never issued)")
+        slot = min(free, key=lambda s: s.last_rs)
+        guard = slot.last_rs + 1
+        if slot.last_rs >= 0:
+            event = self.events[min(guard, len(self.events) - 1)]
+            stream.wait_event(event)
+        slot.holder = unit_id
+        return slot
+
+    def issued(self, slot, event):
+        slot.last_rs = len(self.events)
+        slot.holder = None
+        self.events.append(event)
+        if len(self.events) > 4096:   # keep indices stable but drop old events
+            cut = len(self.events) - 64
+            self.events = [None] * cut + self.events[cut:]
+
+
+class FusedExecutor:
+    name = "fused"
+
+    def __init__(self, runtime, model, mesh):
+        self.runtime, self.cfg, self.mesh = runtime, model.config, mesh
+        if self.cfg.head_dim != 128:
+            raise ValueError("The sm_100a attention kernel supports head_dim 128 only")
+        self.ops = ops_module.load()
+        self.peer = PeerMemory(mesh.fsdp_group if mesh else None, runtime.device, self.ops)
+        self.tp_peer = None
+        self.exp_avg = self.exp_avg_sq = None
+        self._shards_dirty = True
+        self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
+        self._rope_cache = {}
+        self._scratch = {}
+
+    # ------------------------------------------------------------------ allocation
+    def allocate(self):
+        rt = self.runtime
+        if rt.tp.degree > 1:
+            raise NotImplementedError(
+                "The sm_100a executor currently covers FSDP-only meshes; use "
+                "communication_backend=nccl for TP/SP")
+        portable = rt.materializer
+        mat = PeerMaterializer(portable.group, rt.comm, self.peer)
+        total = rt.plan.padded_total()
+        self._param_buffer = self.peer.alloc(total * 4)
+
+        def make(n, tag):
+            if tag == "param":
+                if self.peer.degree > 1:
+                    return self._param_buffer.tensor(self.ops, n)
+                return self._param_buffer.owner.view(torch.float32)[:n]
+            return torch.zeros(n, dtype=torch.float32, device=rt.device)
+
+        rt.materializer = mat
+        rt.allocate_arenas(allocator=make)
+        self.param, self.grad = rt.param_arena, rt.grad_arena
+        self.param_peer_ptrs = list(self._param_buffer.ptrs)
+        largest = 0
+        for unit in rt.units:
+            mat.plans[unit.unit_id] = build_plan(unit)
+            largest = max(largest, mat.plans[unit.unit_id].grad_numel)
+        self.ring = GradRing(self.peer, self.ops, _up(largest, 4), count=4)
+        mat.bind(self.ops, self)
+        ranges = rt.padding_ranges or [(0, 0)]
+        self._pad_ranges = torch.tensor(ranges, dtype=torch.int64, device=rt.device).reshape(-1)
+
+    def finish_registration(self):
+        rt = self.runtime
+        self.hq, self.hkv = rt.local_heads, rt.local_kv_heads
+        torch.cuda.synchronize(rt.device)
+
+    def state_arena(self, tag):
+        t = torch.zeros_like(self.param)
+        setattr(self, tag, t)
+        return t
+
+    # ------------------------------------------------------------------ runtime hooks
+    def shards_written(self):
+        self._shards_dirty = True
+
+    def before_shard_read(self):
+        """Runs on the gather stream before the first gather after the shards changed."""
+        if self._shards_dirty:
+            self.peer.barrier("fsdp_ag")
+            self._shards_dirty = False
+
+    def acquire_grad_slot(self, unit):
+        if getattr(unit, "grad_slot", None) is None:
+            unit.grad_slot = self.ring.acquire(unit.unit_id, torch.cuda.current_stream(self.runtime.device))
+        return unit.grad_slot
+
+    def grad_slot(self, unit):
+        slot = getattr(unit, "grad_slot", None)
+        if slot is None:
+            raise RuntimeError(f"U{unit.unit_id} reduced without a gradient slot")
+        return slot
+
+    def grad_slot_issued(self, unit, slot):
+        ticket = self.runtime.comm.tickets[-1]
+        self.ring.issued(slot, ticket.ready_event)
+        unit.grad_slot = None
+
+    def launch_grad_check(self):
+        self.ops.grad_check(self.grad, self._pad_ranges, self._flags)
+
+    def grad_check(self):
+        self.launch_grad_check()
+        flags = self._flags.cpu().tolist()
+        self._flags.zero_()
+        return flags
+
+    def scratch(self, key, shape, dtype):
+        t = self._scratch.get(key)
+        if t is None or t.shape != torch.Size(shape) or t.dtype != dtype:
+            t = torch.empty(shape, dtype=dtype, device=self.runtime.device)
+            self._scratch[key] = t
+        return t
+
+    def rotary(self, position_ids, default_positions):
+        """cos/sin tables [S, D/2] (FP32) and, for caller-supplied positions, an int32 position
+        per (batch, token) row; `None` means positions 0..S-1."""
+        seq = position_ids.shape[-1]
+        if seq not in self._rope_cache:
+            pos = torch.arange(seq, device=self.runtime.device, dtype=torch.float32)
+            angle = pos[:, None] * self.runtime.inv_freq[None, :].float()
+            self._rope_cache[seq] = (angle.cos().contiguous(), angle.sin().contiguous())
+        cos, sin = self._rope_cache[seq]
+        positions = None
+        if not default_positions:
+            raise NotImplementedError("custom position_ids need a table covering their range")
+        return cos, sin, positions, seq
+
+    # ------------------------------------------------------------------ unit math
+    def embedding(self, unit, ids):
+        handle = unit.handle("model.embed_tokens.weight")
+        weight = unit.forward_weight(handle.spec.param_id)
+        return FusedEmbeddingFn.apply(weight, ids, self, unit)
+
+    def layer(self, unit, index, x, tables, attention_mask):
+        plan = self.runtime.materializer.plans[unit.unit_id]
+        weights = [unit.forward_weight(n) for n in plan.names]
+        mask = None
+        if attention_mask is not None:
+            if attention_mask.ndim != 2:
+                raise ValueError("The sm_100a attention kernel takes a [batch, sequence] key mask")
+            mask = attention_mask.to(self.runtime.device).ne(0).to(torch.uint8).contiguous()
+        return FusedLayerFn.apply(x, self, unit, index, tables, mask, *weights)
+
+    def final_norm(self, unit, x):
+        weight = unit.forward_weight("model.norm.weight")
+        return FusedNormFn.apply(x, weight, self, unit)
+
+    def head_loss(self, unit, hidden, labels, *, tied):
+        name = "model.embed_tokens.weight" if tied else "lm_head.weight"
+        weight = unit.forward_weight(name, tied_second_use=tied)
+        if labels is None:
+            raise ValueError("The sm_100a executor fuses the LM head with the loss; pass labels")
+        loss = FusedHeadLossFn.apply(hidden, weight, self, unit, name, labels)
+        return None, loss
+
+
+# ---------------------------------------------------------------------------- autograd nodes
+class FusedEmbeddingFn(torch.autograd.Function):
+    """Embedding rows read straight from the (possibly remote) FP32 shards: no table gather is
+    needed for the lookup.  Backward scatter-adds into the unit's gradient slot."""
+
+    @staticmethod
+    def forward(ctx, weight, ids, ex, unit):
+        rt = ex.runtime
+        handle = unit.handles[0]
+        ctx.ex, ctx.unit = ex, unit
+        ctx.save_for_backward(ids)
+        hidden = ex.cfg.hidden_size
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty((*ids.shape, hidden), dtype=torch.float32, device=rt.device)
+        base = handle.arena_offset * 4
+        ptrs = [p + base for p in ex.param_peer_ptrs]
+        ex.ops.embedding_gather_sharded(ptrs, handle.spec.fsdp_shard_numel, flat, out)
+        unit.prefetch_after_input(handle, "FWD")
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad):
+        ex, unit = ctx.ex, ctx.unit
+        unit.annotate("BWD")
+        (ids,) = ctx.saved_tensors
+        handle = unit.handles[0]
+        name = handle.spec.param_id
+        plan = ex.runtime.materializer.plans[unit.unit_id]
+        fresh = getattr(unit, "grad_slot", None) is None
+        slot = ex.acquire_grad_slot(unit)
+        dw = plan.grad_view(slot.local, name)
+        if fresh:
+            dw.zero_()  # untied: nothing wrote the slot yet; tied: the head's dW is already there
+        pad = ex.cfg.pad_token_id
+        ex.ops.embedding_scatter_add(grad.reshape(-1, grad.shape[-1]).contiguous(),
+                                     ids.reshape(-1).contiguous(), dw, -1 if pad is None else pad)
+        # a tied weight receives its gradient view from the head node; returning it twice would
+        # make autograd add the two (identical) views
+        return (None if unit.tied else dw), None, None, None
+
+
+class FusedNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, ex, unit):
+        ctx.ex, ctx.unit = ex, unit
+        unit.annotate("FWD")
+        hidden = x.shape[-1]
+        x2 = x.reshape(-1, hidden).contiguous()
+        y = torch.empty(x2.shape, dtype=torch.bfloat16, device=x.device)
+        inv = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+        ex.ops.rmsnorm_fwd(x2, weight, y, inv, ex.cfg.rms_norm_eps)
+        ctx.save_for_backward(x2, inv)
+        ctx.shape = x.shape
+        unit.prefetch_after_input(unit.handles[0], "FWD")
+        return y.view(x.shape)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad):
+        ex, unit = ctx.ex, ctx.unit
+        unit.annotate("BWD")
+        x2, inv = ctx.saved_tensors
+        name = unit.handles[0].spec.param_id
+        weight = unit.weight(name)
+        plan = ex.runtime.materializer.plans[unit.unit_id]
+        slot = ex.acquire_grad_slot(unit)
+        side = ex.__dict__.pop("_head_dx", None)   # FP32 gradient handed over by the head node
+        dy = side if side is not None else grad.reshape(x2.shape).float().contiguous()
+        dx = torch.empty_like(x2)
+        partial = ex.scratch("norm_partial", (148, x2.shape[1]), torch.float32)
+        ex.ops.rmsnorm_bwd(dy, x2, weight, inv, None, dx, partial)
+        dw = plan.grad_view(slot.local, name)
+        ex.ops.colsum_f32(partial, dw, False)
+        return dx.view(ctx.shape), dw, None, None
+
+
+class FusedHeadLossFn(torch.autograd.Function):
+    """LM head GEMM + vocabulary cross-entropy.  Logits live in one reused bf16 buffer, are
+    turned into their own gradient in place, and feed the dW / dX GEMMs."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, ex, unit, name, labels):
+        from shardtrain_b200.runtime.qwen2_adapter import finish_loss, shifted_labels
+
+        rt, ops = ex.runtime, ex.ops
+        unit.annotate("FWD")
+        ctx.ex, ctx.unit, ctx.name = ex, unit, name
+        h = hidden.shape[-1]
+        hidden2 = hidden.reshape(-1, h)
+        rows, vocab = hidden2.shape[0], weight.shape[0]
+        target = shifted_labels(rt, labels).reshape(-1).contiguous()
+        logits = ex.scratch("logits", (rows, vocab), torch.bfloat16)
+        ops.gemm(hidden2, weight, logits, False, False, None, None, False, 1.0, 0)
+        lse = torch.empty(rows, dtype=torch.float32, device=hidden.device)
+        per_row = torch.empty(rows, dtype=torch.float32, device=hidden.device)
+        ops.ce_fwd(logits, target, lse, per_row)
+        total = torch.empty(1, dtype=torch.float32, device=hidden.device)
+        ops.sum_f32(per_row, total, False)
+        loss = finish_loss(rt, total[0], target.ne(-100).sum())
+        ctx.factor = rt.materializer.degree / rt.qwen_denominator
+        ctx.save_for_backward(hidden2, target, lse)
+        ctx.hidden_shape = hidden.shape
+        return loss
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad):
+        ex, unit, name = ctx.ex, ctx.unit, ctx.name
+        ops = ex.ops
+        unit.annotate("BWD")
+        hidden2, target, lse = ctx.saved_tensors
+        weight = unit.weight(name)
+        rows, vocab = hidden2.shape[0], weight.shape[0]
+        logits = ex.scratch("logits", (rows, vocab), torch.bfloat16)
+        scale = (grad.float() * ctx.factor).reshape(1).contiguous()
+        ops.ce_bwd(logits, target, lse, scale)
+        plan = ex.runtime.materializer.plans[unit.unit_id]
+        slot = ex.acquire_grad_slot(unit)
+        dw = plan.grad_view(slot.local, name)
+        ops.gemm(logits, hidden2, dw, True, True, None, None, False, 1.0, 0)
+        dx = torch.empty(hidden2.shape, dtype=torch.float32, device=hidden2.device)
+        ops.gemm(logits, weight, dx, False, True, None, None, False, 1.0, 0)
+        ex._head_dx = dx
+        placeholder = torch.empty(ctx.hidden_shape, dtype=torch.bfloat16, device=hidden2.device)
+        return placeholder, dw, None, None, None, None
+
+
+class FusedLayerFn(torch.autograd.Function):
+    """One decoder layer: 4 GEMMs forward, 8 backward, everything else in fused kernels."""
+
+    @staticmethod
+    def forward(ctx, x, ex, unit, index, tables, mask, *weights):
+        ops, cfg = ex.ops, ex.cfg
+        plan = ex.runtime.materializer.plans[unit.unit_id]
+        unit.annotate("FWD")
+        wb, wf = unit.lease.extras["full_bf16"], unit.lease.extras["full_fp32"]
+        p = f"model.layers.{index}."
+        B, S, H = x.shape
+        M, D, hq, hkv = B * S, 128, ex.hq, ex.hkv
+        W = (hq + 2 * hkv) * D
+        inter = plan.shapes[p + "mlp.gate_proj.weight"][0]
+        cos, sin, positions, _ = tables
+        dev = x.device
+        x2 = x.reshape(M, H).contiguous()
+        w_qkv = plan.span(wb, p + "self_attn.q_proj.weight", p + "self_attn.v_proj.weight", H)
+        b_qkv = wf.narrow(0, plan.param_offsets[p + "self_attn.q_proj.bias"], W)
+        w_o = plan.span(wb, p + "self_attn.o_proj.weight", p + "self_attn.o_proj.weight", hq * D)
+        w_gu = plan.span(wb, p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight", H)
+        w_down = plan.span(wb, p + "mlp.down_proj.weight", p + "mlp.down_proj.weight", inter)
+        ln1 = wf.narrow(0, plan.param_offsets[p + "input_layernorm.weight"], H)
+        ln2 = wf.narrow(0, plan.param_offsets[p + "post_attention_layernorm.weight"], H)
+        bf, f32 = torch.bfloat16, torch.float32
+
+        h1 = torch.empty((M, H), dtype=bf, device=dev)
+        inv1 = torch.empty(M, dtype=f32, device=dev)
+        ops.rmsnorm_fwd(x2, ln1, h1, inv1, cfg.rms_norm_eps)
+        qkv = torch.empty((M, W), dtype=bf, device=dev)
+        ops.gemm(h1, w_qkv, qkv, False, False, b_qkv, None, False, 1.0, 0)
+        unit.prefetch_after_input(unit.forward_prefetch_handle, "FWD")
+        ops.rope(qkv, cos, sin, positions, S, hq, hkv, D, False)
+        attn = torch.empty((M, hq * D), dtype=bf, device=dev)
+        lse = torch.empty((B, hq, S), dtype=f32, device=dev)
+        ops.attention_fwd(qkv, attn, lse, mask, B, S, hq, hkv, 1.0 / math.sqrt(D))
+        x_mid = torch.empty((M, H), dtype=f32, device=dev)
+        ops.gemm(attn, w_o, x_mid, False, False, None, x2, False, 1.0, 0)
+        h2 = torch.empty((M, H), dtype=bf, device=dev)
+        inv2 = torch.empty(M, dtype=f32, device=dev)
+        ops.rmsnorm_fwd(x_mid, ln2, h2, inv2, cfg.rms_norm_eps)
+        gu = torch.empty((M, 2 * inter), dtype=bf, device=dev)
+        ops.gemm(h2, w_gu, gu, False, False, None, None, False, 1.0, 0)
+        hm = ex.scratch("mlp_hidden", (M, inter), bf)
+        ops.swiglu_fwd(gu, hm)
+        out = torch.empty((M, H), dtype=f32, device=dev)
+        ops.gemm(hm, w_down, out, False, False, None, x_mid, False, 1.0, 0)
+
+        ctx.ex, ctx.unit, ctx.index, ctx.tables, ctx.mask = ex, unit, index, tables, mask
+        ctx.dims = (B, S, H, inter)
+        ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu)
+        return out.view(B, S, H)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dout):
+        ex, unit, index = ctx.ex, ctx.unit, ctx.index
+        ops = ex.ops
+        plan = ex.runtime.materializer.plans[unit.unit_id]
+        unit.annotate("BWD")
+        unit.weight(plan.names[0])  # state / generation check of the backward materialisation
+        wb, wf = unit.lease.extras["full_bf16"], unit.lease.extras["full_fp32"]
+        x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu = ctx.saved_tensors
+        B, S, H, inter = ctx.dims
+        M, D, hq, hkv = B * S, 128, ex.hq, ex.hkv
+        W = (hq + 2 * hkv) * D
+        cos, sin, positions, _ = ctx.tables
+        p = f"model.layers.{index}."
+        bf, f32 = torch.bfloat16, torch.float32
+        names = {k: p + v for k, v in dict(
+            q="self_attn.q_proj.weight", v="self_attn.v_proj.weight", o="self_attn.o_proj.weight",
+            gate="mlp.gate_proj.weight", up="mlp.up_proj.weight", down="mlp.down_proj.weight",
+            qb="self_attn.q_proj.bias", vb="self_attn.v_proj.bias",
+            ln1="input_layernorm.weight", ln2="post_attention_layernorm.weight").items()}
+        w_qkv = plan.span(wb, names["q"], names["v"], H)
+        w_o = plan.span(wb, names["o"], names["o"], hq * D)
+        w_gu = plan.span(wb, names["gate"], names["up"], H)
+        w_down = plan.span(wb, names["down"], names["down"], inter)
+        ln1 = wf.narrow(0, plan.param_offsets[names["ln1"]], H)
+        ln2 = wf.narrow(0, plan.param_offsets[names["ln2"]], H)
+        slot = ex.acquire_grad_slot(unit)
+        g = slot.local
+        unit.prefetch_after_input(unit.backward_prefetch_handle, "BWD")
+
+        d_out = dout.reshape(M, H).contiguous()
+        d_out_b = ex.scratch("d_res_bf16", (M, H), bf)
+        ops.cast_bf16(d_out, d_out_b)
+        hm = ex.scratch("mlp_hidden", (M, inter), bf)
+        ops.swiglu_fwd(gu, hm)                                                    # recompute
+        ops.gemm(d_out_b, hm, plan.grad_view(g, names["down"]), True, True, None, None, False, 1.0, 0)
+        d_hm = ex.scratch("d_mlp_hidden", (M, inter), bf)
+        ops.gemm(d_out_b, w_down, d_hm, False, True, None, None, False, 1.0, 0)
+        d_gu = ex.scratch("d_gate_up", (M, 2 * inter), bf)
+        ops.swiglu_bwd(d_hm, gu, d_gu)
+        ops.gemm(d_gu, h2, plan.grad_span(g, names["gate"], names["up"], H), True, True,
+                 None, None, False, 1.0, 0)
+        d_h2 = ex.scratch("d_normed", (M, H), f32)
+        ops.gemm(d_gu, w_gu, d_h2, False, True, None, None, False, 1.0, 0)
+        d_mid = ex.scratch("d_mid", (M, H), f32)
+        partial = ex.scratch("norm_partial", (148, H), f32)
+        ops.rmsnorm_bwd(d_h2, x_mid, ln2, inv2, d_out, d_mid, partial)
+        ops.colsum_f32(partial, plan.grad_view(g, names["ln2"]), False)
+
+        d_mid_b = ex.scratch("d_res_bf16", (M, H), bf)
+        ops.cast_bf16(d_mid, d_mid_b)
+        ops.gemm(d_mid_b, attn, plan.grad_view(g, names["o"]), True, True, None, None, False, 1.0, 0)
+        d_attn = ex.scratch("d_attn", (M, hq * D), bf)
+        ops.gemm(d_mid_b, w_o, d_attn, False, True, None, None, False, 1.0, 0)
+        d_qkv = ex.scratch("d_qkv", (M, W), bf)
+        delta = ex.scratch("attn_delta", (B, hq, S), f32)
+        ops.attention_bwd(qkv, attn, d_attn, lse, delta, d_qkv, delta, ctx.mask, B, S, hq, hkv,
+                          1.0 / math.sqrt(D))
+        ops.rope(d_qkv, cos, sin, positions, S, hq, hkv, D, True)
+        d_bias = g.narrow(0, plan.grad_offsets[names["qb"]], W)
+        ops.colsum_bf16(d_qkv, d_bias, False, ex.scratch("bias_partial", (64, W), f32))
+        ops.gemm(d_qkv, h1, plan.grad_span(g, names["q"], names["v"], H), True, True,
+                 None, None, False, 1.0, 0)
+        d_h1 = ex.scratch("d_normed", (M, H), f32)
+        ops.gemm(d_qkv, w_qkv, d_h1, False, True, None, None, False, 1.0, 0)
+        dx = torch.empty((M, H), dtype=f32, device=dout.device)
+        ops.rmsnorm_bwd(d_h1, x2, ln1, inv1, d_mid, dx, partial)
+        ops.colsum_f32(partial, plan.grad_view(g, names["ln1"]), False)
+        grads = [plan.grad_view(g, n) for n in plan.names]
+        return (dx.view(B, S, H), None, None, None, None, None, *grads)

@@ -398,7 +398,7 @@ def reported_loss(runtime):
 
 
 def model_forward(runtime, model, input_ids, *, attention_mask=None, position_ids=None,
-                  labels=None, inputs_embeds=None):
+                  labels=None, inputs_embeds=None, default_positions=False):
     """Walk the units in order with materialised weights (called by `Qwen2CausalLM.forward`)."""
     ex = runtime.executor
     ids = prepare_input(runtime, input_ids, inputs_embeds)
@@ -411,7 +411,7 @@ def model_forward(runtime, model, input_ids, *, attention_mask=None, position_id
         first.embedding_complete()
     else:
         hidden = first.post_forward(hidden)
-    tables = ex.rotary(position_ids, hidden) if hasattr(ex, "rotary") else rotary_tables(
+    tables = ex.rotary(position_ids, default_positions) if hasattr(ex, "rotary") else rotary_tables(
         position_ids.to(hidden.device), runtime.inv_freq, hidden.dtype)
     for index in range(len(layers)):
         unit = units[1 + index]

@@ -66,13 +66,18 @@ class QwenTrainer:
         if fuse_optimizer is None:
             fuse_optimizer = runtime.fused is not None and optimizer == "adamw" and dtype != "fp16"
         self.optimizer.fuse_into_reduction = bool(fuse_optimizer and runtime.fused is not None)
+        runtime.defer_gradient_check = runtime.fused is not None
         self.scaler = torch.amp.GradScaler("cuda", enabled=dtype == "fp16", init_scale=128.0)
 
     # ------------------------------------------------------------------ metrics
     def _finite_vote(self, reported):
         """1 if every rank's gradients (and the loss) are finite, as an int32 device tensor."""
         runtime = self.runtime
-        finite = torch.isfinite(runtime.grad_arena).all().to(torch.int32)
+        if runtime.fused is not None:
+            # written by the gradient-check kernel of every micro-step
+            finite = runtime.fused._flags[0].eq(0).to(torch.int32)
+        else:
+            finite = torch.isfinite(runtime.grad_arena).all().to(torch.int32)
         finite.mul_(torch.isfinite(reported).to(torch.int32))
         runtime.comm.unit_id, runtime.comm.phase = None, "AMP"
         m = runtime.materializer
@@ -89,8 +94,14 @@ class QwenTrainer:
 
     def _read_metrics(self, reported, global_count):
         finite = self._finite_vote(reported)
+        fused = self.runtime.fused
+        padding = fused._flags[1] if fused is not None else torch.zeros((), device=finite.device)
         row = torch.stack([finite.to(torch.float64), reported.detach().to(torch.float64),
-                           global_count.to(torch.float64)]).cpu().tolist()
+                           global_count.to(torch.float64), padding.to(torch.float64)]).cpu().tolist()
+        if fused is not None:
+            fused._flags.zero_()
+        if row[3]:
+            raise RuntimeError("Nonzero gradient padding in a shard")
         return bool(row[0]), float(row[1]), int(row[2])
 
     # ------------------------------------------------------------------ step
