@@ -1,4 +1,5 @@
 // Host launcher of the tcgen05 GEMM: builds the TMA tensor maps and picks the tile width.
+#include <algorithm>
 #include <mutex>
 
 #include "api.h"
@@ -80,7 +81,14 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   if (attr_err != cudaSuccess) return attr_err;
   const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
   const int n_tiles = (c.N + BN - 1) / BN;
-  kernel<<<m_tiles * n_tiles, kGemmThreads, smem, stream>>>(ta, tb, ep, c.M, c.N, c.K, status);
+  static int sm_count = [] {
+    int dev = 0, n = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  const int grid = std::min(m_tiles * n_tiles, sm_count);   // persistent: one CTA per SM
+  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, ep, c.M, c.N, c.K, status);
   return cudaGetLastError();
 }
 

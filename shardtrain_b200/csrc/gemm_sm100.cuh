@@ -36,7 +36,8 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kGemmBK * 2;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // tiles + barriers (full, empty, accum) + tmem pointer + abort flag, plus 1 KB alignment slack
+  // tiles + barriers (full, empty, accumulator full/empty) + tmem pointer + abort flag, plus
+  // 1 KB alignment slack
   static constexpr int kTotal = kStages * kStageBytes + 1024 + 256;
 };
 
@@ -45,6 +46,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                          const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep, int M, int N,
                          int K, int* __restrict__ status) {
+  // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
+  // double buffered in TMEM (2 x BN columns) so the epilogue of one tile overlaps the MMAs of the
+  // next; the shared-memory operand pipeline runs across tile boundaries without draining.
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -53,34 +57,38 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   uint8_t* tiles = smem;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* accum_bar = empty_bar + STAGES;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2], 128 arrivals each
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + kGemmBK - 1) / kGemmBK;
+  constexpr int GROUP = 8;
+  const int group_span = GROUP * n_tiles;
 
   // Grouped rasterisation: walk up to 8 M-tiles before moving to the next N-tile so that the
   // CTAs resident at one time share operand tiles in L2.
-  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
-  const int n_tiles = (N + BN - 1) / BN;
-  constexpr int GROUP = 8;
-  const int tile = blockIdx.x;
-  const int group_span = GROUP * n_tiles;
-  const int first_m = (tile / group_span) * GROUP;
-  const int gm = min(m_tiles - first_m, GROUP);
-  const int tm = first_m + (tile % group_span) % gm;
-  const int tn = (tile % group_span) / gm;
-  const int m0 = tm * kGemmBM;
-  const int n0 = tn * BN;
-  const int num_kb = (K + kGemmBK - 1) / kGemmBK;
+  auto tile_origin = [&](int tile, int& m0, int& n0) {
+    const int first_m = (tile / group_span) * GROUP;
+    const int gm = min(m_tiles - first_m, GROUP);
+    m0 = (first_m + (tile % group_span) % gm) * kGemmBM;
+    n0 = ((tile % group_span) / gm) * BN;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -88,145 +96,175 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     prefetch_tensormap(&tma_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_ptr, BN);
+    tmem_alloc(tmem_ptr, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_d = *tmem_ptr;
+  const uint32_t tmem_base = *tmem_ptr;
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, status, kErrProducerEmptyWait)) {
-          *abort_flag = 1;
-          break;
-        }
-        uint8_t* sa = tiles + s * S::kStageBytes;
-        uint8_t* sb = sa + S::kABytes;
-        mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        if constexpr (!A_MN) {
-          tma_load_2d(sa, &tma_a, &full_bar[s], kb * kGemmBK, m0);
-        } else {
+      int it = 0;  // k-blocks issued so far, across tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m0, n0;
+        tile_origin(tile, m0, n0);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, status, kErrProducerEmptyWait)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles + s * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(&full_bar[s], S::kStageBytes);
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tma_a, &full_bar[s], kb * kGemmBK, m0);
+          } else {
 #pragma unroll
-          for (int c = 0; c < kGemmBM / 64; ++c)
-            tma_load_2d(sa + c * 8192, &tma_a, &full_bar[s], m0 + c * 64, kb * kGemmBK);
-        }
-        if constexpr (!B_MN) {
-          tma_load_2d(sb, &tma_b, &full_bar[s], kb * kGemmBK, n0);
-        } else {
+            for (int c = 0; c < kGemmBM / 64; ++c)
+              tma_load_2d(sa + c * 8192, &tma_a, &full_bar[s], m0 + c * 64, kb * kGemmBK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tma_b, &full_bar[s], kb * kGemmBK, n0);
+          } else {
 #pragma unroll
-          for (int c = 0; c < BN / 64; ++c)
-            tma_load_2d(sb + c * 8192, &tma_b, &full_bar[s], n0 + c * 64, kb * kGemmBK);
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * 8192, &tma_b, &full_bar[s], n0 + c * 64, kb * kGemmBK);
+          }
         }
-        issued = kb + 1;
       }
       // Error path only: wait (bounded) for copies this thread issued that nobody consumed.
       if (*abort_flag) {
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-          mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1, status, kErrDrainWait);
+        for (int k = max(0, it - STAGES); k < it; ++k)
+          mbar_wait(&full_bar[k % STAGES], (k / STAGES) & 1, status, kErrDrainWait);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(kGemmBM, BN, A_MN, B_MN);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], ph, status, kErrMmaFullWait)) {
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int ab = local & 1;
+        // the epilogue must have drained this accumulator buffer (two tiles ago)
+        if (!mbar_wait(&acc_empty[ab], ((local >> 1) & 1) ^ 1, status, kErrMmaFullWait)) {
           *abort_flag = 1;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t a_base = smem_u32(tiles + s * S::kStageBytes);
-        const uint32_t b_base = a_base + S::kABytes;
+        const uint32_t tmem_d = tmem_base + ab * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, status, kErrMmaFullWait)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(tiles + s * S::kStageBytes);
+          const uint32_t b_base = a_base + S::kABytes;
 #pragma unroll
-        for (int k = 0; k < kGemmBK / 16; ++k) {
-          // K-major: the 16-element K slice is 32 bytes further along each 128-byte row.
-          // MN-major: the slice is 16 K-rows (two 8-row swizzle atoms, 1024 B apart) further on;
-          // 64-wide MN chunks sit 8192 B apart (the leading-dimension byte offset).
-          const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + k * 2048, 8192, 1024)
-                                   : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
-          const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
-                                   : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-          tc_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < kGemmBK / 16; ++k) {
+            // K-major: the 16-element K slice is 32 bytes further along each 128-byte row.
+            // MN-major: the slice is 16 K-rows (two 8-row swizzle atoms, 1024 B apart) further
+            // on; 64-wide MN chunks sit 8192 B apart (the leading-dimension byte offset).
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            tc_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         }
-        tc_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        tc_commit(&acc_full[ab]);
       }
-      tc_commit(accum_bar);
     }
   } else {
     // Epilogue: 4 warps x 32 lanes = the 128 accumulator rows.
-    const bool ok = mbar_wait(accum_bar, 0, status, kErrEpilogueAccumWait);
-    tc_fence_after_sync();
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    const int64_t g_row = static_cast<int64_t>(m0) + row;
-    const bool row_ok = ok && g_row < M;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      int m0, n0;
+      tile_origin(tile, m0, n0);
+      const int ab = local & 1;
+      if (ok) ok = mbar_wait(&acc_full[ab], (local >> 1) & 1, status, kErrEpilogueAccumWait);
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + ab * BN;
+      const int64_t g_row = static_cast<int64_t>(m0) + row;
+      const bool row_ok = ok && g_row < M;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
-      tmem_ld_wait();
-      const int col0 = n0 + c * 32;
-      if (!row_ok || col0 >= N) continue;
-      float v[32];
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= N) continue;
+        float v[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ep.alpha;
-      if (ep.bias != nullptr) {
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ep.alpha;
+        if (ep.bias != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (col0 + i < N) v[i] += __ldg(ep.bias + col0 + i);
-      }
-      if (ep.out_fp32) {
-        float* o = reinterpret_cast<float*>(ep.out) + g_row * ep.ldo + col0;
-        const float* rs = ep.residual ? reinterpret_cast<const float*>(ep.residual) +
-                                            g_row * ep.ldo + col0
-                                      : nullptr;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          if (col0 + i >= N) break;
-          float4 x = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-          if (rs) {
-            const float4 y = *reinterpret_cast<const float4*>(rs + i);
-            x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-          }
-          if (ep.accumulate) {
-            const float4 y = *reinterpret_cast<const float4*>(o + i);
-            x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-          }
-          *reinterpret_cast<float4*>(o + i) = x;
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < N) v[i] += __ldg(ep.bias + col0 + i);
         }
-      } else {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + g_row * ep.ldo + col0;
-        const __nv_bfloat16* rs =
-            ep.residual ? reinterpret_cast<const __nv_bfloat16*>(ep.residual) + g_row * ep.ldo + col0
-                        : nullptr;
+        if (ep.out_fp32) {
+          float* o = reinterpret_cast<float*>(ep.out) + g_row * ep.ldo + col0;
+          const float* rs = ep.residual ? reinterpret_cast<const float*>(ep.residual) +
+                                              g_row * ep.ldo + col0
+                                        : nullptr;
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          if (col0 + i >= N) break;
-          if (rs) {
-            const uint4 y = *reinterpret_cast<const uint4*>(rs + i);
-            const __nv_bfloat162* yb = reinterpret_cast<const __nv_bfloat162*>(&y);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(yb[j]);
-              v[i + 2 * j] += f.x;
-              v[i + 2 * j + 1] += f.y;
+          for (int i = 0; i < 32; i += 4) {
+            if (col0 + i >= N) break;
+            float4 x = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            if (rs) {
+              const float4 y = *reinterpret_cast<const float4*>(rs + i);
+              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
             }
+            if (ep.accumulate) {
+              const float4 y = *reinterpret_cast<const float4*>(o + i);
+              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            }
+            *reinterpret_cast<float4*>(o + i) = x;
           }
-          uint4 pk;
-          pk.x = pack_bf16x2(v[i], v[i + 1]);
-          pk.y = pack_bf16x2(v[i + 2], v[i + 3]);
-          pk.z = pack_bf16x2(v[i + 4], v[i + 5]);
-          pk.w = pack_bf16x2(v[i + 6], v[i + 7]);
-          *reinterpret_cast<uint4*>(o + i) = pk;
+        } else {
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + g_row * ep.ldo + col0;
+          const __nv_bfloat16* rs =
+              ep.residual
+                  ? reinterpret_cast<const __nv_bfloat16*>(ep.residual) + g_row * ep.ldo + col0
+                  : nullptr;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (col0 + i >= N) break;
+            if (rs) {
+              const uint4 y = *reinterpret_cast<const uint4*>(rs + i);
+              const __nv_bfloat162* yb = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(yb[j]);
+                v[i + 2 * j] += f.x;
+                v[i + 2 * j + 1] += f.y;
+              }
+            }
+            uint4 pk;
+            pk.x = pack_bf16x2(v[i], v[i + 1]);
+            pk.y = pack_bf16x2(v[i + 2], v[i + 3]);
+            pk.z = pack_bf16x2(v[i + 4], v[i + 5]);
+            pk.w = pack_bf16x2(v[i + 6], v[i + 7]);
+            *reinterpret_cast<uint4*>(o + i) = pk;
+          }
         }
       }
+      // this thread's TMEM reads of the buffer are complete: hand it back to the MMA warp
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[ab]);
     }
   }
 
@@ -234,7 +272,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_d, BN);
+    tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 

@@ -116,10 +116,35 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
           }
         }
       }
-      for (int j = 0; j < cnt; ++j) {
-        const int64_t e = sg.shard_off + i + j;
-        if (i + j >= sg.q) break;
-        float g = acc[j] * scale;  // padding stays exactly zero: acc is 0 there
+      if (vec) {
+        // q % 4 == 0: the four elements are inside the shard; 16-byte accesses throughout
+        const int64_t e = sg.shard_off + i;
+        float4 g = make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
+        if (accumulate) {
+          const float4 o = *reinterpret_cast<const float4*>(gshard + e);
+          g.x += o.x; g.y += o.y; g.z += o.z; g.w += o.w;
+        }
+        *reinterpret_cast<float4*>(gshard + e) = g;   // padding stays exactly zero: acc is 0 there
+        if (ADAMW) {
+          float4 pv = *reinterpret_cast<const float4*>(p + e);
+          float4 mv = *reinterpret_cast<const float4*>(m + e);
+          float4 vv = *reinterpret_cast<const float4*>(v + e);
+          float* pp = &pv.x; float* mp = &mv.x; float* vp = &vv.x; const float* gp = &g.x;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float gr = gp[j] * a.grad_scale;
+            pp[j] *= 1.f - a.lr * a.weight_decay;
+            mp[j] = a.beta1 * mp[j] + (1.f - a.beta1) * gr;
+            vp[j] = a.beta2 * vp[j] + (1.f - a.beta2) * gr * gr;
+            pp[j] -= step_size * mp[j] / (sqrtf(vp[j]) * inv_bc2_sqrt + a.eps);
+          }
+          *reinterpret_cast<float4*>(p + e) = pv;   // padding has p = g = m = v = 0 and stays 0
+          *reinterpret_cast<float4*>(m + e) = mv;
+          *reinterpret_cast<float4*>(v + e) = vv;
+        }
+      } else {
+        const int64_t e = sg.shard_off + i;
+        float g = acc[0] * scale;
         if (accumulate) g += gshard[e];
         gshard[e] = g;
         if (ADAMW) {
@@ -128,7 +153,6 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
           const float mj = a.beta1 * m[e] + (1.f - a.beta1) * gr;
           const float vj = a.beta2 * v[e] + (1.f - a.beta2) * gr * gr;
           pj -= step_size * mj / (sqrtf(vj) * inv_bc2_sqrt + a.eps);
-          // padding elements have p = g = m = v = 0 and stay 0
           p[e] = pj;
           m[e] = mj;
           v[e] = vj;

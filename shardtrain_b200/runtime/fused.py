@@ -172,6 +172,7 @@ class FusedExecutor:
         self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
         self._rope_cache = {}
         self._scratch = {}
+        self.token_grad = torch.zeros(1, dtype=torch.float32, device=runtime.device)
 
     # ------------------------------------------------------------------ allocation
     def allocate(self):
@@ -339,7 +340,7 @@ class FusedEmbeddingFn(torch.autograd.Function):
                                      ids.reshape(-1).contiguous(), dw, -1 if pad is None else pad)
         # a tied weight receives its gradient view from the head node; returning it twice would
         # make autograd add the two (identical) views
-        return (None if unit.tied else dw), None, None, None
+        return (None if unit.tied else ex.token_grad), None, None, None
 
 
 class FusedNormFn(torch.autograd.Function):
@@ -348,6 +349,7 @@ class FusedNormFn(torch.autograd.Function):
         ctx.ex, ctx.unit = ex, unit
         unit.annotate("FWD")
         hidden = x.shape[-1]
+        weight = unit.lease.weights[unit.handles[0].spec.param_id]   # `weight` is only the edge token
         x2 = x.reshape(-1, hidden).contiguous()
         y = torch.empty(x2.shape, dtype=torch.bfloat16, device=x.device)
         inv = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
@@ -370,11 +372,11 @@ class FusedNormFn(torch.autograd.Function):
         side = ex.__dict__.pop("_head_dx", None)   # FP32 gradient handed over by the head node
         dy = side if side is not None else grad.reshape(x2.shape).float().contiguous()
         dx = torch.empty_like(x2)
-        partial = ex.scratch("norm_partial", (148, x2.shape[1]), torch.float32)
+        partial = ex.scratch("norm_partial", (592, x2.shape[1]), torch.float32)
         ex.ops.rmsnorm_bwd(dy, x2, weight, inv, None, dx, partial)
         dw = plan.grad_view(slot.local, name)
         ex.ops.colsum_f32(partial, dw, False)
-        return dx.view(ctx.shape), dw, None, None
+        return dx.view(ctx.shape), ex.token_grad, None, None
 
 
 class FusedHeadLossFn(torch.autograd.Function):
@@ -389,6 +391,7 @@ class FusedHeadLossFn(torch.autograd.Function):
         unit.annotate("FWD")
         ctx.ex, ctx.unit, ctx.name = ex, unit, name
         h = hidden.shape[-1]
+        weight = unit.lease.weights[name]   # the `weight` argument is only the autograd edge token
         hidden2 = hidden.reshape(-1, h)
         rows, vocab = hidden2.shape[0], weight.shape[0]
         target = shifted_labels(rt, labels).reshape(-1).contiguous()
@@ -425,7 +428,7 @@ class FusedHeadLossFn(torch.autograd.Function):
         ops.gemm(logits, weight, dx, False, True, None, None, False, 1.0, 0)
         ex._head_dx = dx
         placeholder = torch.empty(ctx.hidden_shape, dtype=torch.bfloat16, device=hidden2.device)
-        return placeholder, dw, None, None, None, None
+        return placeholder, ex.token_grad, None, None, None, None
 
 
 class FusedLayerFn(torch.autograd.Function):
@@ -527,7 +530,7 @@ class FusedLayerFn(torch.autograd.Function):
         d_h2 = ex.scratch("d_normed", (M, H), f32)
         ops.gemm(d_gu, w_gu, d_h2, False, True, None, None, False, 1.0, 0)
         d_mid = ex.scratch("d_mid", (M, H), f32)
-        partial = ex.scratch("norm_partial", (148, H), f32)
+        partial = ex.scratch("norm_partial", (592, H), f32)
         ops.rmsnorm_bwd(d_h2, x_mid, ln2, inv2, d_out, d_mid, partial)
         ops.colsum_f32(partial, plan.grad_view(g, names["ln2"]), False)
 
@@ -550,5 +553,4 @@ class FusedLayerFn(torch.autograd.Function):
         dx = torch.empty((M, H), dtype=f32, device=dout.device)
         ops.rmsnorm_bwd(d_h1, x2, ln1, inv1, d_mid, dx, partial)
         ops.colsum_f32(partial, plan.grad_view(g, names["ln1"]), False)
-        grads = [plan.grad_view(g, n) for n in plan.names]
-        return (dx.view(B, S, H), None, None, None, None, None, *grads)
+        return (dx.view(B, S, H), None, None, None, None, None, *([ex.token_grad] * len(plan.names)))

@@ -247,7 +247,7 @@ class PeerMaterializer:
         self.degree, self.rank, self.backend = _group_shape(group)
         self.plans: dict[int, object] = {}
         self.ops = None
-        self._grad_ring = None
+        self._tokens = None
 
     def bind(self, ops, arenas):
         """`arenas`: object with param/grad/exp_avg/exp_avg_sq flat tensors and peer pointers."""
@@ -300,19 +300,21 @@ class PeerMaterializer:
         lease.copy_out_ready_event = torch.cuda.Event()
         lease.copy_out_ready_event.record(torch.cuda.current_stream(self.comm.device))
         self.comm.event("copy_out_ready", unit_id=unit.unit_id)
-        return tuple(lease.weights[h.spec.param_id] for h in unit.handles)
+        # The autograd edges of this executor carry one-element FP32 tokens, not the bf16
+        # weights: autograd would cast an FP32 weight gradient to the dtype of a bf16 edge.  The
+        # kernels read the weights from the lease and write gradients into the unit's slot.
+        if self._tokens is None or self._tokens.numel() < len(unit.handles):
+            self._tokens = torch.zeros(max(64, len(unit.handles)), device=self.comm.device)
+        return tuple(self._tokens[i:i + 1] for i in range(len(unit.handles)))
 
     def reduce(self, unit, grads):
-        """`grads` are views into the unit's full-gradient buffer written by the fused backward."""
+        """The fused backward already wrote every full gradient into the unit's slot; `grads`
+        are the token gradients that made autograd schedule this reduction."""
         runtime = unit.runtime
         plan = self.plans[unit.unit_id]
         if len(grads) != len(unit.handles) or any(g is None for g in grads):
             raise RuntimeError(f"Missing full parameter gradient U{unit.unit_id}")
-        slot = runtime.fused.grad_slot(unit)          # the peer-visible buffer the views alias
-        for handle, grad in zip(unit.handles, grads):
-            expect = slot.local.data_ptr() + 4 * plan.grad_offsets[handle.spec.param_id]
-            if grad.data_ptr() != expect:
-                slot.local.narrow(0, plan.grad_offsets[handle.spec.param_id], handle.spec.numel).copy_(grad.reshape(-1))
+        slot = runtime.fused.grad_slot(unit)          # peer-visible buffer holding the gradients
         first = runtime.first_commit(unit)
         fuse_adamw = runtime.fused_optimizer_armed(unit)
         arenas = self.arenas
