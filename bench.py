@@ -91,11 +91,10 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
-def qwen15b_config(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
-    from shardtrain_b200.config import config_from_dict
-
+def qwen15b_dict(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
+    """The benchmark configuration as a plain mapping (shared by both arms)."""
     layers = args.layers or 28
-    return config_from_dict({
+    return ({
         "model": dict(model_type="qwen2", vocab_size=151936, layers=layers, hidden_size=1536,
                       num_heads=12, num_key_value_heads=2, mlp_hidden_size=8960, seq_len=512,
                       rope_theta=1000000.0, tie_word_embeddings=True, rms_norm_eps=1e-6),
@@ -112,12 +111,20 @@ def qwen15b_config(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
     })
 
 
-def resolve_strategy(args):
-    from shardtrain_b200.config import parse_strategy
+def qwen15b_config(args, fsdp, tp, sp):
+    from shardtrain_b200.config import config_from_dict
 
-    if args.strategy:
-        return parse_strategy(args.strategy)
-    return args.gpus, 1, False
+    return config_from_dict(qwen15b_dict(args, fsdp, tp, sp))
+
+
+def resolve_strategy(args):
+    """(fsdp, tp, sp) from `--strategy F4T2/SP`; default is FSDP over all GPUs."""
+    if not args.strategy:
+        return args.gpus, 1, False
+    text = args.strategy.upper()
+    sp = text.endswith("/SP")
+    f, t = text[:-3 if sp else None][1:].split("T")
+    return int(f), int(t), sp
 
 
 def run_ours(args):

@@ -457,6 +457,61 @@ class CommunicationCoordinator:
             ticket.ready_event.record(here)
 
     @_locked
+    def issue_kernel(self, pg_id, kind, group, launch, *, channel, after_streams=(),
+                     after_events=(), numel=0, leases=(), group_role=None):
+        """Submit a collective implemented by this package's own kernels.
+
+        `launch()` enqueues the kernels; it runs with `channel`'s stream current, after that
+        stream has been made to wait for the work already queued on each stream named in
+        `after_streams` and for each event in `after_events`.  The ticket's `ready_event` is
+        recorded behind the kernels.  Ordering between GPUs is carried by flags in peer memory,
+        so neither policy adds edges here; the per-communicator sequence is still recorded.
+        """
+        _, members, _ = self._describe_group(group)
+        seq = self.sequence.get(pg_id, 0)
+        if self.expected_sequence is not None:
+            position = self.next_op_id
+            if position >= len(self.expected_sequence) or tuple(self.expected_sequence[position]) != (pg_id, kind):
+                raise RuntimeError(f"ProcessGroup order divergence at {position}: {pg_id}/{kind}")
+        self.sequence[pg_id] = seq + 1
+        ticket = CommunicationTicket(self.next_op_id, pg_id, seq, self.unit_id, self.phase, kind)
+        self.next_op_id += 1
+        stream = self.streams[channel]
+        ticket.group_members, ticket.issue_stream = members, channel
+        ticket.generation, ticket.group_role = self.generation, group_role or self.group_role
+        ticket.execution_mode, ticket.api_async_op = "peer_kernel", False
+        ticket.logical_cuda_stream = ticket.collective_cuda_stream = stream.cuda_stream
+        ticket.output_leases = tuple(leases)
+        self.tickets.append(ticket)
+        self._track(ticket)
+        try:
+            if self.diagnostics_enabled:
+                self.event("collective_issue", op_id=ticket.op_id, pg_id=pg_id, pg_seq=seq, kind=kind,
+                           numel=numel, dtype="torch.float32", op_kind=kind, pg_local_seq=seq,
+                           group_members=list(members), group_role=ticket.group_role,
+                           issue_stream=channel, backend="peer_kernel",
+                           output_buffer_ids=[l.buffer_id for l in leases])
+            for name in after_streams:
+                produced = torch.cuda.Event()
+                produced.record(self.streams[name])
+                stream.wait_event(produced)
+                if self.diagnostics_enabled:
+                    self.dependency("DATA_DEP", consumer_ticket=ticket.op_id,
+                                    consumer="collective_input", wait_stream=channel, producer_stream=name)
+            for event in after_events:
+                stream.wait_event(event)
+            with torch.cuda.stream(stream):
+                launch()
+            if self.diagnostics_enabled:
+                self.event("work_issued", op_id=ticket.op_id, work_issued=False, issue_stream=channel)
+            ticket.ready_event = torch.cuda.Event()
+            ticket.ready_event.record(stream)
+            return ticket
+        except BaseException:
+            self._fail(ticket)
+            raise
+
+    @_locked
     def consume(self, ticket, *, dependency_type="DATA_DEP", consumer_ticket=None,
                 consumer="collective_output"):
         """Make the calling stream (or the CPU) wait for the collective's completion."""

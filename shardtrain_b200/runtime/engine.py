@@ -76,6 +76,9 @@ class UnitState:
         if comm.streams:
             self.lease.fullparam_last_consumer_event = torch.cuda.Event()
             self.lease.fullparam_last_consumer_event.record(torch.cuda.current_stream(self.runtime.device))
+        notify = getattr(self.runtime.materializer, "released", None)
+        if notify is not None:
+            notify(self, self.lease.fullparam_last_consumer_event)
         for lease in self.lease.full_param_storages.values():
             comm.retire(lease)
         self.lease.full_param_storages.clear()

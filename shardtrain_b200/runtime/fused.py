@@ -53,6 +53,14 @@ class UnitPlan:
     shard_numel: int = 0
     gather_table: torch.Tensor | None = None
     reduce_table: torch.Tensor | None = None
+    # persistent materialisation state (allocated once at registration)
+    full_bf16: torch.Tensor | None = None
+    full_fp32: torch.Tensor | None = None
+    weights: dict = field(default_factory=dict)      # name -> view of the buffers above
+    tokens: tuple = ()                                # one-element FP32 autograd edge tokens
+    last_reader: object = None                        # event after the buffers' last consumer
+    fwd: dict = field(default_factory=dict)           # fused operand views (built on first use)
+    gslots: dict = field(default_factory=dict)        # id(slot) -> fused gradient views
 
     def views(self, full_bf16, full_fp32):
         out = {}
@@ -198,9 +206,17 @@ class FusedExecutor:
         self.param, self.grad = rt.param_arena, rt.grad_arena
         self.param_peer_ptrs = list(self._param_buffer.ptrs)
         largest = 0
+        token_pool = torch.zeros(64 * max(1, len(rt.units)), dtype=torch.float32, device=rt.device)
         for unit in rt.units:
-            mat.plans[unit.unit_id] = build_plan(unit)
-            largest = max(largest, mat.plans[unit.unit_id].grad_numel)
+            plan = mat.plans[unit.unit_id] = build_plan(unit)
+            largest = max(largest, plan.grad_numel)
+            plan.full_bf16 = torch.empty(max(plan.bf16_numel, 8), dtype=torch.bfloat16, device=rt.device)
+            plan.full_fp32 = torch.empty(max(plan.fp32_numel, 4), dtype=torch.float32, device=rt.device)
+            plan.weights = plan.views(plan.full_bf16, plan.full_fp32)
+            base = 64 * unit.unit_id
+            if len(unit.handles) > 64:
+                raise ValueError("A unit may hold at most 64 parameters")
+            plan.tokens = tuple(token_pool[base + i: base + i + 1] for i in range(len(unit.handles)))
         self.ring = GradRing(self.peer, self.ops, _up(largest, 4), count=4)
         mat.bind(self.ops, self)
         ranges = rt.padding_ranges or [(0, 0)]
@@ -237,10 +253,48 @@ class FusedExecutor:
             raise RuntimeError(f"U{unit.unit_id} reduced without a gradient slot")
         return slot
 
-    def grad_slot_issued(self, unit, slot):
-        ticket = self.runtime.comm.tickets[-1]
+    def grad_slot_issued(self, unit, slot, ticket):
         self.ring.issued(slot, ticket.ready_event)
         unit.grad_slot = None
+
+    def layer_operands(self, plan, index):
+        """Fused operand views of a decoder layer's persistent buffers (built once)."""
+        if not plan.fwd:
+            p = f"model.layers.{index}."
+            wb, wf = plan.full_bf16, plan.full_fp32
+            H = self.cfg.hidden_size
+            W = (self.hq + 2 * self.hkv) * 128
+            inter = plan.shapes[p + "mlp.gate_proj.weight"][0]
+            plan.fwd = dict(
+                w_qkv=plan.span(wb, p + "self_attn.q_proj.weight", p + "self_attn.v_proj.weight", H),
+                b_qkv=wf.narrow(0, plan.param_offsets[p + "self_attn.q_proj.bias"], W),
+                w_o=plan.span(wb, p + "self_attn.o_proj.weight", p + "self_attn.o_proj.weight", self.hq * 128),
+                w_gu=plan.span(wb, p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight", H),
+                w_down=plan.span(wb, p + "mlp.down_proj.weight", p + "mlp.down_proj.weight", inter),
+                ln1=wf.narrow(0, plan.param_offsets[p + "input_layernorm.weight"], H),
+                ln2=wf.narrow(0, plan.param_offsets[p + "post_attention_layernorm.weight"], H),
+                inter=inter, width=W,
+            )
+        return plan.fwd
+
+    def layer_gradients(self, plan, slot, index):
+        """Fused gradient views of a decoder layer inside one ring slot (built once per slot)."""
+        views = plan.gslots.get(id(slot))
+        if views is None:
+            p = f"model.layers.{index}."
+            g = slot.local
+            H = self.cfg.hidden_size
+            W = (self.hq + 2 * self.hkv) * 128
+            views = plan.gslots[id(slot)] = dict(
+                down=plan.grad_view(g, p + "mlp.down_proj.weight"),
+                gate_up=plan.grad_span(g, p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight", H),
+                ln2=plan.grad_view(g, p + "post_attention_layernorm.weight"),
+                o=plan.grad_view(g, p + "self_attn.o_proj.weight"),
+                bias=g.narrow(0, plan.grad_offsets[p + "self_attn.q_proj.bias"], W),
+                qkv=plan.grad_span(g, p + "self_attn.q_proj.weight", p + "self_attn.v_proj.weight", H),
+                ln1=plan.grad_view(g, p + "input_layernorm.weight"),
+            )
+        return views
 
     def launch_grad_check(self):
         self.ops.grad_check(self.grad, self._pad_ranges, self._flags)
@@ -439,22 +493,17 @@ class FusedLayerFn(torch.autograd.Function):
         ops, cfg = ex.ops, ex.cfg
         plan = ex.runtime.materializer.plans[unit.unit_id]
         unit.annotate("FWD")
-        wb, wf = unit.lease.extras["full_bf16"], unit.lease.extras["full_fp32"]
-        p = f"model.layers.{index}."
+        if unit.lease is None or unit.state != "FWD_ACTIVE":
+            raise RuntimeError("Layer forward without a current materialization")
+        w = ex.layer_operands(plan, index)
         B, S, H = x.shape
         M, D, hq, hkv = B * S, 128, ex.hq, ex.hkv
-        W = (hq + 2 * hkv) * D
-        inter = plan.shapes[p + "mlp.gate_proj.weight"][0]
+        W, inter = w["width"], w["inter"]
         cos, sin, positions, _ = tables
         dev = x.device
         x2 = x.reshape(M, H).contiguous()
-        w_qkv = plan.span(wb, p + "self_attn.q_proj.weight", p + "self_attn.v_proj.weight", H)
-        b_qkv = wf.narrow(0, plan.param_offsets[p + "self_attn.q_proj.bias"], W)
-        w_o = plan.span(wb, p + "self_attn.o_proj.weight", p + "self_attn.o_proj.weight", hq * D)
-        w_gu = plan.span(wb, p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight", H)
-        w_down = plan.span(wb, p + "mlp.down_proj.weight", p + "mlp.down_proj.weight", inter)
-        ln1 = wf.narrow(0, plan.param_offsets[p + "input_layernorm.weight"], H)
-        ln2 = wf.narrow(0, plan.param_offsets[p + "post_attention_layernorm.weight"], H)
+        w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2 = (
+            w["w_qkv"], w["b_qkv"], w["w_o"], w["w_gu"], w["w_down"], w["ln1"], w["ln2"])
         bf, f32 = torch.bfloat16, torch.float32
 
         h1 = torch.empty((M, H), dtype=bf, device=dev)
@@ -492,27 +541,16 @@ class FusedLayerFn(torch.autograd.Function):
         plan = ex.runtime.materializer.plans[unit.unit_id]
         unit.annotate("BWD")
         unit.weight(plan.names[0])  # state / generation check of the backward materialisation
-        wb, wf = unit.lease.extras["full_bf16"], unit.lease.extras["full_fp32"]
         x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu = ctx.saved_tensors
         B, S, H, inter = ctx.dims
         M, D, hq, hkv = B * S, 128, ex.hq, ex.hkv
-        W = (hq + 2 * hkv) * D
         cos, sin, positions, _ = ctx.tables
-        p = f"model.layers.{index}."
         bf, f32 = torch.bfloat16, torch.float32
-        names = {k: p + v for k, v in dict(
-            q="self_attn.q_proj.weight", v="self_attn.v_proj.weight", o="self_attn.o_proj.weight",
-            gate="mlp.gate_proj.weight", up="mlp.up_proj.weight", down="mlp.down_proj.weight",
-            qb="self_attn.q_proj.bias", vb="self_attn.v_proj.bias",
-            ln1="input_layernorm.weight", ln2="post_attention_layernorm.weight").items()}
-        w_qkv = plan.span(wb, names["q"], names["v"], H)
-        w_o = plan.span(wb, names["o"], names["o"], hq * D)
-        w_gu = plan.span(wb, names["gate"], names["up"], H)
-        w_down = plan.span(wb, names["down"], names["down"], inter)
-        ln1 = wf.narrow(0, plan.param_offsets[names["ln1"]], H)
-        ln2 = wf.narrow(0, plan.param_offsets[names["ln2"]], H)
+        w = ex.layer_operands(plan, index)
+        W = w["width"]
+        w_qkv, w_o, w_gu, w_down, ln1, ln2 = w["w_qkv"], w["w_o"], w["w_gu"], w["w_down"], w["ln1"], w["ln2"]
         slot = ex.acquire_grad_slot(unit)
-        g = slot.local
+        gv = ex.layer_gradients(plan, slot, index)
         unit.prefetch_after_input(unit.backward_prefetch_handle, "BWD")
 
         d_out = dout.reshape(M, H).contiguous()
@@ -520,23 +558,22 @@ class FusedLayerFn(torch.autograd.Function):
         ops.cast_bf16(d_out, d_out_b)
         hm = ex.scratch("mlp_hidden", (M, inter), bf)
         ops.swiglu_fwd(gu, hm)                                                    # recompute
-        ops.gemm(d_out_b, hm, plan.grad_view(g, names["down"]), True, True, None, None, False, 1.0, 0)
+        ops.gemm(d_out_b, hm, gv["down"], True, True, None, None, False, 1.0, 0)
         d_hm = ex.scratch("d_mlp_hidden", (M, inter), bf)
         ops.gemm(d_out_b, w_down, d_hm, False, True, None, None, False, 1.0, 0)
         d_gu = ex.scratch("d_gate_up", (M, 2 * inter), bf)
         ops.swiglu_bwd(d_hm, gu, d_gu)
-        ops.gemm(d_gu, h2, plan.grad_span(g, names["gate"], names["up"], H), True, True,
-                 None, None, False, 1.0, 0)
+        ops.gemm(d_gu, h2, gv["gate_up"], True, True, None, None, False, 1.0, 0)
         d_h2 = ex.scratch("d_normed", (M, H), f32)
         ops.gemm(d_gu, w_gu, d_h2, False, True, None, None, False, 1.0, 0)
         d_mid = ex.scratch("d_mid", (M, H), f32)
         partial = ex.scratch("norm_partial", (592, H), f32)
         ops.rmsnorm_bwd(d_h2, x_mid, ln2, inv2, d_out, d_mid, partial)
-        ops.colsum_f32(partial, plan.grad_view(g, names["ln2"]), False)
+        ops.colsum_f32(partial, gv["ln2"], False)
 
         d_mid_b = ex.scratch("d_res_bf16", (M, H), bf)
         ops.cast_bf16(d_mid, d_mid_b)
-        ops.gemm(d_mid_b, attn, plan.grad_view(g, names["o"]), True, True, None, None, False, 1.0, 0)
+        ops.gemm(d_mid_b, attn, gv["o"], True, True, None, None, False, 1.0, 0)
         d_attn = ex.scratch("d_attn", (M, hq * D), bf)
         ops.gemm(d_mid_b, w_o, d_attn, False, True, None, None, False, 1.0, 0)
         d_qkv = ex.scratch("d_qkv", (M, W), bf)
@@ -544,13 +581,11 @@ class FusedLayerFn(torch.autograd.Function):
         ops.attention_bwd(qkv, attn, d_attn, lse, delta, d_qkv, delta, ctx.mask, B, S, hq, hkv,
                           1.0 / math.sqrt(D))
         ops.rope(d_qkv, cos, sin, positions, S, hq, hkv, D, True)
-        d_bias = g.narrow(0, plan.grad_offsets[names["qb"]], W)
-        ops.colsum_bf16(d_qkv, d_bias, False, ex.scratch("bias_partial", (64, W), f32))
-        ops.gemm(d_qkv, h1, plan.grad_span(g, names["q"], names["v"], H), True, True,
-                 None, None, False, 1.0, 0)
+        ops.colsum_bf16(d_qkv, gv["bias"], False, ex.scratch("bias_partial", (64, W), f32))
+        ops.gemm(d_qkv, h1, gv["qkv"], True, True, None, None, False, 1.0, 0)
         d_h1 = ex.scratch("d_normed", (M, H), f32)
         ops.gemm(d_qkv, w_qkv, d_h1, False, True, None, None, False, 1.0, 0)
         dx = torch.empty((M, H), dtype=f32, device=dout.device)
         ops.rmsnorm_bwd(d_h1, x2, ln1, inv1, d_mid, dx, partial)
-        ops.colsum_f32(partial, plan.grad_view(g, names["ln1"]), False)
+        ops.colsum_f32(partial, gv["ln1"], False)
         return (dx.view(B, S, H), None, None, None, None, None, *([ex.token_grad] * len(plan.names)))

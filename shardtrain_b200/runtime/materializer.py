@@ -235,9 +235,12 @@ class _null:
 class PeerMaterializer:
     """sm_100a materialiser: gather+cast and reduce-scatter(+AdamW) kernels over peer memory.
 
-    `plans[unit_id]` (built at registration by the fused executor) carries, per unit:
-    `gather_table` / `reduce_table` (int64 [n,5] segment tables), `bf16_numel`, `fp32_numel`,
-    `grad_numel`, and `views(lease_buffers)` producing the per-parameter tensors.
+    `plans[unit_id]` (built at registration by the fused executor) carries, per unit, the segment
+    tables of the two kernels, the unit's persistent compute-dtype buffers with every parameter
+    view precomputed, and the one-element FP32 tokens used as autograd edges.  The buffers are
+    allocated once (180 GB of HBM makes a per-unit bf16 copy cheap); "resharding" a unit ends the
+    *validity* of its buffer -- lease, generation and step checks are unchanged -- so the next use
+    must gather again, but no allocator traffic or view construction happens inside a step.
     """
 
     kind = "peer"
@@ -247,7 +250,6 @@ class PeerMaterializer:
         self.degree, self.rank, self.backend = _group_shape(group)
         self.plans: dict[int, object] = {}
         self.ops = None
-        self._tokens = None
 
     def bind(self, ops, arenas):
         """`arenas`: object with param/grad/exp_avg/exp_avg_sq flat tensors and peer pointers."""
@@ -257,55 +259,51 @@ class PeerMaterializer:
     def issue(self, unit, phase) -> MaterializationLease:
         runtime = unit.runtime
         plan = self.plans[unit.unit_id]
-        with self.comm.stream_context("fsdp_ag"):
-            if self.comm.streams:
-                runtime.wait_parameter_shards_ready()
-            full_bf16 = torch.empty(max(plan.bf16_numel, 8), dtype=torch.bfloat16, device=self.comm.device)
-            full_fp32 = torch.empty(max(plan.fp32_numel, 4), dtype=torch.float32, device=self.comm.device)
-            lease = MaterializationLease(unit.unit_id, runtime.step_id, phase, unit.generation,
-                                         self.comm.buffer(full_bf16, "fsdp_ag"))
-            lease.extras["full_bf16"], lease.extras["full_fp32"] = full_bf16, full_fp32
-            lease.extras["fp32_lease"] = self.comm.buffer(full_fp32, "fsdp_ag_fp32")
-            anchor = unit.handles[0].local_shard
-            ptrs = self.arenas.param_peer_ptrs
+        comm = self.comm
+        lease = MaterializationLease(unit.unit_id, runtime.step_id, phase, unit.generation)
+        lease.ag_storage = comm.buffer(plan.full_bf16, "fsdp_ag")
+        lease.extras["full_bf16"], lease.extras["full_fp32"] = plan.full_bf16, plan.full_fp32
+        ptrs = self.arenas.param_peer_ptrs
 
-            def operation(async_):
-                self.ops.gather_params(ptrs, plan.gather_table, full_bf16, full_fp32)
-                return None
+        def launch():
+            # the shards depend on the optimizer's writes (and on every peer having finished
+            # its own), never on activations queued on the compute stream
+            runtime.wait_parameter_shards_ready()
+            self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32)
 
-            lease.ag_ticket = self.comm.issue(
-                "fsdp", "fsdp_ag_cast", self.group, anchor, full_bf16, operation,
-                channel="fsdp_ag", asynchronous=True, group_role="parameter_materialization",
-                extra_outputs=(full_fp32,), peer_kernel=True,
-            )
+        # a buffer may be re-gathered only after its last reader on the compute stream
+        after = (plan.last_reader,) if plan.last_reader is not None else ()
+        lease.ag_ticket = comm.issue_kernel(
+            "fsdp", "fsdp_ag_cast", self.group, launch, channel="fsdp_ag", after_events=after,
+            numel=plan.shard_numel, leases=(lease.ag_storage,),
+            group_role="parameter_materialization")
         return lease
 
     def finish(self, unit):
         lease = unit.lease
         if lease.weights:
             raise RuntimeError(f"Duplicate copy-out U{unit.unit_id}")
-        self.comm.consume(lease.ag_ticket, consumer=f"copy_out/U{unit.unit_id}")
+        comm = self.comm
+        comm.consume(lease.ag_ticket, consumer=f"copy_out/U{unit.unit_id}")
         plan = self.plans[unit.unit_id]
-        if self.comm.diagnostics_enabled:
-            self.comm.event("copy_out_start", unit_id=unit.unit_id,
-                            producer_ticket=lease.ag_ticket.op_id,
-                            buffer_id=lease.ag_storage.buffer_id,
-                            issue_stream=self.comm.stream_name())
-        # the gather kernel already landed every parameter in its final place: the "copy-out"
-        # is taking views
-        lease.weights = plan.views(lease.extras["full_bf16"], lease.extras["full_fp32"])
+        if comm.diagnostics_enabled:
+            comm.event("copy_out_start", unit_id=unit.unit_id, producer_ticket=lease.ag_ticket.op_id,
+                       buffer_id=lease.ag_storage.buffer_id, issue_stream=comm.stream_name())
+        # the gather kernel already landed every parameter in its final place and dtype: the
+        # "copy-out" is handing out the precomputed views
+        lease.weights = plan.weights
         lease.full_param_storages["bf16"] = lease.ag_storage
-        lease.full_param_storages["fp32"] = lease.extras.pop("fp32_lease")
         lease.ag_storage = None
-        lease.copy_out_ready_event = torch.cuda.Event()
-        lease.copy_out_ready_event.record(torch.cuda.current_stream(self.comm.device))
-        self.comm.event("copy_out_ready", unit_id=unit.unit_id)
+        lease.copy_out_ready_event = lease.ag_ticket.ready_event
+        comm.event("copy_out_ready", unit_id=unit.unit_id)
         # The autograd edges of this executor carry one-element FP32 tokens, not the bf16
         # weights: autograd would cast an FP32 weight gradient to the dtype of a bf16 edge.  The
         # kernels read the weights from the lease and write gradients into the unit's slot.
-        if self._tokens is None or self._tokens.numel() < len(unit.handles):
-            self._tokens = torch.zeros(max(64, len(unit.handles)), device=self.comm.device)
-        return tuple(self._tokens[i:i + 1] for i in range(len(unit.handles)))
+        return plan.tokens
+
+    def released(self, unit, event):
+        """Called when the unit's full parameters are given up; `event` marks the last reader."""
+        self.plans[unit.unit_id].last_reader = event
 
     def reduce(self, unit, grads):
         """The fused backward already wrote every full gradient into the unit's slot; `grads`
@@ -318,9 +316,8 @@ class PeerMaterializer:
         first = runtime.first_commit(unit)
         fuse_adamw = runtime.fused_optimizer_armed(unit)
         arenas = self.arenas
-        anchor = slot.local
 
-        def operation(async_):
+        def launch():
             if self.degree > 1:
                 self.peer.barrier("fsdp_rs")
             if fuse_adamw:
@@ -331,19 +328,19 @@ class PeerMaterializer:
             else:
                 self.ops.reduce_scatter(slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad,
                                         1.0 / self.degree, not first)
-            return None
 
-        channel = "fsdp_rs"
-        ticket = self.comm.issue(
+        comm = self.comm
+        ticket = comm.issue_kernel(
             "fsdp_grad", "fsdp_rs_accumulate_adamw" if fuse_adamw else "fsdp_rs_accumulate",
-            self.group, anchor, arenas.grad, operation, channel=channel,
-            asynchronous=runtime.async_grad_rs, group_role="main_gradient_bucket", peer_kernel=True,
-        )
-        if self.comm.diagnostics_enabled:
-            self.comm.event("gradient_bucket_issued", bucket="main",
-                            parameters=[h.spec.param_id for h in unit.handles],
-                            producer_ticket=ticket.op_id, output_numel=plan.shard_numel)
-        runtime.fused.grad_slot_issued(unit, slot)
+            self.group, launch, channel="fsdp_rs", after_streams=("compute",),
+            numel=plan.grad_numel, group_role="main_gradient_bucket")
+        if not runtime.async_grad_rs:
+            comm.consume(ticket, consumer="main_gradient_bucket")
+        if comm.diagnostics_enabled:
+            comm.event("gradient_bucket_issued", bucket="main",
+                       parameters=[h.spec.param_id for h in unit.handles],
+                       producer_ticket=ticket.op_id, output_numel=plan.shard_numel)
+        runtime.fused.grad_slot_issued(unit, slot, ticket)
         if getattr(runtime, "gradient_dispatch_prefetch", False):
             runtime.dispatch_backward_prefetch(unit)
         for handle in unit.handles:

@@ -29,6 +29,10 @@ def main():
     ap.add_argument("--tied", type=int, default=1)
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--mismatch", type=int, default=0)
+    ap.add_argument("--shape", default="tiny", choices=["tiny", "d128"])
+    ap.add_argument("--dtype", default="fp32")
+    ap.add_argument("--optimizer", default="adamw")
+    ap.add_argument("--backend", default="auto")
     a = ap.parse_args()
     worker = WorkerEnvironment.read()
     out = Path(a.out)
@@ -36,10 +40,19 @@ def main():
     logger = logging.getLogger(f"w{worker.rank}")
     backend = "gloo" if a.device == "cpu" else "nccl"
     par = ParallelConfig(a.fsdp, a.tp, bool(a.sp), a.device, backend)
+    if a.device == "cuda" and a.policy == "stream_ordered" and worker.world_size > 1:
+        from shardtrain_b200.distributed.nccl_ordering import prepare_nccl_launch_order
+        prepare_nccl_launch_order()   # what WorkerSession does for the NCCL path
     with DistributedContext(par, worker, 60, logger) as ctx:
-        cfg = Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128,
-                               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
-                               tie_word_embeddings=bool(a.tied))
+        if a.shape == "d128":   # head_dim 128: the shape class of the sm_100a kernels
+            cfg = Qwen2ModelConfig(vocab_size=2048, hidden_size=256, intermediate_size=512,
+                                   num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+                                   tie_word_embeddings=bool(a.tied))
+        else:
+            cfg = Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128,
+                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                   tie_word_embeddings=bool(a.tied))
+        vocab, seq = cfg.vocab_size, (256 if a.shape == "d128" else 64)
         torch.manual_seed(7 + (worker.rank if a.mismatch else 0))
         dense = Qwen2CausalLM(cfg)
         import copy
@@ -47,28 +60,33 @@ def main():
         fp, bp, ar = (c == "1" for c in a.flags)
         rt = ShardedRuntime(device=ctx.device, reshard_after_forward=bool(a.reshard),
                             forward_prefetch=fp, backward_prefetch=bp, async_grad_rs=ar,
-                            communication_policy=a.policy, directory=out)
+                            communication_policy=a.policy, directory=out,
+                            communication_backend=a.backend)
         rt.register(model, ctx, sp=bool(a.sp))
-        tr = QwenTrainer(model, rt, lr=1e-3, optimizer="adamw", accumulation_steps=a.accum)
-        opt = torch.optim.AdamW(dense.parameters(), lr=1e-3)
+        lr = 1e-3 if a.optimizer == "adamw" else 0.05
+        tr = QwenTrainer(model, rt, lr=lr, optimizer=a.optimizer, accumulation_steps=a.accum,
+                         dtype=a.dtype)
+        dense = dense.to(ctx.device)
+        opt = (torch.optim.AdamW if a.optimizer == "adamw" else torch.optim.SGD)(dense.parameters(), lr=lr)
         batch = 2 * a.accum
         rows = []
         for step in range(a.steps):
             gen = torch.Generator().manual_seed(100 + step)
             # every FSDP coordinate trains on its own batch; TP ranks of a replica share it
-            all_ids = torch.randint(0, 1024, (a.fsdp, batch, 64), generator=gen)
+            all_ids = torch.randint(0, vocab, (a.fsdp, batch, seq), generator=gen)
             ids = all_ids[ctx.coordinate.fsdp].to(ctx.device)
             res = tr.train_step(ids)
             opt.zero_grad()
-            flat = all_ids.reshape(-1, 64)
-            ref = dense(flat, labels=flat)
+            flat = all_ids.reshape(-1, seq).to(ctx.device)
+            with torch.autocast(ctx.device.type, dtype=torch.bfloat16, enabled=a.dtype == "bf16"):
+                ref = dense(flat, labels=flat)
             ref.loss.backward()
             opt.step()
             rows.append(dict(step=step, loss=res.loss, ref=ref.loss.item(), valid=res.valid_tokens))
         full = rt.reconstruct_tp_local()
         err, errs = 0.0, {}
         for name, p in dense.named_parameters():
-            part = rt.qwen_partitions[name].local_slice(p.detach())
+            part = rt.qwen_partitions[name].local_slice(p.detach()).cpu()
             e = (full[name].cpu() - part).abs().max().item()
             errs[name] = e
             err = max(err, e)
@@ -85,6 +103,10 @@ def main():
             live=len(rt.comm.live_buffers), names=[n for n, _ in model.named_parameters()][:4],
             units=len(rt.units), leaves=len(rt.registry), errs=errs)))
         rt.comm.flush_diagnostics()
+        if ctx.device.type == "cuda":
+            from shardtrain_b200 import ops
+            torch.cuda.synchronize()
+            ops.check_status("worker")
 
 
 if __name__ == "__main__":
