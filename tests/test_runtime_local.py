@@ -1,0 +1,175 @@
+"""Single-process (degree-1) runtime: every lifecycle rule is enforced without a process group."""
+import copy
+import itertools
+import weakref
+
+import pytest
+import torch
+
+from shardtrain_b200.config import ModelConfig
+from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+from shardtrain_b200.models.reference import build_reference_model, synthetic_batch
+from shardtrain_b200.runtime.engine import ShardedRuntime
+from shardtrain_b200.training.qwen2_trainer import QwenTrainer
+from shardtrain_b200.training.reference import dense_oracle
+from shardtrain_b200.training.sharded_trainer import ShardedTrainer
+
+TOY = ModelConfig(layers=3, hidden_size=32, num_heads=4, mlp_hidden_size=64, seq_len=8)
+
+
+def tiny_qwen(tied=True):
+    return Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                            num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=tied)
+
+
+@pytest.mark.parametrize("policy", ["conservative", "stream_ordered"])
+@pytest.mark.parametrize("flags", list(itertools.product([False, True], repeat=3)))
+def test_toy_matches_dense_for_every_switch_combination(flags, policy):
+    dense = build_reference_model(TOY, 3)
+    model = copy.deepcopy(dense)
+    fp, bp, ar = flags
+    rt = ShardedRuntime(device="cpu", reshard_after_forward=True, forward_prefetch=fp,
+                        backward_prefetch=bp, async_grad_rs=ar, communication_policy=policy)
+    rt.register(model)
+    trainer = ShardedTrainer(model, rt, 0.1)
+    ref = torch.optim.SGD(dense.parameters(), lr=0.1)
+    for step in range(3):
+        x = synthetic_batch(TOY, 4, step)
+        got = trainer.train_step(x, torch.zeros_like(x))
+        ref.zero_grad()
+        loss = dense(x).square().mean()
+        loss.backward()
+        ref.step()
+        assert got.loss == pytest.approx(loss.item(), rel=1e-6)
+    full = rt.reconstruct_tp_local()
+    for name, p in dense.named_parameters():
+        torch.testing.assert_close(full[name], p, atol=3e-6, rtol=3e-5)
+    per_step = rt.comm.events.count  # noqa: B018 - events exist
+    materialized = [e for e in rt.comm.events if e["event_type"] == "materialize_issue"]
+    assert len(materialized) == 3 * (TOY.layers + TOY.layers - 1)   # no BWD gather for the last unit
+    assert not rt.comm.live_buffers
+
+
+def test_toy_output_matches_functional_oracle():
+    dense = build_reference_model(TOY, 5)
+    params = {n: p.detach().clone() for n, p in dense.named_parameters()}
+    x = synthetic_batch(TOY, 2, 0)
+    torch.testing.assert_close(dense(x), dense_oracle(x, params, TOY)[-1], atol=2e-6, rtol=2e-5)
+
+
+def test_no_full_parameter_is_saved_for_backward():
+    dense = Qwen2CausalLM(tiny_qwen())
+    model = copy.deepcopy(dense)
+    rt = ShardedRuntime(device="cpu", reshard_after_forward=True)
+    rt.register(model)
+    rt.compute_dtype = torch.float32
+    weight_shapes = {h.spec.tp_local_shape for h in rt.registry.values() if len(h.spec.tp_local_shape) == 2}
+    full_storages, saved = set(), []
+    original = rt.comm.buffer
+
+    def tracking_buffer(tensor, owner):
+        if owner == "full_parameter":
+            full_storages.add(tensor.untyped_storage().data_ptr())
+        return original(tensor, owner)
+
+    rt.comm.buffer = tracking_buffer
+
+    def pack(t):
+        saved.append((tuple(t.shape), t.untyped_storage().data_ptr()))
+        return t
+
+    ids = torch.randint(0, 1024, (2, 16))
+    rt.begin_step(0)
+    rt.zero_grad()
+    with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+        out = model(ids, labels=ids)
+    assert full_storages and saved
+    # freed storages can be reused by later activations, so pointer identity is only meaningful
+    # for the full parameters that are still alive (retained units)
+    alive = {l.tensor.untyped_storage().data_ptr() for l in rt.comm.live_buffers.values()
+             if l.owner == "full_parameter"}
+    assert alive
+    assert not any(ptr in alive for _, ptr in saved)
+    assert not any(shape in weight_shapes for shape, _ in saved)
+    out.loss.backward()
+    rt.finalize_backward()
+    assert not rt.comm.live_buffers
+
+
+@pytest.mark.parametrize("tied", [True, False])
+@pytest.mark.parametrize("reshard", [True, False])
+def test_qwen_sgd_parity_and_state_layout(tied, reshard):
+    torch.manual_seed(0)
+    dense = Qwen2CausalLM(tiny_qwen(tied))
+    model = copy.deepcopy(dense)
+    rt = ShardedRuntime(device="cpu", reshard_after_forward=reshard, forward_prefetch=True,
+                        backward_prefetch=True)
+    rt.register(model)
+    trainer = QwenTrainer(model, rt, lr=0.05, optimizer="sgd", accumulation_steps=2)
+    ref = torch.optim.SGD(dense.parameters(), lr=0.05)
+    for step in range(3):
+        ids = torch.randint(0, 1024, (4, 16), generator=torch.Generator().manual_seed(step))
+        got = trainer.train_step(ids)
+        ref.zero_grad()
+        out = dense(ids, labels=ids)
+        out.loss.backward()
+        ref.step()
+        assert got.loss == pytest.approx(out.loss.item(), rel=2e-6)
+        assert got.valid_tokens == 4 * 15
+    full = rt.reconstruct_tp_local()
+    for name, p in dense.named_parameters():
+        torch.testing.assert_close(full[name], p, atol=3e-6, rtol=3e-5)
+    # HF names survive, every value is this rank's flat FP32 shard, tied head aliases the embedding
+    names = dict(model.named_parameters())
+    assert set(names) == set(dict(dense.named_parameters()))
+    assert all(p.ndim == 1 and p.dtype == torch.float32 for p in names.values())
+    assert (model.lm_head.weight is model.model.embed_tokens.weight) == tied
+    assert len(rt.units) == (4 if tied else 5)
+    # tied: L+2 forward, L backward (unit 0 and the last unit stay materialised)
+    # untied: L+3 forward, L+2 backward (only the head, the last unit, is retained)
+    per_step = 2 * 2 + 2 if tied else 2 * 2 + 5
+    issued = [e for e in rt.comm.events if e["event_type"] == "materialize_issue"]
+    if reshard:
+        assert len(issued) == 3 * 2 * per_step
+
+
+def test_step_protocol_guards():
+    dense = Qwen2CausalLM(tiny_qwen())
+    rt = ShardedRuntime(device="cpu")
+    rt.register(dense)
+    trainer = QwenTrainer(dense, rt, optimizer="sgd")
+    with pytest.raises(ValueError, match="exactly the persistent local shards"):
+        rt.bind_optimizer(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1))
+    with pytest.raises(RuntimeError, match="Premature optimizer"):
+        trainer.optimizer.step()
+    with pytest.raises(RuntimeError, match="Invalid step boundary"):
+        rt.begin_step(5)
+    rt.begin_step(0)
+    with pytest.raises(RuntimeError, match="Invalid step boundary"):
+        rt.begin_step(1)
+    with pytest.raises(RuntimeError, match="Missing gradient readiness"):
+        rt.finalize_backward()
+    rt.fail("test")
+    assert all(u.state == "FAILED" for u in rt.units)
+    rt.active = False
+    with pytest.raises(RuntimeError, match="FAILED runtime"):
+        rt.begin_step(1)
+    with pytest.raises(RuntimeError, match="already registered"):
+        rt.register(dense)
+
+
+def test_nonzero_padding_and_nonfinite_gradients_are_rejected():
+    torch.manual_seed(0)
+    model = Qwen2CausalLM(tiny_qwen())
+    rt = ShardedRuntime(device="cpu")
+    rt.register(model)
+    trainer = QwenTrainer(model, rt, optimizer="sgd")
+    ids = torch.randint(0, 1024, (2, 16))
+    trainer.train_step(ids)
+    handle = next(iter(rt.registry.values()))
+    rt.begin_step(rt.step_id + 1)
+    rt.zero_grad()
+    model(ids, labels=ids).loss.backward()
+    handle.grad_shard[0] = float("nan")
+    with pytest.raises(RuntimeError, match="Nonfinite gradient"):
+        rt.finalize_backward()
