@@ -93,12 +93,15 @@ cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc*
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        cudaStream_t s);
+                                        int* flags, cudaStream_t s);
 // Same, and applies AdamW to the owned shard in the same pass (last micro-step only).
+// `flags` (optional, int[2]) receives the gradient check of what was written: [0] non-finite
+// value, [1] non-zero shard padding.
 cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
-                                        float scale, bool accumulate, AdamWArgs a, cudaStream_t s);
+                                        float scale, bool accumulate, AdamWArgs a, int* flags,
+                                        cudaStream_t s);
 // Embedding lookup straight from the (possibly remote) fp32 shards: no all-gather of the table.
 cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t q,
                                             const int64_t* ids, float* out, int rows, int cols,

@@ -322,8 +322,16 @@ void gather_params(c10::ArrayRef<int64_t> shard_ptrs, const Tensor& segs, Tensor
   }
 }
 
+int* flags_ptr(const c10::optional<Tensor>& flags) {
+  if (!flags.has_value()) return nullptr;
+  need(*flags, at::kInt, "flags");
+  TORCH_CHECK(flags->numel() >= 2, "flags needs two int32 words");
+  return flags->data_ptr<int>();
+}
+
 void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor& segs,
-                    Tensor grad_shard, double scale, bool accumulate) {
+                    Tensor grad_shard, double scale, bool accumulate,
+                    const c10::optional<Tensor>& flags) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
   for (size_t i = 0; i < table.size(); i += 32) {
@@ -331,7 +339,8 @@ void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor
     check(stb::launch_reduce_scatter_grads(pp, static_cast<int>(full_ptrs.size()),
                                            static_cast<int>(rank), table.data() + i, n,
                                            grad_shard.data_ptr<float>(), grad_shard.numel(),
-                                           static_cast<float>(scale), accumulate, cur_stream()),
+                                           static_cast<float>(scale), accumulate, flags_ptr(flags),
+                                           cur_stream()),
           "reduce_scatter");
   }
 }
@@ -339,7 +348,8 @@ void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor
 void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor& segs,
                           Tensor grad_shard, Tensor p, Tensor m, Tensor v, double scale,
                           bool accumulate, double lr, double b1, double b2, double eps, double wd,
-                          double bc1, double bc2, double gscale) {
+                          double bc1, double bc2, double gscale,
+                          const c10::optional<Tensor>& flags) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
   for (size_t i = 0; i < table.size(); i += 32) {
@@ -348,7 +358,7 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
               pp, static_cast<int>(full_ptrs.size()), static_cast<int>(rank), table.data() + i, n,
               grad_shard.data_ptr<float>(), p.data_ptr<float>(), m.data_ptr<float>(),
               v.data_ptr<float>(), grad_shard.numel(), static_cast<float>(scale), accumulate,
-              adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), cur_stream()),
+              adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream()),
           "reduce_scatter_adamw");
   }
 }

@@ -84,13 +84,16 @@ template <bool ADAMW>
 __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTable tab,
                                       float* __restrict__ gshard, float* __restrict__ p,
                                       float* __restrict__ m, float* __restrict__ v, float scale,
-                                      int accumulate, AdamWArgs a) {
+                                      int accumulate, AdamWArgs a, int* __restrict__ flags) {
   const SegmentDesc sg = tab.s[blockIdx.y];
   const int64_t lo = static_cast<int64_t>(rank) * sg.q;
   const int64_t valid = max(static_cast<int64_t>(0), min(sg.q, sg.numel - lo));
   const bool vec = (sg.q % 4 == 0) && (sg.shard_off % 4 == 0) && (sg.full_off % 4 == 0);
   const float step_size = ADAMW ? a.lr / a.bias_correction1 : 0.f;
   const float inv_bc2_sqrt = ADAMW ? rsqrtf(a.bias_correction2) : 0.f;
+  // the gradient check rides along: flags[0] = a non-finite reduced gradient was written,
+  // flags[1] = a padding element of the shard is not exactly zero
+  int bad = 0, pad_bad = 0;
   for (int64_t chunk = blockIdx.x; chunk * kChunk < sg.q; chunk += gridDim.x) {
     const int64_t base = chunk * kChunk;
     const int64_t end = min(base + kChunk, sg.q);
@@ -125,6 +128,12 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
           g.x += o.x; g.y += o.y; g.z += o.z; g.w += o.w;
         }
         *reinterpret_cast<float4*>(gshard + e) = g;   // padding stays exactly zero: acc is 0 there
+        bad |= !(isfinite(g.x) && isfinite(g.y) && isfinite(g.z) && isfinite(g.w));
+        if (i + 3 >= valid) {
+          const float* gp = &g.x;
+          for (int j = 0; j < 4; ++j)
+            if (i + j >= valid && gp[j] != 0.f) pad_bad = 1;
+        }
         if (ADAMW) {
           float4 pv = *reinterpret_cast<const float4*>(p + e);
           float4 mv = *reinterpret_cast<const float4*>(m + e);
@@ -147,6 +156,8 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
         float g = acc[0] * scale;
         if (accumulate) g += gshard[e];
         gshard[e] = g;
+        bad |= !isfinite(g);
+        if (i >= valid && g != 0.f) pad_bad = 1;
         if (ADAMW) {
           float pj = p[e] * (1.f - a.lr * a.weight_decay);
           const float gr = g * a.grad_scale;
@@ -159,6 +170,10 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
         }
       }
     }
+  }
+  if (flags != nullptr) {
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(&flags[0], 1);
+    if (__syncthreads_or(pad_bad) && threadIdx.x == 0) atomicOr(&flags[1], 1);
   }
 }
 
@@ -286,7 +301,7 @@ cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc*
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        cudaStream_t s) {
+                                        int* flags, cudaStream_t s) {
   (void)shard_total;
   SegTable tab;
   if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree ||
@@ -295,14 +310,15 @@ cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int ran
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(full_grads, degree, rank, tab, grad_shard,
                                                     nullptr, nullptr, nullptr, scale,
-                                                    accumulate ? 1 : 0, AdamWArgs{});
+                                                    accumulate ? 1 : 0, AdamWArgs{}, flags);
   return cudaGetLastError();
 }
 
 cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
-                                        float scale, bool accumulate, AdamWArgs a, cudaStream_t s) {
+                                        float scale, bool accumulate, AdamWArgs a, int* flags,
+                                        cudaStream_t s) {
   (void)shard_total;
   SegTable tab;
   if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree ||
@@ -310,7 +326,7 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
     return cudaErrorInvalidValue;
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(full_grads, degree, rank, tab, grad_shard, p, m,
-                                                   v, scale, accumulate ? 1 : 0, a);
+                                                   v, scale, accumulate ? 1 : 0, a, flags);
   return cudaGetLastError();
 }
 

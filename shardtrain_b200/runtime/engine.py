@@ -428,6 +428,7 @@ class ShardedRuntime:
             if kept is not None:
                 # carried over from the previous micro-step of the same optimizer step
                 kept.step_id = step_id
+                kept.extras["carried"] = True
                 unit.lease = kept
                 unit.generation += 1
                 kept.generation = unit.generation
@@ -474,8 +475,8 @@ class ShardedRuntime:
         """One sweep over the gradient arena, one host read: non-finite values and padding that
         is not exactly zero (NaN/Inf in padding count as non-zero)."""
         if self.fused is not None and getattr(self, "defer_gradient_check", False):
-            # the flags accumulate on the device and are read with the step metrics
-            self.fused.launch_grad_check()
+            # every reduce-scatter kernel already checked what it wrote; the flags accumulate
+            # on the device and are read together with the step metrics
             return
         if self.fused is not None:
             bad = self.fused.grad_check()

@@ -178,6 +178,7 @@ class FusedExecutor:
         self.exp_avg = self.exp_avg_sq = None
         self._shards_dirty = True
         self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
+        self.check_flags = self._flags   # written by every reduce-scatter kernel
         self._rope_cache = {}
         self._scratch = {}
         self.token_grad = torch.zeros(1, dtype=torch.float32, device=runtime.device)

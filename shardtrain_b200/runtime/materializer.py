@@ -107,6 +107,9 @@ class Materializer:
 
     def finish(self, unit):
         lease = unit.lease
+        if lease.extras.pop("carried", False):
+            # kept from the previous micro-step of the same optimizer step: nothing to do
+            return tuple(lease.weights[h.spec.param_id] for h in unit.handles)
         if lease.full_param_storages:
             raise RuntimeError(f"Duplicate copy-out U{unit.unit_id}")
         self._await_gather(unit, lease)
@@ -281,6 +284,9 @@ class PeerMaterializer:
 
     def finish(self, unit):
         lease = unit.lease
+        plan = self.plans[unit.unit_id]
+        if lease.extras.pop("carried", False):
+            return plan.tokens
         if lease.weights:
             raise RuntimeError(f"Duplicate copy-out U{unit.unit_id}")
         comm = self.comm
@@ -324,10 +330,11 @@ class PeerMaterializer:
                 hp = runtime.fused_optimizer_args()
                 self.ops.reduce_scatter_adamw(
                     slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad, arenas.param,
-                    arenas.exp_avg, arenas.exp_avg_sq, 1.0 / self.degree, not first, *hp)
+                    arenas.exp_avg, arenas.exp_avg_sq, 1.0 / self.degree, not first, *hp,
+                    arenas.check_flags)
             else:
                 self.ops.reduce_scatter(slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad,
-                                        1.0 / self.degree, not first)
+                                        1.0 / self.degree, not first, arenas.check_flags)
 
         comm = self.comm
         ticket = comm.issue_kernel(

@@ -1,0 +1,112 @@
+import copy
+import json
+
+import pytest
+import torch
+
+from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+from shardtrain_b200.models.qwen2_checkpoint import (CheckpointError, QwenCheckpoint, SafetensorsFile,
+                                                     load_qwen_checkpoint, save_safetensors)
+from shardtrain_b200.runtime.checkpoint import (full_state_dict, load_full_optimizer, load_sharded,
+                                                save_full, save_sharded)
+from shardtrain_b200.runtime.engine import ShardedRuntime
+from shardtrain_b200.training.qwen2_trainer import QwenTrainer
+
+CFG = Qwen2ModelConfig(vocab_size=256, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2)
+
+
+def trained(steps=2, seed=0):
+    torch.manual_seed(seed)
+    model = Qwen2CausalLM(CFG)
+    rt = ShardedRuntime(device="cpu")
+    rt.register(model)
+    tr = QwenTrainer(model, rt, lr=1e-3, optimizer="adamw")
+    for s in range(steps):
+        tr.train_step(torch.randint(0, 256, (2, 8), generator=torch.Generator().manual_seed(s)))
+    return model, rt, tr
+
+
+def test_safetensors_roundtrip_and_slices(tmp_path):
+    tensors = {"a": torch.arange(12.).view(3, 4), "b": torch.ones(5, dtype=torch.bfloat16),
+               "c": torch.tensor(3, dtype=torch.int64)}
+    save_safetensors(tmp_path / "x.safetensors", tensors, {"k": "v"})
+    f = SafetensorsFile(tmp_path / "x.safetensors")
+    assert f.metadata == {"k": "v"}
+    for k, v in tensors.items():
+        assert torch.equal(f.tensor(k), v)
+    assert torch.equal(f.rows("a", 1, 2), tensors["a"][1:3])
+    # the file is readable by the reference ecosystem's parser too
+    from safetensors import safe_open
+    with safe_open(str(tmp_path / "x.safetensors"), framework="pt") as h:
+        assert torch.equal(h.get_tensor("a"), tensors["a"])
+
+
+def test_strict_reader_rejections(tmp_path):
+    save_safetensors(tmp_path / "model.safetensors", {"w": torch.zeros(2, 2), "extra": torch.zeros(1)})
+    with pytest.raises(CheckpointError, match="Unexpected keys: extra"):
+        QwenCheckpoint(tmp_path, {"w": (2, 2)})
+    with pytest.raises(CheckpointError, match="Missing keys"):
+        QwenCheckpoint(tmp_path, {"w": (2, 2), "extra": (1,), "gone": (1,)})
+    with pytest.raises(CheckpointError, match="Shape mismatches"):
+        QwenCheckpoint(tmp_path, {"w": (4,), "extra": (1,)})
+    with pytest.raises(CheckpointError, match="does not exist"):
+        QwenCheckpoint(tmp_path / "nope")
+    idx = tmp_path / "idx"
+    idx.mkdir()
+    save_safetensors(idx / "s1.safetensors", {"w": torch.zeros(1), "hidden": torch.zeros(1)})
+    (idx / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"w": "s1.safetensors"}}))
+    with pytest.raises(CheckpointError, match="absent from the index"):
+        QwenCheckpoint(idx)
+    (idx / "model.safetensors.index.json").write_text('{"weight_map": {"w": "../x.safetensors"}}')
+    with pytest.raises(CheckpointError, match="escapes|Missing or unsupported"):
+        QwenCheckpoint(idx)
+    (idx / "model.safetensors.index.json").write_text('{"weight_map": {"w": "a"}, "weight_map": {}}')
+    with pytest.raises(CheckpointError, match="Duplicate JSON key"):
+        QwenCheckpoint(idx)
+    with pytest.raises(CheckpointError, match="tied_aliases require"):
+        QwenCheckpoint(tmp_path, None, {"a": "b"})
+
+
+def test_dense_loader_and_tied_alias(tmp_path):
+    torch.manual_seed(1)
+    src = Qwen2CausalLM(CFG)
+    state = {k: v.detach().clone() for k, v in src.state_dict().items() if k != "lm_head.weight"}
+    save_safetensors(tmp_path / "model.safetensors", state)
+    dst = Qwen2CausalLM(CFG)
+    report = load_qwen_checkpoint(dst, tmp_path)
+    assert report.omitted_tied_aliases == ("lm_head.weight",)
+    for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), n
+
+
+def test_sharded_resume_is_bit_exact(tmp_path):
+    model, rt, tr = trained()
+    save_sharded(rt, tmp_path, tr.optimizer, trainer_step=tr.step_id)
+    ids = torch.randint(0, 256, (2, 8), generator=torch.Generator().manual_seed(9))
+    expected = tr.train_step(ids).loss
+    after = {n: h.local_shard.detach().clone() for n, h in rt.registry.items()}
+    model2, rt2, tr2 = trained(steps=0, seed=5)
+    meta = load_sharded(rt2, tmp_path, tr2.optimizer)
+    assert meta["optimizer_step"] == 2 and tr2.optimizer.arena_step == 2
+    assert tr2.train_step(ids).loss == expected
+    for n, h in rt2.registry.items():
+        assert torch.equal(h.local_shard, after[n]), n
+
+
+def test_full_export_reloads_through_the_strict_reader(tmp_path):
+    model, rt, tr = trained()
+    save_full(rt, tmp_path, tr.optimizer)
+    full = full_state_dict(rt)
+    assert full["model.layers.0.self_attn.q_proj.weight"].shape == (32, 32)
+    fresh = Qwen2CausalLM(CFG, device="meta", dtype=torch.float32)
+    fresh._qwen_weight_source = QwenCheckpoint(tmp_path)
+    rt2 = ShardedRuntime(device="cpu")
+    rt2.register(fresh)
+    tr2 = QwenTrainer(fresh, rt2, lr=1e-3, optimizer="adamw")
+    load_full_optimizer(rt2, tmp_path, tr2.optimizer)
+    for n, h in rt.registry.items():
+        assert torch.equal(rt2.registry[n].local_shard, h.local_shard), n
+    assert torch.equal(tr2.optimizer.exp_avg_sq, tr.optimizer.exp_avg_sq)
+    ids = torch.randint(0, 256, (2, 8), generator=torch.Generator().manual_seed(9))
+    assert tr2.train_step(ids).loss == tr.train_step(ids).loss

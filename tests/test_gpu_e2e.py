@@ -1,0 +1,69 @@
+"""Fused sm_100a executor end to end on one GPU against the dense model (run with -m gpu)."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def build(tied, accumulate=2, optimizer="sgd", lr=0.05, retain=False):
+    from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+    from shardtrain_b200.runtime.engine import ShardedRuntime
+    from shardtrain_b200.training.qwen2_trainer import QwenTrainer
+
+    torch.manual_seed(0)
+    cfg = Qwen2ModelConfig(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                           num_attention_heads=2, num_key_value_heads=1, tie_word_embeddings=tied)
+    dense = Qwen2CausalLM(cfg).cuda()
+    model = copy.deepcopy(dense)
+    rt = ShardedRuntime(device="cuda:0", reshard_after_forward=True, forward_prefetch=True,
+                        backward_prefetch=True, async_grad_rs=True, communication_policy="stream_ordered",
+                        retain_parameters=retain)
+    rt.register(model)
+    assert rt.executor.name == "fused"
+    tr = QwenTrainer(model, rt, lr=lr, dtype="bf16", optimizer=optimizer, accumulation_steps=accumulate)
+    return dense, model, rt, tr
+
+
+@pytest.mark.parametrize("tied", [True, False])
+def test_gradients_match_dense_bf16_autocast(tied):
+    from shardtrain_b200 import ops
+
+    dense, model, rt, tr = build(tied)
+    ids = torch.randint(0, 2048, (4, 256), device="cuda")
+    before = {n: p.detach().clone() for n, p in dense.named_parameters()}
+    got = tr.train_step(ids)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = dense(ids, labels=ids)
+    out.loss.backward()
+    assert got.loss == pytest.approx(out.loss.item(), rel=2e-3)
+    assert got.valid_tokens == 4 * 255
+    torch.cuda.synchronize()
+    ops.check_status("e2e")
+    full = rt.reconstruct_tp_local()
+    # one SGD step: (before - after) / lr is the gradient; compare with the dense bf16 gradient
+    for name, p in dense.named_parameters():
+        grad = (before[name] - full[name]) / 0.05
+        err = (grad - p.grad).norm() / (p.grad.norm() + 1e-12)
+        assert err < 3e-2, (name, err.item())
+    assert all(p.ndim == 1 and p.dtype == torch.float32 for p in model.parameters())
+    assert not rt.comm.live_buffers
+
+
+@pytest.mark.parametrize("retain", [False, True])
+def test_adamw_training_reduces_loss_and_fuses_the_update(retain):
+    from shardtrain_b200 import ops
+
+    dense, model, rt, tr = build(True, optimizer="adamw", lr=1e-3, retain=retain)
+    assert tr.optimizer.fuse_into_reduction
+    ids = torch.randint(0, 2048, (4, 256), device="cuda")
+    losses = [tr.train_step(ids).loss for _ in range(6)]
+    torch.cuda.synchronize()
+    ops.check_status("e2e adamw")
+    assert losses[-1] < losses[0] - 0.05
+    kinds = [t.kind for t in rt.comm.tickets]
+    assert "fsdp_rs_accumulate_adamw" in kinds and "fsdp_ag_cast" in kinds
+    per_micro = 2 * 2 + 2
+    gathers = kinds.count("fsdp_ag_cast")
+    assert gathers == (6 * 2 * per_micro if not retain else 6 * (2 + 2))

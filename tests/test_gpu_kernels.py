@@ -1,0 +1,266 @@
+"""sm_100a kernels against plain PyTorch FP32 references of the same op (run with -m gpu)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from shardtrain_b200 import ops as module
+
+    namespace = module.load()      # raises if the in-tree extension is missing: no fallback
+    yield namespace
+    torch.cuda.synchronize()
+    module.check_status("kernel tests")
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+GEMM_CASES = [
+    # M, N, K, a_mn, b_mn, out_fp32, bias, residual, accumulate, force_bn
+    (128, 128, 64, False, False, False, False, False, False, 128),
+    (256, 256, 512, False, False, False, False, False, False, 256),
+    (512, 2048, 1536, False, False, False, True, False, False, 0),
+    (512, 1536, 8960, False, False, True, False, True, False, 0),
+    (200, 328, 192, False, False, False, True, True, False, 0),
+    (512, 1536, 2048, False, True, True, False, False, False, 0),
+    (256, 256, 128, False, True, False, False, False, False, 128),
+    (2048, 1536, 512, True, True, True, False, False, True, 0),
+    (1000, 520, 264, True, True, True, False, False, False, 256),
+    (4096, 1536, 8960, False, False, False, False, False, False, 256),   # several tiles per CTA
+]
+
+
+@pytest.mark.parametrize("case", GEMM_CASES, ids=[f"{c[0]}x{c[1]}x{c[2]}_{int(c[3])}{int(c[4])}" for c in GEMM_CASES])
+def test_tcgen05_gemm(ops, case):
+    M, N, K, a_mn, b_mn, out_fp32, bias, resid, acc, bn = case
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = torch.randn(N, K, device=DEV).bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    ref = A.float() @ B.float().t()
+    out = torch.zeros(M, N, device=DEV, dtype=torch.float32 if out_fp32 else torch.bfloat16)
+    bias_t = torch.randn(N, device=DEV) if bias else None
+    res_t = torch.randn(M, N, device=DEV).to(out.dtype) if resid else None
+    if acc:
+        out.normal_()
+        ref = ref + out.float()
+    if bias:
+        ref = ref + bias_t
+    if resid:
+        ref = ref + res_t.float()
+    ops.gemm(a, b, out, a_mn, b_mn, bias_t, res_t, acc, 1.0, bn)
+    assert rel(out, ref) < (2e-5 if out_fp32 else 4e-3)
+
+
+def test_gemm_rejects_bad_arguments(ops):
+    a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.gemm(a, torch.zeros(128, 72, device=DEV, dtype=torch.bfloat16),
+                 torch.zeros(128, 128, device=DEV, dtype=torch.bfloat16), False, False, None, None,
+                 False, 1.0, 0)
+    with pytest.raises(RuntimeError):   # N not a multiple of 8
+        ops.gemm(a, torch.zeros(12, 64, device=DEV, dtype=torch.bfloat16),
+                 torch.zeros(128, 12, device=DEV, dtype=torch.bfloat16), False, False, None, None,
+                 False, 1.0, 0)
+
+
+def attention_reference(qkv, B, S, hq, hkv, mask, scale):
+    D = 128
+    x = qkv.float().view(B, S, hq + 2 * hkv, D).clone().requires_grad_(True)
+    q = x[:, :, :hq].transpose(1, 2)
+    k = x[:, :, hq:hq + hkv].transpose(1, 2).repeat_interleave(hq // hkv, 1)
+    v = x[:, :, hq + hkv:].transpose(1, 2).repeat_interleave(hq // hkv, 1)
+    scores = q @ k.transpose(-1, -2) * scale
+    allow = torch.ones(S, S, dtype=torch.bool, device=DEV).tril()[None, None].expand(B, 1, S, S)
+    if mask is not None:
+        allow = allow & mask.bool()[:, None, None, :]
+    scores = scores.masked_fill(~allow, float("-inf"))
+    dead = ~allow.any(-1, keepdim=True)
+    probs = torch.softmax(scores.masked_fill(dead, 0), -1).masked_fill(dead, 0)
+    return x, (probs @ v).transpose(1, 2).reshape(B * S, hq * D)
+
+
+@pytest.mark.parametrize("B,S,hq,hkv,masked", [(1, 128, 2, 1, False), (2, 512, 12, 2, False),
+                                               (2, 384, 4, 2, True), (1, 200, 2, 1, False),
+                                               (1, 1024, 4, 1, False)])
+def test_attention_forward_backward(ops, B, S, hq, hkv, masked):
+    torch.manual_seed(0)
+    D, W = 128, (hq + 2 * hkv) * 128
+    qkv = (torch.randn(B * S, W, device=DEV) * 0.5).bfloat16()
+    mask = None
+    if masked:
+        mask = torch.ones(B, S, dtype=torch.uint8, device=DEV)
+        mask[0, : S // 3] = 0
+        mask[-1, S // 2:] = 0
+    scale = 1 / math.sqrt(D)
+    out = torch.zeros(B * S, hq * D, device=DEV, dtype=torch.bfloat16)
+    lse = torch.zeros(B, hq, S, device=DEV)
+    ops.attention_fwd(qkv, out, lse, mask, B, S, hq, hkv, scale)
+    x, ref = attention_reference(qkv, B, S, hq, hkv, mask, scale)
+    assert rel(out, ref) < 5e-3
+    dout = (torch.randn(B * S, hq * D, device=DEV) * 0.5).bfloat16()
+    ref.backward(dout.float())
+    want = x.grad.view(B * S, W)
+    delta = torch.zeros(B, hq, S, device=DEV)
+    dqkv = torch.zeros(B * S, W, device=DEV, dtype=torch.bfloat16)
+    ops.attention_bwd(qkv, out, dout, lse, delta, dqkv, delta, mask, B, S, hq, hkv, scale)
+    for lo, hi in ((0, hq * D), (hq * D, (hq + hkv) * D), ((hq + hkv) * D, W)):
+        assert rel(dqkv[:, lo:hi], want[:, lo:hi]) < 6e-3
+
+
+def test_rmsnorm_rope_swiglu(ops):
+    torch.manual_seed(1)
+    T, H = 300, 1536
+    x, w = torch.randn(T, H, device=DEV), torch.randn(H, device=DEV)
+    y = torch.empty(T, H, device=DEV, dtype=torch.bfloat16)
+    inv = torch.empty(T, device=DEV)
+    ops.rmsnorm_fwd(x, w, y, inv, 1e-6)
+    assert rel(y, x * torch.rsqrt(x.square().mean(-1, keepdim=True) + 1e-6) * w) < 4e-3
+    dy, dres = torch.randn(T, H, device=DEV), torch.randn(T, H, device=DEV)
+    dx, part = torch.empty_like(x), torch.empty(592, H, device=DEV)
+    ops.rmsnorm_bwd(dy, x, w, inv, dres, dx, part)
+    dw = torch.empty(H, device=DEV)
+    ops.colsum_f32(part, dw, False)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    (xr * torch.rsqrt(xr.square().mean(-1, keepdim=True) + 1e-6) * wr).backward(dy)
+    assert rel(dx, xr.grad + dres) < 1e-5 and rel(dw, wr.grad) < 1e-5
+    hq, hkv, d, S = 12, 2, 128, 256
+    rows = 2 * S
+    qkv = torch.randn(rows, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    ang = torch.arange(S, device=DEV).float()[:, None] * (1e6 ** (-torch.arange(0, d, 2, device=DEV).float() / d))[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    before = qkv.clone()
+    ops.rope(qkv, cos, sin, None, S, hq, hkv, d, False)
+    t = before[:, :hq * d].float().view(rows, hq, d)
+    c = torch.cat([cos, cos], -1).repeat(2, 1)[:, None]
+    s = torch.cat([sin, sin], -1).repeat(2, 1)[:, None]
+    want = (t * c + torch.cat([-t[..., d // 2:], t[..., :d // 2]], -1) * s).reshape(rows, hq * d)
+    assert rel(qkv[:, :hq * d], want) < 4e-3
+    assert torch.equal(qkv[:, (hq + hkv) * d:], before[:, (hq + hkv) * d:])
+    ops.rope(qkv, cos, sin, None, S, hq, hkv, d, True)
+    assert rel(qkv, before) < 4e-3
+    inter = 8960
+    gu = torch.randn(T, 2 * inter, device=DEV).bfloat16()
+    h = torch.empty(T, inter, device=DEV, dtype=torch.bfloat16)
+    ops.swiglu_fwd(gu, h)
+    g, u = gu[:, :inter].float(), gu[:, inter:].float()
+    assert rel(h, torch.nn.functional.silu(g) * u) < 6e-3
+    dh, dgu = torch.randn(T, inter, device=DEV).bfloat16(), torch.empty_like(gu)
+    ops.swiglu_bwd(dh, gu, dgu)
+    gr, ur = g.clone().requires_grad_(True), u.clone().requires_grad_(True)
+    (torch.nn.functional.silu(gr) * ur).backward(dh.float())
+    assert rel(dgu[:, :inter], gr.grad) < 4e-3 and rel(dgu[:, inter:], ur.grad) < 4e-3
+
+
+def test_cross_entropy_and_column_sums(ops):
+    torch.manual_seed(2)
+    R, V = 200, 151936
+    logits = (torch.randn(R, V, device=DEV) * 2).bfloat16()
+    labels = torch.randint(0, V, (R,), device=DEV)
+    labels[::7] = -100
+    lse, rows, total = torch.empty(R, device=DEV), torch.empty(R, device=DEV), torch.zeros(1, device=DEV)
+    ops.ce_fwd(logits, labels, lse, rows)
+    ops.sum_f32(rows, total, False)
+    lf = logits.float().clone().requires_grad_(True)
+    want = torch.nn.functional.cross_entropy(lf, labels, ignore_index=-100, reduction="sum")
+    assert abs(total.item() - want.item()) / want.item() < 1e-5
+    want.backward()
+    ops.ce_bwd(logits, labels, lse, torch.full((1,), 0.5, device=DEV))
+    assert rel(logits, lf.grad * 0.5) < 5e-3
+    x = torch.randn(777, 2048, device=DEV).bfloat16()
+    out, scratch = torch.empty(2048, device=DEV), torch.empty(64, 2048, device=DEV)
+    ops.colsum_bf16(x, out, False, scratch)
+    assert rel(out, x.float().sum(0)) < 1e-5
+
+
+def test_optimizer_and_gradient_check(ops):
+    torch.manual_seed(3)
+    n = 1000003
+    p, g = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    ref = torch.nn.Parameter(p.clone())
+    ref.grad = g.clone()
+    opt = torch.optim.AdamW([ref], lr=1e-3)
+    for step in (1, 2, 3):
+        opt.step()
+        ops.adamw(p, g, m, v, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1 - 0.9 ** step, 1 - 0.999 ** step, 1.0)
+    assert (p - ref.data).abs().max().item() < 3e-6
+    flags = torch.zeros(2, device=DEV, dtype=torch.int32)
+    grad = torch.zeros(10000, device=DEV)
+    pads = torch.tensor([100, 200], device=DEV)
+    ops.grad_check(grad, pads, flags)
+    assert flags.tolist() == [0, 0]
+    grad[150] = 1.0
+    ops.grad_check(grad, pads, flags)
+    assert flags.tolist() == [0, 1]
+    flags.zero_()
+    grad[150], grad[5000] = 0, float("nan")
+    ops.grad_check(grad, pads, flags)
+    assert flags.tolist() == [1, 0]
+
+
+def test_shard_gather_and_reduce_scatter_with_emulated_ranks(ops):
+    """Degree-2 tables over two buffers of one GPU: the kernels only use plain loads, so the
+    rank dimension can be emulated without a second device."""
+    F = 2
+    numels = [1536 * 2048, 1536, 2048 * 3 + 1, 1000]
+    segs, shard_off, full_off = [], 0, 0
+    for i, n in enumerate(numels):
+        q = -(-n // F)
+        segs.append([shard_off, q, n, full_off, 1 if i in (1, 3) else 0])
+        shard_off += -(-q // 4) * 4
+        full_off += -(-n // 8) * 8
+    table = torch.tensor(segs, dtype=torch.int64)
+    fulls = [torch.randn(n, device=DEV) for n in numels]
+    shards = [torch.zeros(shard_off, device=DEV) for _ in range(F)]
+    for (so, q, n, fo, k), f in zip(segs, fulls):
+        for r in range(F):
+            keep = max(0, min(q, n - r * q))
+            shards[r][so:so + keep] = f[r * q:r * q + keep]
+    fb, ff = torch.zeros(full_off, device=DEV, dtype=torch.bfloat16), torch.zeros(full_off, device=DEV)
+    ops.gather_params([s.data_ptr() for s in shards], table, fb, ff)
+    for (so, q, n, fo, k), f in zip(segs, fulls):
+        got = ff[fo:fo + n] if k else fb[fo:fo + n].float()
+        assert torch.equal(got, f if k else f.bfloat16().float())
+    grads = [torch.randn(full_off, device=DEV) for _ in range(F)]
+    for r in range(F):
+        gs = torch.ones(shard_off, device=DEV)
+        p, m, v = torch.randn(shard_off, device=DEV), torch.zeros(shard_off, device=DEV), torch.zeros(shard_off, device=DEV)
+        p0 = p.clone()
+        ops.reduce_scatter_adamw([t.data_ptr() for t in grads], r, table, gs, p, m, v, 0.5, True,
+                                 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, None)
+        for (so, q, n, fo, k) in segs:
+            keep = max(0, min(q, n - r * q))
+            want = 1 + 0.5 * sum(t[fo + r * q:fo + r * q + keep] for t in grads)
+            torch.testing.assert_close(gs[so:so + keep], want, atol=1e-6, rtol=1e-6)
+            assert (gs[so + keep:so + q] == 1).all()      # accumulate adds exact zero in the padding
+            ref = torch.nn.Parameter(p0[so:so + keep].clone())
+            ref.grad = want.clone()
+            torch.optim.AdamW([ref], lr=1e-3).step()
+            torch.testing.assert_close(p[so:so + keep], ref.data, atol=2e-6, rtol=2e-6)
+
+
+def test_bounded_peer_wait_reports_instead_of_hanging(ops):
+    """A flag nobody sets: the barrier kernel gives up after its iteration limit and records a
+    status code; the context stays usable."""
+    from shardtrain_b200 import ops as module
+
+    pad_a = torch.zeros(64, device=DEV, dtype=torch.int32)
+    pad_b = torch.zeros(64, device=DEV, dtype=torch.int32)
+    ops.peer_barrier([pad_a.data_ptr()], 0, 1, 0, 1000)
+    torch.cuda.synchronize()
+    assert ops.status_read() == 0
+    ops.peer_barrier([pad_a.data_ptr(), pad_b.data_ptr()], 0, 5, 1, 2000)   # "peer 1" never signals
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer flag wait expired"):
+        module.check_status("test")
+    assert ops.status_read() == 0
+    assert torch.ones(4, device=DEV).sum().item() == 4
