@@ -37,7 +37,7 @@ class PeerBuffer:
 
 
 class PeerMemory:
-    def __init__(self, group, device, ops, *, max_spin: int = 50_000_000):
+    def __init__(self, group, device, ops, *, max_spin: int = 200_000_000):
         self.group, self.device, self.ops = group, torch.device(device), ops
         live = dist.is_initialized() and group is not None
         self.degree = dist.get_world_size(group) if live else 1
