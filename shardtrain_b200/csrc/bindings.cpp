@@ -40,6 +40,7 @@ int64_t status_read() {
   return status_tensor().index({0}).item<int64_t>();
 }
 void status_reset() { status_tensor().zero_(); }
+Tensor status_tensor_op() { return status_tensor(); }
 
 void gemm(const Tensor& a, const Tensor& b, Tensor out, bool a_mn, bool b_mn,
           const c10::optional<Tensor>& bias, const c10::optional<Tensor>& residual,
@@ -488,6 +489,7 @@ void attention_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, con
 TORCH_LIBRARY(stb, m) {
   m.def("status_read", &status_read);
   m.def("status_reset", &status_reset);
+  m.def("status_tensor", &status_tensor_op);
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

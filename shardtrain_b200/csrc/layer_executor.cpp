@@ -1,0 +1,171 @@
+// Native executor of one Qwen2 decoder layer: the whole forward (11 launches) or backward
+// (27 launches) sequence is issued from C++ in one call, so the host cost per layer is a few
+// microseconds per launch instead of a Python round trip per kernel.  The math and the launch
+// order are those documented in shardtrain_b200/runtime/fused.py (FusedLayerFn); this file only
+// moves the sequencing off the interpreter.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/library.h>
+
+#include <cmath>
+#include <vector>
+
+#include "api.h"
+
+namespace {
+
+using at::Tensor;
+
+void ok(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, "shardtrain_b200 layer executor: ", what, ": ", cudaGetErrorString(e));
+}
+
+struct Gemm {
+  cudaStream_t stream;
+  int* status;
+  void run(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, const float* bias,
+           const Tensor* residual) const {
+    stb::GemmCall c{};
+    c.M = static_cast<int>(a_mn ? a.size(1) : a.size(0));
+    c.K = static_cast<int>(a_mn ? a.size(0) : a.size(1));
+    c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+    c.a = a.data_ptr();
+    c.b = b.data_ptr();
+    c.out = out.data_ptr();
+    c.lda = a.stride(0);
+    c.ldb = b.stride(0);
+    c.ldo = out.stride(0);
+    c.a_mn = a_mn;
+    c.b_mn = b_mn;
+    c.out_fp32 = out.scalar_type() == at::kFloat;
+    c.accumulate = false;
+    c.alpha = 1.f;
+    c.force_bn = 0;
+    c.bias = bias;
+    c.residual = residual ? residual->data_ptr() : nullptr;
+    ok(stb::launch_gemm_bf16(c, status, stream), "gemm");
+  }
+};
+
+// x2 [M,H] fp32 -> {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out}
+std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const Tensor& b_qkv,
+                                  const Tensor& w_o, const Tensor& w_gu, const Tensor& w_down,
+                                  const Tensor& ln1, const Tensor& ln2, const Tensor& cos,
+                                  const Tensor& sin, const c10::optional<Tensor>& positions,
+                                  const c10::optional<Tensor>& mask, Tensor status, int64_t B,
+                                  int64_t S, int64_t hq, int64_t hkv, double eps) {
+  const int64_t M = B * S, H = x2.size(1), D = 128;
+  const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
+  auto bf = x2.options().dtype(at::kBFloat16);
+  auto f32 = x2.options().dtype(at::kFloat);
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  Gemm g{st, status.data_ptr<int>()};
+  const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
+  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+
+  Tensor h1 = at::empty({M, H}, bf), inv1 = at::empty({M}, f32);
+  ok(stb::launch_rmsnorm_fwd(x2.data_ptr<float>(), ln1.data_ptr<float>(), h1.data_ptr(),
+                             inv1.data_ptr<float>(), M, H, static_cast<float>(eps), false, st), "rmsnorm");
+  Tensor qkv = at::empty({M, W}, bf);
+  g.run(h1, w_qkv, qkv, false, false, b_qkv.data_ptr<float>(), nullptr);
+  ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
+                      hkv, D, false, st), "rope");
+  Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
+  stb::AttnCall ac{qkv.data_ptr(), attn.data_ptr(), lse.data_ptr<float>(), km, static_cast<int>(B),
+                   static_cast<int>(S), static_cast<int>(hq), static_cast<int>(hkv),
+                   static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)))};
+  ok(stb::launch_attention_fwd(ac, g.status, st), "attention_fwd");
+  Tensor x_mid = at::empty({M, H}, f32);
+  g.run(attn, w_o, x_mid, false, false, nullptr, &x2);
+  Tensor h2 = at::empty({M, H}, bf), inv2 = at::empty({M}, f32);
+  ok(stb::launch_rmsnorm_fwd(x_mid.data_ptr<float>(), ln2.data_ptr<float>(), h2.data_ptr(),
+                             inv2.data_ptr<float>(), M, H, static_cast<float>(eps), false, st), "rmsnorm");
+  Tensor gu = at::empty({M, 2 * inter}, bf);
+  g.run(h2, w_gu, gu, false, false, nullptr, nullptr);
+  Tensor hm = at::empty({M, inter}, bf);
+  ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu");
+  Tensor out = at::empty({M, H}, f32);
+  g.run(hm, w_down, out, false, false, nullptr, &x_mid);
+  return {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out};
+}
+
+// Gradient views (down, gate_up, ln2, o, bias, qkv, ln1) point into the unit's gradient slot.
+Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1, const Tensor& h1,
+                      const Tensor& qkv, const Tensor& attn, const Tensor& lse, const Tensor& x_mid,
+                      const Tensor& inv2, const Tensor& h2, const Tensor& gu, const Tensor& w_qkv,
+                      const Tensor& w_o, const Tensor& w_gu, const Tensor& w_down, const Tensor& ln1,
+                      const Tensor& ln2, Tensor g_down, Tensor g_gate_up, Tensor g_ln2, Tensor g_o,
+                      Tensor g_bias, Tensor g_qkv, Tensor g_ln1, const Tensor& cos, const Tensor& sin,
+                      const c10::optional<Tensor>& positions, const c10::optional<Tensor>& mask,
+                      Tensor status, int64_t B, int64_t S, int64_t hq, int64_t hkv) {
+  const int64_t M = B * S, H = x2.size(1), D = 128;
+  const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
+  auto bf = x2.options().dtype(at::kBFloat16);
+  auto f32 = x2.options().dtype(at::kFloat);
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  Gemm g{st, status.data_ptr<int>()};
+  const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
+  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  constexpr int kPartial = 592;
+
+  Tensor d_out_b = at::empty({M, H}, bf);
+  ok(stb::launch_cast_f32_to_bf16(d_out.data_ptr<float>(), d_out_b.data_ptr(), M * H, st), "cast");
+  Tensor hm = at::empty({M, inter}, bf);
+  ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu recompute");
+  g.run(d_out_b, hm, g_down, true, true, nullptr, nullptr);                 // dW down
+  Tensor d_hm = at::empty({M, inter}, bf);
+  g.run(d_out_b, w_down, d_hm, false, true, nullptr, nullptr);              // dX down
+  Tensor d_gu = at::empty({M, 2 * inter}, bf);
+  ok(stb::launch_swiglu_bwd(d_hm.data_ptr(), gu.data_ptr(), d_gu.data_ptr(), M, inter, st), "swiglu_bwd");
+  g.run(d_gu, h2, g_gate_up, true, true, nullptr, nullptr);                 // dW gate|up
+  Tensor d_h2 = at::empty({M, H}, f32);
+  g.run(d_gu, w_gu, d_h2, false, true, nullptr, nullptr);                   // dX gate|up
+  Tensor d_mid = at::empty({M, H}, f32), partial = at::empty({kPartial, H}, f32);
+  ok(stb::launch_rmsnorm_bwd(d_h2.data_ptr<float>(), x_mid.data_ptr<float>(), ln2.data_ptr<float>(),
+                             inv2.data_ptr<float>(), d_out.data_ptr<float>(), d_mid.data_ptr<float>(),
+                             partial.data_ptr<float>(), kPartial, M, H, st), "rmsnorm_bwd");
+  ok(stb::launch_colsum_f32(partial.data_ptr<float>(), g_ln2.data_ptr<float>(), kPartial, H, false, st), "colsum");
+
+  Tensor d_mid_b = at::empty({M, H}, bf);
+  ok(stb::launch_cast_f32_to_bf16(d_mid.data_ptr<float>(), d_mid_b.data_ptr(), M * H, st), "cast");
+  g.run(d_mid_b, attn, g_o, true, true, nullptr, nullptr);                  // dW o
+  Tensor d_attn = at::empty({M, hq * D}, bf);
+  g.run(d_mid_b, w_o, d_attn, false, true, nullptr, nullptr);               // dX o
+  Tensor d_qkv = at::empty({M, W}, bf), delta = at::empty({B, hq, S}, f32);
+  stb::AttnBwdCall bc{};
+  bc.qkv = qkv.data_ptr();
+  bc.out = attn.data_ptr();
+  bc.dout = d_attn.data_ptr();
+  bc.lse = lse.data_ptr<float>();
+  bc.delta = delta.data_ptr<float>();
+  bc.dqkv = d_qkv.data_ptr();
+  bc.dkv_accum = nullptr;
+  bc.key_mask = km;
+  bc.batch = static_cast<int>(B);
+  bc.seq = static_cast<int>(S);
+  bc.hq = static_cast<int>(hq);
+  bc.hkv = static_cast<int>(hkv);
+  bc.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)));
+  ok(stb::launch_attention_bwd(bc, g.status, st), "attention_bwd");
+  ok(stb::launch_rope(d_qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
+                      hkv, D, true, st), "rope inverse");
+  Tensor bias_partial = at::empty({64, W}, f32);
+  ok(stb::launch_colsum_bf16(d_qkv.data_ptr(), W, g_bias.data_ptr<float>(), M, W, false,
+                             bias_partial.data_ptr<float>(), 64, st), "bias colsum");
+  g.run(d_qkv, h1, g_qkv, true, true, nullptr, nullptr);                    // dW q|k|v
+  Tensor d_h1 = at::empty({M, H}, f32);
+  g.run(d_qkv, w_qkv, d_h1, false, true, nullptr, nullptr);                 // dX q|k|v
+  Tensor dx = at::empty({M, H}, f32);
+  ok(stb::launch_rmsnorm_bwd(d_h1.data_ptr<float>(), x2.data_ptr<float>(), ln1.data_ptr<float>(),
+                             inv1.data_ptr<float>(), d_mid.data_ptr<float>(), dx.data_ptr<float>(),
+                             partial.data_ptr<float>(), kPartial, M, H, st), "rmsnorm_bwd");
+  ok(stb::launch_colsum_f32(partial.data_ptr<float>(), g_ln1.data_ptr<float>(), kPartial, H, false, st), "colsum");
+  return dx;
+}
+
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(stb, m) {
+  m.def("layer_forward", &layer_forward);
+  m.def("layer_backward", &layer_backward);
+}

@@ -40,7 +40,28 @@ __global__ void gather_params_kernel(PeerPtrs shards, int degree, SegTable tab,
   const bool vec = (sg.q % 4 == 0) && (sg.shard_off % 4 == 0) && (sg.full_off % 4 == 0);
   for (int64_t chunk = blockIdx.x; chunk * kChunk < sg.numel; chunk += gridDim.x) {
     const int64_t base = chunk * kChunk;
-    if (vec) {
+    if (vec && base + kChunk <= sg.numel && blockDim.x * 4 * 4 == kChunk) {
+      // full chunk: four independent 16-byte loads in flight per thread before any store
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + (u * blockDim.x + threadIdx.x) * 4;
+        const int r = static_cast<int>(i / sg.q);
+        v[u] = *reinterpret_cast<const float4*>(shards.p[r] + sg.shard_off + (i - r * sg.q));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + (u * blockDim.x + threadIdx.x) * 4;
+        if (sg.keep_fp32) {
+          *reinterpret_cast<float4*>(full_fp32 + sg.full_off + i) = v[u];
+        } else {
+          uint2 o;
+          o.x = pk2(v[u].x, v[u].y);
+          o.y = pk2(v[u].z, v[u].w);
+          *reinterpret_cast<uint2*>(full_bf16 + sg.full_off + i) = o;
+        }
+      }
+    } else if (vec) {
       for (int64_t i = base + threadIdx.x * 4; i < min(base + kChunk, sg.numel);
            i += blockDim.x * 4) {
         const int r = static_cast<int>(i / sg.q);  // q % 4 == 0: the 4 elements share a rank

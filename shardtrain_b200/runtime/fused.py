@@ -173,6 +173,7 @@ class FusedExecutor:
         if self.cfg.head_dim != 128:
             raise ValueError("The sm_100a attention kernel supports head_dim 128 only")
         self.ops = ops_module.load()
+        self.status = self.ops.status_tensor()
         self.peer = PeerMemory(mesh.fsdp_group if mesh else None, runtime.device, self.ops)
         self.tp_peer = None
         self.exp_avg = self.exp_avg_sq = None
@@ -505,29 +506,11 @@ class FusedLayerFn(torch.autograd.Function):
         x2 = x.reshape(M, H).contiguous()
         w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2 = (
             w["w_qkv"], w["b_qkv"], w["w_o"], w["w_gu"], w["w_down"], w["ln1"], w["ln2"])
-        bf, f32 = torch.bfloat16, torch.float32
-
-        h1 = torch.empty((M, H), dtype=bf, device=dev)
-        inv1 = torch.empty(M, dtype=f32, device=dev)
-        ops.rmsnorm_fwd(x2, ln1, h1, inv1, cfg.rms_norm_eps)
-        qkv = torch.empty((M, W), dtype=bf, device=dev)
-        ops.gemm(h1, w_qkv, qkv, False, False, b_qkv, None, False, 1.0, 0)
         unit.prefetch_after_input(unit.forward_prefetch_handle, "FWD")
-        ops.rope(qkv, cos, sin, positions, S, hq, hkv, D, False)
-        attn = torch.empty((M, hq * D), dtype=bf, device=dev)
-        lse = torch.empty((B, hq, S), dtype=f32, device=dev)
-        ops.attention_fwd(qkv, attn, lse, mask, B, S, hq, hkv, 1.0 / math.sqrt(D))
-        x_mid = torch.empty((M, H), dtype=f32, device=dev)
-        ops.gemm(attn, w_o, x_mid, False, False, None, x2, False, 1.0, 0)
-        h2 = torch.empty((M, H), dtype=bf, device=dev)
-        inv2 = torch.empty(M, dtype=f32, device=dev)
-        ops.rmsnorm_fwd(x_mid, ln2, h2, inv2, cfg.rms_norm_eps)
-        gu = torch.empty((M, 2 * inter), dtype=bf, device=dev)
-        ops.gemm(h2, w_gu, gu, False, False, None, None, False, 1.0, 0)
-        hm = ex.scratch("mlp_hidden", (M, inter), bf)
-        ops.swiglu_fwd(gu, hm)
-        out = torch.empty((M, H), dtype=f32, device=dev)
-        ops.gemm(hm, w_down, out, False, False, None, x_mid, False, 1.0, 0)
+        # the 11 launches of the forward run from C++ (csrc/layer_executor.cpp)
+        h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out = ops.layer_forward(
+            x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask, ex.status,
+            B, S, hq, hkv, cfg.rms_norm_eps)
 
         ctx.ex, ctx.unit, ctx.index, ctx.tables, ctx.mask = ex, unit, index, tables, mask
         ctx.dims = (B, S, H, inter)
@@ -555,38 +538,9 @@ class FusedLayerFn(torch.autograd.Function):
         unit.prefetch_after_input(unit.backward_prefetch_handle, "BWD")
 
         d_out = dout.reshape(M, H).contiguous()
-        d_out_b = ex.scratch("d_res_bf16", (M, H), bf)
-        ops.cast_bf16(d_out, d_out_b)
-        hm = ex.scratch("mlp_hidden", (M, inter), bf)
-        ops.swiglu_fwd(gu, hm)                                                    # recompute
-        ops.gemm(d_out_b, hm, gv["down"], True, True, None, None, False, 1.0, 0)
-        d_hm = ex.scratch("d_mlp_hidden", (M, inter), bf)
-        ops.gemm(d_out_b, w_down, d_hm, False, True, None, None, False, 1.0, 0)
-        d_gu = ex.scratch("d_gate_up", (M, 2 * inter), bf)
-        ops.swiglu_bwd(d_hm, gu, d_gu)
-        ops.gemm(d_gu, h2, gv["gate_up"], True, True, None, None, False, 1.0, 0)
-        d_h2 = ex.scratch("d_normed", (M, H), f32)
-        ops.gemm(d_gu, w_gu, d_h2, False, True, None, None, False, 1.0, 0)
-        d_mid = ex.scratch("d_mid", (M, H), f32)
-        partial = ex.scratch("norm_partial", (592, H), f32)
-        ops.rmsnorm_bwd(d_h2, x_mid, ln2, inv2, d_out, d_mid, partial)
-        ops.colsum_f32(partial, gv["ln2"], False)
-
-        d_mid_b = ex.scratch("d_res_bf16", (M, H), bf)
-        ops.cast_bf16(d_mid, d_mid_b)
-        ops.gemm(d_mid_b, attn, gv["o"], True, True, None, None, False, 1.0, 0)
-        d_attn = ex.scratch("d_attn", (M, hq * D), bf)
-        ops.gemm(d_mid_b, w_o, d_attn, False, True, None, None, False, 1.0, 0)
-        d_qkv = ex.scratch("d_qkv", (M, W), bf)
-        delta = ex.scratch("attn_delta", (B, hq, S), f32)
-        ops.attention_bwd(qkv, attn, d_attn, lse, delta, d_qkv, delta, ctx.mask, B, S, hq, hkv,
-                          1.0 / math.sqrt(D))
-        ops.rope(d_qkv, cos, sin, positions, S, hq, hkv, D, True)
-        ops.colsum_bf16(d_qkv, gv["bias"], False, ex.scratch("bias_partial", (64, W), f32))
-        ops.gemm(d_qkv, h1, gv["qkv"], True, True, None, None, False, 1.0, 0)
-        d_h1 = ex.scratch("d_normed", (M, H), f32)
-        ops.gemm(d_qkv, w_qkv, d_h1, False, True, None, None, False, 1.0, 0)
-        dx = torch.empty((M, H), dtype=f32, device=dout.device)
-        ops.rmsnorm_bwd(d_h1, x2, ln1, inv1, d_mid, dx, partial)
-        ops.colsum_f32(partial, gv["ln1"], False)
+        # the 27 launches of the backward run from C++ (csrc/layer_executor.cpp)
+        dx = ops.layer_backward(
+            d_out, x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, w_qkv, w_o, w_gu, w_down, ln1,
+            ln2, gv["down"], gv["gate_up"], gv["ln2"], gv["o"], gv["bias"], gv["qkv"], gv["ln1"], cos,
+            sin, positions, ctx.mask, ex.status, B, S, hq, hkv)
         return (dx.view(B, S, H), None, None, None, None, None, *([ex.token_grad] * len(plan.names)))
