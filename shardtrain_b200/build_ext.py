@@ -93,5 +93,10 @@ def build(verbose: bool = False) -> Path:
     return OUT
 
 
-if __name__ == "__main__":
+def main() -> int:
     print(build(verbose=True))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

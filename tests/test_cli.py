@@ -1,0 +1,157 @@
+"""Entry points: `shardtrain_b200.train` routing and the Qwen benchmark's records
+(modelled on tests/test_train_cli.py and tests/test_qwen2_benchmark.py of the reference)."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from shardtrain_b200 import train
+from shardtrain_b200.config import ConfigError, load_config
+from shardtrain_b200.training import qwen2_benchmark
+from tests.launch import ROOT, run_workers
+
+CONFIGS = ROOT / "configs"
+
+
+def test_every_preset_parses():
+    names = sorted(p.name for p in CONFIGS.glob("*.yaml") if p.name != "qwen25_1p5b_config.yaml")
+    assert {"qwen25_tiny.yaml", "qwen25_1p5b_b200.yaml", "correctness.yaml", "tp_sp.yaml",
+            "runtime_cpu.yaml", "smoke_gloo.yaml"} <= set(names)
+    for name in names:
+        load_config(CONFIGS / name)
+    headline = load_config(CONFIGS / "qwen25_1p5b_b200.yaml")
+    assert headline.parallel.strategy == "F8T1"
+    assert headline.training.local_batch_size * headline.parallel.fsdp_degree == 8
+
+
+def test_train_toy_reference_writes_step_rows(tmp_path):
+    out = tmp_path / "run"
+    assert train.main(["--config", str(CONFIGS / "correctness.yaml"), "--debug.output_dir", str(out),
+                       "--training.steps", "2"]) == 0
+    rows = json.loads((out / "steps.rank0.json").read_text())
+    assert [r["step"] for r in rows] == [0, 1]
+    assert rows[1]["loss"] != rows[0]["loss"]
+    assert (out / "environment.rank0.json").exists() and (out / "resolved_config.rank0.yaml").exists()
+
+
+def test_train_toy_through_runtime_flag(tmp_path):
+    out = tmp_path / "run"
+    assert train.main(["--config", str(CONFIGS / "correctness.yaml"), "--sharded-runtime",
+                       "--debug.output_dir", str(out), "--training.steps", "2"]) == 0
+    assert len(json.loads((out / "steps.rank0.json").read_text())) == 2
+    assert (out / "runtime_events.rank0.jsonl").exists()
+
+
+def test_train_qwen_routes_to_benchmark(tmp_path):
+    out = tmp_path / "run"
+    assert train.main(["--config", str(CONFIGS / "qwen25_tiny.yaml"), "--debug.output_dir", str(out),
+                       "--training.steps", "2"]) == 0
+    record = json.loads((out / "benchmark.rank0.json").read_text())
+    assert record["status"] == "completed" and record["warmup"] == 0
+    assert record["steady_steps_completed"] == 2
+
+
+def test_bad_override_is_a_usage_error(tmp_path, capsys):
+    with pytest.raises(SystemExit) as info:
+        train.main(["--config", str(CONFIGS / "correctness.yaml"), "--training.nonsense", "1"])
+    assert info.value.code == 2
+    assert "nonsense" in capsys.readouterr().err
+
+
+def test_benchmark_record_contents_and_directory_reuse(tmp_path):
+    out = tmp_path / "bench"
+    config = load_config(CONFIGS / "qwen25_tiny.yaml", ["--debug.output_dir", str(out),
+                                                         "--training.steps", "3"])
+    record = qwen2_benchmark.run(config, warmup=1, peak_tflops_per_gpu=100.0)
+    assert record["status"] == "completed" and len(record["warmup_steps"]) == 1
+    assert [row["measured_step"] for row in record["steps"]] == [0, 1, 2]
+    assert record["step_seconds_p50"] <= record["step_seconds_p95"]
+    assert record["global_batch"] == 2 and record["steps"][0]["valid_tokens"] == 2 * 15
+    own = record["ownership"]
+    assert own["stable_shard_identity"] and own["units_reduced_once_last_microbatch"]
+    assert own["live_buffers"] == 0 and own["live_fullparam_leases"] == 0
+    assert own["optimizer_tensor_bytes"] == 2 * own["parameter_bytes"]
+    perf = record["performance"]
+    assert perf["mfu_percent"] > 0 and perf["unprofiled_timing"]
+    assert record["model_source"]["tied_aliases"] == {"lm_head.weight": "model.embed_tokens.weight"}
+    assert json.loads((out / "benchmark.rank0.json").read_text())["input_batch_digest"] == \
+        record["input_batch_digest"]
+    with pytest.raises(ConfigError, match="already contains rank 0"):
+        qwen2_benchmark.run(config, warmup=0)
+
+
+def test_benchmark_rejects_bad_arguments(tmp_path):
+    config = load_config(CONFIGS / "qwen25_tiny.yaml", ["--debug.output_dir", str(tmp_path / "x")])
+    for kwargs in ({"warmup": -1}, {"profile_mode": "nsight"}, {"profile_mode": "bogus"},
+                   {"profile_detail": "bogus"}, {"peak_tflops_per_gpu": 0.0}):
+        with pytest.raises(ConfigError):
+            qwen2_benchmark.run(config, **kwargs)
+    toy = load_config(CONFIGS / "correctness.yaml")
+    with pytest.raises(ConfigError, match="qwen2"):
+        qwen2_benchmark.run(toy)
+
+
+def test_benchmark_failure_is_recorded_then_raised(tmp_path, monkeypatch):
+    out = tmp_path / "bench"
+    config = load_config(CONFIGS / "qwen25_tiny.yaml", ["--debug.output_dir", str(out)])
+
+    def explode(self, *a, **k):
+        raise RuntimeError("CUDA out of memory (injected on the host)")
+
+    monkeypatch.setattr(qwen2_benchmark.QwenTrainer, "train_step", explode)
+    with pytest.raises(RuntimeError, match="injected"):
+        qwen2_benchmark.run(config, warmup=0)
+    record = json.loads((out / "benchmark.rank0.json").read_text())
+    assert record["status"] == "failed" and record["oom"] and record["steady_steps_completed"] == 0
+
+
+def test_benchmark_torch_profile_mode_on_cpu(tmp_path):
+    out = tmp_path / "bench"
+    config = load_config(CONFIGS / "qwen25_tiny.yaml", ["--debug.output_dir", str(out),
+                                                         "--training.steps", "1"])
+    record = qwen2_benchmark.run(config, warmup=0, profile_mode="torch")
+    assert record["runtime_events_enabled"] and not record["performance"]["unprofiled_timing"]
+    assert (out / "profile.rank0.json").exists() and (out / "profiling.rank0.json").exists()
+    assert (out / "runtime_events.rank0.jsonl").exists()
+
+
+def test_percentile_interpolates():
+    assert qwen2_benchmark.percentile([], 0.5) is None
+    assert qwen2_benchmark.percentile([4.0], 0.95) == 4.0
+    assert qwen2_benchmark.percentile([1.0, 2.0, 3.0, 4.0], 0.5) == 2.5
+
+
+def test_module_entry_point_runs_as_a_script(tmp_path):
+    done = subprocess.run([sys.executable, "-m", "shardtrain_b200.train", "--help"], cwd=ROOT,
+                          capture_output=True, text=True, timeout=120)
+    assert done.returncode == 0 and "--smoke-groups" in done.stdout
+
+
+@pytest.mark.distributed
+def test_smoke_groups_on_four_gloo_ranks(tmp_path):
+    out = tmp_path / "smoke"
+    code, log = run_workers("shardtrain_b200.train", 4,
+                            ["--config", CONFIGS / "smoke_gloo.yaml", "--smoke-groups",
+                             "--debug.output_dir", out])
+    assert code == 0, log[-3000:]
+    for rank in range(4):
+        result = json.loads((out / f"smoke.rank{rank}.json").read_text())
+        assert set(result) >= {"tp", "fsdp"}
+    assert not list(Path(out).glob("steps.rank*.json"))
+
+
+@pytest.mark.distributed
+def test_qwen_benchmark_two_ranks_fsdp(tmp_path):
+    out = tmp_path / "bench"
+    code, log = run_workers("shardtrain_b200.training.qwen2_benchmark", 2,
+                            ["--config", CONFIGS / "qwen25_tiny.yaml", "--warmup", "1",
+                             "--parallel.fsdp_degree", "2", "--training.steps", "2",
+                             "--runtime.forward_prefetch", "true", "--runtime.backward_prefetch",
+                             "true", "--runtime.async_grad_rs", "true", "--debug.output_dir", out])
+    assert code == 0, log[-3000:]
+    records = [json.loads((out / f"benchmark.rank{r}.json").read_text()) for r in range(2)]
+    assert all(r["status"] == "completed" and r["global_batch"] == 4 for r in records)
+    assert records[0]["steps"][0]["max_rank_seconds"] == records[1]["steps"][0]["max_rank_seconds"]
+    assert records[0]["steps"][1]["loss"] == pytest.approx(records[1]["steps"][1]["loss"])
