@@ -21,12 +21,23 @@ struct GemmCall {
   bool accumulate;
   float alpha;
   int force_bn;  // 0 = heuristic, else 128 or 256
+  // Optional sequence scatter of an fp32 result (see GemmEpilogue): row b*seq + s is written to
+  // scatter_out[s / seq_local] at row b*seq_local + s % seq_local; `out` is then unused.
+  float* scatter_out[8];
+  int scatter_degree;  // 0 or 1: plain output
+  int scatter_seq;
+  int scatter_seq_local;
 };
 cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream);
 
 // ------------------------------------------------------------------ elementwise (elementwise.cu)
 cudaError_t launch_rmsnorm_fwd(const float* x, const float* w, void* y, float* inv, int rows,
                                int cols, float eps, bool y_fp32, cudaStream_t s);
+// sum_out = residual (optional) + sum of n_slots fp32 [rows, cols] slots spaced slot_stride
+// elements apart; with w: y = bf16 rmsnorm(sum_out) * w and inv = per-row inverse RMS.
+cudaError_t launch_slot_sum_rmsnorm(const float* slots, int n_slots, int64_t slot_stride,
+                                    const float* residual, float* sum_out, const float* w, void* y,
+                                    float* inv, int rows, int cols, float eps, cudaStream_t s);
 // dx_out = dres_in (optional) + rmsnorm backward of dy ; dw_partial [blocks, cols]
 cudaError_t launch_rmsnorm_bwd(const float* dy, const float* x, const float* w, const float* inv,
                                const float* dres_in, float* dx_out, float* dw_partial,
@@ -74,7 +85,7 @@ struct SegmentDesc {
   int64_t numel;      // TP-local numel
   int64_t full_off;   // element offset inside the unit's full buffers
   int32_t keep_fp32;  // materialise as fp32 into the small fp32 buffer instead of bf16
-  int32_t pad;
+  int32_t pad;        // reduce-scatter only: non-zero marks a TP-replicated parameter
 };
 constexpr int kMaxPeers = 8;
 struct PeerPtrs {
@@ -88,12 +99,20 @@ struct PeerPtrsMut {
 cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc* segs, int n_segs,
                                  void* full_bf16, float* full_fp32, int64_t total_full,
                                  cudaStream_t s);
+// Tensor-parallel axis of a gradient reduction.  With degree > 1 the pointer table lists the
+// whole mesh (index f * degree + t); segments whose `pad` field is non-zero are TP-replicated
+// parameters, summed over every rank of the mesh and scaled by replicated_scale.
+struct TpAxis {
+  int degree = 1;
+  int rank = 0;
+  float replicated_scale = 1.f;
+};
 // Reduce-scatter fused with the fp32 accumulate into the persistent gradient shard: rank r pulls
 // its slice of every peer's full fp32 gradient, sums, scales and adds (or stores).
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        int* flags, cudaStream_t s);
+                                        int* flags, cudaStream_t s, TpAxis tp = TpAxis{});
 // Same, and applies AdamW to the owned shard in the same pass (last micro-step only).
 // `flags` (optional, int[2]) receives the gradient check of what was written: [0] non-finite
 // value, [1] non-zero shard padding.
@@ -101,7 +120,7 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
-                                        cudaStream_t s);
+                                        cudaStream_t s, TpAxis tp = TpAxis{});
 // Embedding lookup straight from the (possibly remote) fp32 shards: no all-gather of the table.
 cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t q,
                                             const int64_t* ids, float* out, int rows, int cols,

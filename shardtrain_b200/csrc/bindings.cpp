@@ -98,6 +98,70 @@ void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor inv, double 
         "rmsnorm_fwd");
 }
 
+// Row-parallel GEMM whose fp32 result rows are scattered along the sequence into per-owner
+// buffers (peer pointers allowed): row b*seq + s -> dest_ptrs[s / seq_local][b*seq_local + s %
+// seq_local, :].  `cols` is the row pitch of every destination (= N).
+void gemm_scatter(const Tensor& a, const Tensor& b, c10::ArrayRef<int64_t> dest_ptrs, int64_t seq,
+                  bool a_mn, bool b_mn, int64_t force_bn) {
+  need(a, at::kBFloat16, "a");
+  need(b, at::kBFloat16, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1,
+              "gemm operands must be 2-D with a contiguous inner dimension");
+  TORCH_CHECK(dest_ptrs.size() >= 2 && dest_ptrs.size() <= 8, "2..8 scatter destinations expected");
+  const c10::cuda::CUDAGuard guard(a.device());
+  stb::GemmCall c{};
+  c.M = static_cast<int>(a_mn ? a.size(1) : a.size(0));
+  c.K = static_cast<int>(a_mn ? a.size(0) : a.size(1));
+  c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == c.K, "gemm reduction sizes differ");
+  c.a = a.data_ptr();
+  c.b = b.data_ptr();
+  c.lda = a.stride(0);
+  c.ldb = b.stride(0);
+  c.ldo = c.N;
+  c.a_mn = a_mn;
+  c.b_mn = b_mn;
+  c.out_fp32 = true;
+  c.alpha = 1.f;
+  c.force_bn = static_cast<int>(force_bn);
+  c.scatter_degree = static_cast<int>(dest_ptrs.size());
+  c.scatter_seq = static_cast<int>(seq);
+  c.scatter_seq_local = static_cast<int>(seq / static_cast<int64_t>(dest_ptrs.size()));
+  for (size_t i = 0; i < dest_ptrs.size(); ++i)
+    c.scatter_out[i] = reinterpret_cast<float*>(dest_ptrs[i]);
+  c.out = c.scatter_out[0];
+  check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm_scatter");
+}
+
+void slot_sum_rmsnorm(const Tensor& slots, const c10::optional<Tensor>& residual, Tensor sum_out,
+                      const c10::optional<Tensor>& w, const c10::optional<Tensor>& y,
+                      const c10::optional<Tensor>& inv, double eps) {
+  need(slots, at::kFloat, "slots");
+  need(sum_out, at::kFloat, "sum_out");
+  TORCH_CHECK(slots.dim() == 3 && slots.is_contiguous() && sum_out.is_contiguous() &&
+                  sum_out.numel() == slots.size(1) * slots.size(2),
+              "slots must be [n, rows, cols] and sum_out [rows, cols]");
+  const int rows = static_cast<int>(slots.size(1)), cols = static_cast<int>(slots.size(2));
+  if (residual.has_value()) {
+    need(*residual, at::kFloat, "residual");
+    TORCH_CHECK(residual->is_contiguous() && residual->numel() == sum_out.numel());
+  }
+  if (w.has_value()) {
+    need(*w, at::kFloat, "w");
+    TORCH_CHECK(y.has_value() && inv.has_value() && y->scalar_type() == at::kBFloat16 &&
+                y->is_contiguous() && y->numel() == sum_out.numel() && inv->numel() == rows &&
+                w->numel() == cols);
+    need(*inv, at::kFloat, "inv");
+  }
+  check(stb::launch_slot_sum_rmsnorm(
+            slots.data_ptr<float>(), static_cast<int>(slots.size(0)), slots.stride(0),
+            residual.has_value() ? residual->data_ptr<float>() : nullptr, sum_out.data_ptr<float>(),
+            w.has_value() ? w->data_ptr<float>() : nullptr, w.has_value() ? y->data_ptr() : nullptr,
+            w.has_value() ? inv->data_ptr<float>() : nullptr, rows, cols, static_cast<float>(eps),
+            cur_stream()),
+        "slot_sum_rmsnorm");
+}
+
 void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& inv,
                  const c10::optional<Tensor>& dres, Tensor dx, Tensor dw_partial) {
   need(dy, at::kFloat, "dy");
@@ -296,8 +360,9 @@ std::vector<stb::SegmentDesc> read_segs(const Tensor& segs) {
     out[i].q = p[5 * i + 1];
     out[i].numel = p[5 * i + 2];
     out[i].full_off = p[5 * i + 3];
-    out[i].keep_fp32 = static_cast<int32_t>(p[5 * i + 4]);
-    out[i].pad = 0;
+    // column 4: bit 0 = keep fp32 (gather tables), bit 1 = TP-replicated (reduce tables)
+    out[i].keep_fp32 = static_cast<int32_t>(p[5 * i + 4] & 1);
+    out[i].pad = static_cast<int32_t>((p[5 * i + 4] >> 1) & 1);
   }
   return out;
 }
@@ -330,18 +395,31 @@ int* flags_ptr(const c10::optional<Tensor>& flags) {
   return flags->data_ptr<int>();
 }
 
+stb::TpAxis tp_axis(c10::ArrayRef<int64_t> full_ptrs, int64_t tp_degree, int64_t tp_rank,
+                    double rep_scale) {
+  TORCH_CHECK(tp_degree >= 1 && full_ptrs.size() % tp_degree == 0,
+              "the pointer table must list fsdp_degree * tp_degree slots");
+  stb::TpAxis tp;
+  tp.degree = static_cast<int>(tp_degree);
+  tp.rank = static_cast<int>(tp_rank);
+  tp.replicated_scale = static_cast<float>(rep_scale);
+  return tp;
+}
+
 void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor& segs,
                     Tensor grad_shard, double scale, bool accumulate,
-                    const c10::optional<Tensor>& flags) {
+                    const c10::optional<Tensor>& flags, int64_t tp_degree, int64_t tp_rank,
+                    double rep_scale) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
+  const auto tp = tp_axis(full_ptrs, tp_degree, tp_rank, rep_scale);
   for (size_t i = 0; i < table.size(); i += 32) {
     const int n = static_cast<int>(std::min<size_t>(32, table.size() - i));
-    check(stb::launch_reduce_scatter_grads(pp, static_cast<int>(full_ptrs.size()),
+    check(stb::launch_reduce_scatter_grads(pp, static_cast<int>(full_ptrs.size() / tp_degree),
                                            static_cast<int>(rank), table.data() + i, n,
                                            grad_shard.data_ptr<float>(), grad_shard.numel(),
                                            static_cast<float>(scale), accumulate, flags_ptr(flags),
-                                           cur_stream()),
+                                           cur_stream(), tp),
           "reduce_scatter");
   }
 }
@@ -350,16 +428,19 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
                           Tensor grad_shard, Tensor p, Tensor m, Tensor v, double scale,
                           bool accumulate, double lr, double b1, double b2, double eps, double wd,
                           double bc1, double bc2, double gscale,
-                          const c10::optional<Tensor>& flags) {
+                          const c10::optional<Tensor>& flags, int64_t tp_degree, int64_t tp_rank,
+                          double rep_scale) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
+  const auto tp = tp_axis(full_ptrs, tp_degree, tp_rank, rep_scale);
   for (size_t i = 0; i < table.size(); i += 32) {
     const int n = static_cast<int>(std::min<size_t>(32, table.size() - i));
     check(stb::launch_reduce_scatter_adamw(
-              pp, static_cast<int>(full_ptrs.size()), static_cast<int>(rank), table.data() + i, n,
-              grad_shard.data_ptr<float>(), p.data_ptr<float>(), m.data_ptr<float>(),
-              v.data_ptr<float>(), grad_shard.numel(), static_cast<float>(scale), accumulate,
-              adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream()),
+              pp, static_cast<int>(full_ptrs.size() / tp_degree), static_cast<int>(rank),
+              table.data() + i, n, grad_shard.data_ptr<float>(), p.data_ptr<float>(),
+              m.data_ptr<float>(), v.data_ptr<float>(), grad_shard.numel(),
+              static_cast<float>(scale), accumulate,
+              adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream(), tp),
           "reduce_scatter_adamw");
   }
 }
@@ -491,6 +572,8 @@ TORCH_LIBRARY(stb, m) {
   m.def("status_reset", &status_reset);
   m.def("status_tensor", &status_tensor_op);
   m.def("gemm", &gemm);
+  m.def("gemm_scatter", &gemm_scatter);
+  m.def("slot_sum_rmsnorm", &slot_sum_rmsnorm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("colsum_f32", &colsum_f32);
@@ -508,8 +591,14 @@ TORCH_LIBRARY(stb, m) {
   m.def("sgd", &sgd);
   m.def("grad_check", &grad_check);
   m.def("gather_params", &gather_params);
-  m.def("reduce_scatter", &reduce_scatter);
-  m.def("reduce_scatter_adamw", &reduce_scatter_adamw);
+  m.def("reduce_scatter(int[] full_ptrs, int rank, Tensor segs, Tensor grad_shard, float scale, "
+        "bool accumulate, Tensor? flags, int tp_degree=1, int tp_rank=0, float rep_scale=1.0) -> ()",
+        &reduce_scatter);
+  m.def("reduce_scatter_adamw(int[] full_ptrs, int rank, Tensor segs, Tensor grad_shard, Tensor p, "
+        "Tensor m, Tensor v, float scale, bool accumulate, float lr, float b1, float b2, float eps, "
+        "float wd, float bc1, float bc2, float gscale, Tensor? flags, int tp_degree=1, "
+        "int tp_rank=0, float rep_scale=1.0) -> ()",
+        &reduce_scatter_adamw);
   m.def("embedding_gather_sharded", &embedding_gather_sharded);
   m.def("seq_gather", &seq_gather);
   m.def("seq_reduce_scatter", &seq_reduce_scatter);

@@ -87,6 +87,43 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
+// Tail of a sequence reduce-scatter whose partial sums were pushed into `n_slots` receive slots
+// (slot k at slots + k * slot_stride): sum_out = residual + sum_k slot_k, and, when a norm weight
+// is given, y = bf16(rmsnorm(sum_out) * w) with the row's inverse RMS.  One CTA per row.
+__global__ void slot_sum_rmsnorm_kernel(const float* __restrict__ slots, int n_slots,
+                                        int64_t slot_stride, const float* __restrict__ residual,
+                                        float* __restrict__ sum_out, const float* __restrict__ w,
+                                        __nv_bfloat16* __restrict__ y, float* __restrict__ inv_out,
+                                        int cols, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int64_t off = row * cols;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
+    float4 acc = residual ? *reinterpret_cast<const float4*>(residual + off + c)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < n_slots; ++k) {
+      const float4 t = *reinterpret_cast<const float4*>(slots + k * slot_stride + off + c);
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    *reinterpret_cast<float4*>(sum_out + off + c) = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  if (w == nullptr) return;
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / cols + eps);
+  if (threadIdx.x == 0) inv_out[row] = inv;
+  for (int c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
+    // each thread re-reads exactly the elements it wrote above
+    const float4 v = *reinterpret_cast<const float4*>(sum_out + off + c);
+    const float4 g = *reinterpret_cast<const float4*>(w + c);
+    uint2 pk;
+    pk.x = pack2(v.x * inv * g.x, v.y * inv * g.y);
+    pk.y = pack2(v.z * inv * g.z, v.w * inv * g.w);
+    *reinterpret_cast<uint2*>(y + off + c) = pk;
+  }
+}
+
 // dx = inv * (g*w - x * inv^2 * mean(g*w*x)) (+ incoming residual gradient);
 // d(weight) partial per CTA = sum over its rows of g * (x*inv).  Rows are strided over CTAs.
 __global__ void rmsnorm_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x,
@@ -458,6 +495,18 @@ cudaError_t launch_rmsnorm_fwd(const float* x, const float* w, void* y, float* i
     rmsnorm_fwd_kernel<true><<<rows, threads, 0, s>>>(x, w, y, inv, cols, eps);
   else
     rmsnorm_fwd_kernel<false><<<rows, threads, 0, s>>>(x, w, y, inv, cols, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_slot_sum_rmsnorm(const float* slots, int n_slots, int64_t slot_stride,
+                                    const float* residual, float* sum_out, const float* w, void* y,
+                                    float* inv, int rows, int cols, float eps, cudaStream_t s) {
+  if (cols % 4 || n_slots < 1 || slot_stride % 4 || (w != nullptr && (y == nullptr || inv == nullptr)))
+    return cudaErrorInvalidValue;
+  const int threads = cols >= 1024 ? 256 : 128;
+  slot_sum_rmsnorm_kernel<<<rows, threads, 0, s>>>(slots, n_slots, slot_stride, residual, sum_out, w,
+                                                   reinterpret_cast<__nv_bfloat16*>(y), inv, cols,
+                                                   eps);
   return cudaGetLastError();
 }
 

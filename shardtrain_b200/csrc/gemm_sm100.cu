@@ -70,6 +70,10 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   ep.out_fp32 = c.out_fp32 ? 1 : 0;
   ep.accumulate = c.accumulate ? 1 : 0;
   ep.alpha = c.alpha;
+  ep.scatter_degree = c.scatter_degree > 1 ? c.scatter_degree : 0;
+  ep.scatter_seq = c.scatter_seq;
+  ep.scatter_seq_local = c.scatter_seq_local;
+  for (int i = 0; i < 8; ++i) ep.scatter_out[i] = i < ep.scatter_degree ? c.scatter_out[i] : nullptr;
 
   auto kernel = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
   constexpr int smem = GemmSmem<BN>::kTotal;
@@ -111,6 +115,16 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
     return cudaErrorInvalidValue;
   if (c.residual != nullptr && !aligned16(c.residual)) return cudaErrorInvalidValue;
   if (c.accumulate && !c.out_fp32) return cudaErrorInvalidValue;
+  if (c.scatter_degree > 1) {
+    // the scatter epilogue writes fp32 rows; every destination must be 16-byte aligned and the
+    // sequence must split evenly over the owners
+    if (!c.out_fp32 || c.accumulate || c.residual != nullptr || c.scatter_degree > 8 ||
+        c.scatter_seq_local <= 0 || c.scatter_seq != c.scatter_seq_local * c.scatter_degree ||
+        c.M % c.scatter_seq)
+      return cudaErrorInvalidValue;
+    for (int i = 0; i < c.scatter_degree; ++i)
+      if (c.scatter_out[i] == nullptr || !aligned16(c.scatter_out[i])) return cudaErrorInvalidValue;
+  }
   int bn = c.force_bn;
   if (bn == 0) {
     const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;

@@ -24,6 +24,15 @@ struct GemmEpilogue {
   int out_fp32;           // 1: fp32 output, 0: bf16 output
   int accumulate;         // 1: out += result (fp32 output only)
   float alpha;            // result scale applied before bias/residual
+  // Sequence scatter (row-parallel GEMM -> reduce-scatter along the sequence): when
+  // scatter_degree > 1 the fp32 result row m = b * scatter_seq + s goes to the buffer of the rank
+  // that owns sequence position s, scatter_out[s / scatter_seq_local], at row
+  // b * scatter_seq_local + s % scatter_seq_local.  The buffers may be peer memory: the partial
+  // sums cross NVLink tile by tile from this epilogue, while later tiles are still in the MMAs.
+  float* scatter_out[8];
+  int scatter_degree;
+  int scatter_seq;
+  int scatter_seq_local;
 };
 
 constexpr int kGemmBM = 128;
@@ -217,6 +226,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         if (ep.out_fp32) {
           float* o = reinterpret_cast<float*>(ep.out) + g_row * ep.ldo + col0;
+          if (ep.scatter_degree > 1) {
+            const int64_t b = g_row / ep.scatter_seq;
+            const int pos = static_cast<int>(g_row - b * ep.scatter_seq);
+            const int owner = pos / ep.scatter_seq_local;
+            o = ep.scatter_out[owner] +
+                (b * ep.scatter_seq_local + (pos - owner * ep.scatter_seq_local)) * ep.ldo + col0;
+          }
           const float* rs = ep.residual ? reinterpret_cast<const float*>(ep.residual) +
                                               g_row * ep.ldo + col0
                                         : nullptr;

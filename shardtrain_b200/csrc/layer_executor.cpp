@@ -45,7 +45,61 @@ struct Gemm {
     c.residual = residual ? residual->data_ptr() : nullptr;
     ok(stb::launch_gemm_bf16(c, status, stream), "gemm");
   }
+  // fp32 result rows scattered along the sequence into the owners' receive slots (peer memory)
+  void scatter(const Tensor& a, const Tensor& b, bool b_mn, c10::ArrayRef<int64_t> dest, int seq) const {
+    stb::GemmCall c{};
+    c.M = static_cast<int>(a.size(0));
+    c.K = static_cast<int>(a.size(1));
+    c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+    c.a = a.data_ptr();
+    c.b = b.data_ptr();
+    c.lda = a.stride(0);
+    c.ldb = b.stride(0);
+    c.ldo = c.N;
+    c.b_mn = b_mn;
+    c.out_fp32 = true;
+    c.alpha = 1.f;
+    c.scatter_degree = static_cast<int>(dest.size());
+    c.scatter_seq = seq;
+    c.scatter_seq_local = seq / static_cast<int>(dest.size());
+    for (size_t i = 0; i < dest.size(); ++i) c.scatter_out[i] = reinterpret_cast<float*>(dest[i]);
+    c.out = c.scatter_out[0];
+    ok(stb::launch_gemm_bf16(c, status, stream), "gemm scatter");
+  }
 };
+
+// Sequence-parallel plumbing of one layer call: the TP group's flag pads for the in-stream
+// barrier, and the epoch counter the caller advances by the number of barriers used.
+struct SpLink {
+  cudaStream_t stream;
+  int* status;
+  std::vector<uint32_t*> pads;
+  int rank;
+  uint32_t epoch;
+  int slot;
+  uint32_t max_spin;
+  void barrier() {
+    ++epoch;
+    ok(stb::launch_peer_barrier(pads.data(), static_cast<int>(pads.size()), rank, epoch, slot, status,
+                                max_spin, stream), "sp barrier");
+  }
+  // out[b, r*sl + s, :] = peer r's [b, s, :]
+  void gather(c10::ArrayRef<int64_t> src, Tensor& out, int64_t B, int64_t seq_local) const {
+    std::vector<const void*> p(src.size());
+    for (size_t i = 0; i < src.size(); ++i) p[i] = reinterpret_cast<const void*>(src[i]);
+    ok(stb::launch_seq_gather(p.data(), static_cast<int>(p.size()), out.data_ptr(),
+                              static_cast<int>(B), static_cast<int>(seq_local),
+                              out.size(1) * out.element_size(), stream), "seq gather");
+  }
+};
+
+SpLink make_link(cudaStream_t st, int* status, c10::ArrayRef<int64_t> pads, int64_t rank,
+                 int64_t epoch, int64_t slot, int64_t max_spin) {
+  SpLink l{st, status, {}, static_cast<int>(rank), static_cast<uint32_t>(epoch),
+           static_cast<int>(slot), static_cast<uint32_t>(max_spin)};
+  for (int64_t p : pads) l.pads.push_back(reinterpret_cast<uint32_t*>(p));
+  return l;
+}
 
 // x2 [M,H] fp32 -> {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out}
 std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const Tensor& b_qkv,
@@ -163,9 +217,177 @@ Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1,
   return dx;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor + sequence parallel layer.  The residual stream is sequence sharded ([B, S/T, H] per TP
+// rank); column-parallel GEMMs consume a sequence all-gather of the normalised activations (one
+// gather feeds q|k|v, one feeds gate|up -- src/sharded_runtime/runtime/qwen2_operators.py:253-265),
+// row-parallel GEMMs scatter their fp32 partial sums from the epilogue straight into the owning
+// rank's receive slots over NVLink, and the next kernel adds the T slots (+ residual, + RMSNorm).
+// h1 / h2 / bf16 output gradients live in peer-visible buffers so the peers' gathers (and the
+// backward's re-gathers) read them in place.
+//
+// x2 [B*S/T, H] fp32 -> {inv1, qkv, attn, lse, x_mid, inv2, gu, out}; uses 4 barrier epochs.
+std::vector<Tensor> layer_forward_sp(
+    const Tensor& x2, const Tensor& w_qkv, const Tensor& b_qkv, const Tensor& w_o,
+    const Tensor& w_gu, const Tensor& w_down, const Tensor& ln1, const Tensor& ln2,
+    const Tensor& cos, const Tensor& sin, const c10::optional<Tensor>& positions,
+    const c10::optional<Tensor>& mask, Tensor status, int64_t B, int64_t S, int64_t hq,
+    int64_t hkv, double eps, Tensor h1_local, Tensor h2_local, c10::ArrayRef<int64_t> h1_ptrs,
+    c10::ArrayRef<int64_t> h2_ptrs, c10::ArrayRef<int64_t> push_ptrs, Tensor recv,
+    c10::ArrayRef<int64_t> flag_ptrs, int64_t tp_rank, int64_t epoch, int64_t flag_slot,
+    int64_t max_spin) {
+  const int64_t T = static_cast<int64_t>(h1_ptrs.size());
+  const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
+  const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
+  TORCH_CHECK(S % T == 0 && x2.size(0) == Ml && recv.dim() == 3 && recv.size(0) == T &&
+                  recv.size(1) == Ml && recv.size(2) == H && recv.is_contiguous(),
+              "sequence-parallel layer: shapes do not match the TP degree");
+  auto bf = x2.options().dtype(at::kBFloat16);
+  auto f32 = x2.options().dtype(at::kFloat);
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  Gemm g{st, status.data_ptr<int>()};
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
+  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const float feps = static_cast<float>(eps);
+
+  Tensor inv1 = at::empty({Ml}, f32);
+  ok(stb::launch_rmsnorm_fwd(x2.data_ptr<float>(), ln1.data_ptr<float>(), h1_local.data_ptr(),
+                             inv1.data_ptr<float>(), Ml, H, feps, false, st), "rmsnorm");
+  sp.barrier();                                   // every rank's h1 slice is written
+  Tensor h_full = at::empty({M, H}, bf);
+  sp.gather(h1_ptrs, h_full, B, Sl);
+  Tensor qkv = at::empty({M, W}, bf);
+  g.run(h_full, w_qkv, qkv, false, false, b_qkv.data_ptr<float>(), nullptr);
+  ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
+                      hkv, D, false, st), "rope");
+  Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
+  stb::AttnCall ac{qkv.data_ptr(), attn.data_ptr(), lse.data_ptr<float>(), km, static_cast<int>(B),
+                   static_cast<int>(S), static_cast<int>(hq), static_cast<int>(hkv),
+                   static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)))};
+  ok(stb::launch_attention_fwd(ac, g.status, st), "attention_fwd");
+  g.scatter(attn, w_o, false, push_ptrs, static_cast<int>(S));
+  sp.barrier();                                   // every rank's partial rows have landed
+  Tensor x_mid = at::empty({Ml, H}, f32), inv2 = at::empty({Ml}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv.data_ptr<float>(), T, recv.stride(0), x2.data_ptr<float>(),
+                                  x_mid.data_ptr<float>(), ln2.data_ptr<float>(),
+                                  h2_local.data_ptr(), inv2.data_ptr<float>(), Ml, H, feps, st),
+     "slot sum + rmsnorm");
+  sp.barrier();                                   // h2 slices written, receive slots consumed
+  sp.gather(h2_ptrs, h_full, B, Sl);
+  Tensor gu = at::empty({M, 2 * inter}, bf);
+  g.run(h_full, w_gu, gu, false, false, nullptr, nullptr);
+  Tensor hm = at::empty({M, inter}, bf);
+  ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu");
+  g.scatter(hm, w_down, false, push_ptrs, static_cast<int>(S));
+  sp.barrier();
+  Tensor out = at::empty({Ml, H}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv.data_ptr<float>(), T, recv.stride(0),
+                                  x_mid.data_ptr<float>(), out.data_ptr<float>(), nullptr, nullptr,
+                                  nullptr, Ml, H, feps, st), "slot sum");
+  return {inv1, qkv, attn, lse, x_mid, inv2, gu, out};
+}
+
+// Backward of the layer above; uses 4 barrier epochs.  d_out / d_mid travel as bf16 through the
+// peer-visible buffers dob_local / dmb_local; dX partial sums of the column-parallel GEMMs are
+// scattered in fp32.
+Tensor layer_backward_sp(
+    const Tensor& d_out, const Tensor& x2, const Tensor& inv1, const Tensor& qkv,
+    const Tensor& attn, const Tensor& lse, const Tensor& x_mid, const Tensor& inv2,
+    const Tensor& gu, const Tensor& w_qkv, const Tensor& w_o, const Tensor& w_gu,
+    const Tensor& w_down, const Tensor& ln1, const Tensor& ln2, Tensor g_down, Tensor g_gate_up,
+    Tensor g_ln2, Tensor g_o, Tensor g_bias, Tensor g_qkv, Tensor g_ln1, const Tensor& cos,
+    const Tensor& sin, const c10::optional<Tensor>& positions, const c10::optional<Tensor>& mask,
+    Tensor status, int64_t B, int64_t S, int64_t hq, int64_t hkv, Tensor dob_local,
+    Tensor dmb_local, c10::ArrayRef<int64_t> h1_ptrs, c10::ArrayRef<int64_t> h2_ptrs,
+    c10::ArrayRef<int64_t> dob_ptrs, c10::ArrayRef<int64_t> dmb_ptrs,
+    c10::ArrayRef<int64_t> push_ptrs, Tensor recv, c10::ArrayRef<int64_t> flag_ptrs,
+    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t max_spin) {
+  const int64_t T = static_cast<int64_t>(h1_ptrs.size());
+  const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
+  const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
+  auto bf = x2.options().dtype(at::kBFloat16);
+  auto f32 = x2.options().dtype(at::kFloat);
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  Gemm g{st, status.data_ptr<int>()};
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
+  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  constexpr int kPartial = 592;
+
+  ok(stb::launch_cast_f32_to_bf16(d_out.data_ptr<float>(), dob_local.data_ptr(), Ml * H, st), "cast");
+  sp.barrier();
+  Tensor d_full = at::empty({M, H}, bf), h_full = at::empty({M, H}, bf);
+  sp.gather(dob_ptrs, d_full, B, Sl);
+  Tensor hm = at::empty({M, inter}, bf);
+  ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu recompute");
+  g.run(d_full, hm, g_down, true, true, nullptr, nullptr);                  // dW down
+  Tensor d_hm = at::empty({M, inter}, bf);
+  g.run(d_full, w_down, d_hm, false, true, nullptr, nullptr);               // dX down (local cols)
+  Tensor d_gu = at::empty({M, 2 * inter}, bf);
+  ok(stb::launch_swiglu_bwd(d_hm.data_ptr(), gu.data_ptr(), d_gu.data_ptr(), M, inter, st), "swiglu_bwd");
+  sp.gather(h2_ptrs, h_full, B, Sl);                                        // re-gather h2
+  g.run(d_gu, h_full, g_gate_up, true, true, nullptr, nullptr);             // dW gate|up
+  g.scatter(d_gu, w_gu, true, push_ptrs, static_cast<int>(S));              // dX gate|up partial
+  sp.barrier();
+  Tensor d_h2 = at::empty({Ml, H}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv.data_ptr<float>(), T, recv.stride(0), nullptr,
+                                  d_h2.data_ptr<float>(), nullptr, nullptr, nullptr, Ml, H, 0.f, st),
+     "slot sum");
+  Tensor d_mid = at::empty({Ml, H}, f32), partial = at::empty({kPartial, H}, f32);
+  ok(stb::launch_rmsnorm_bwd(d_h2.data_ptr<float>(), x_mid.data_ptr<float>(), ln2.data_ptr<float>(),
+                             inv2.data_ptr<float>(), d_out.data_ptr<float>(), d_mid.data_ptr<float>(),
+                             partial.data_ptr<float>(), kPartial, Ml, H, st), "rmsnorm_bwd");
+  ok(stb::launch_colsum_f32(partial.data_ptr<float>(), g_ln2.data_ptr<float>(), kPartial, H, false, st), "colsum");
+
+  ok(stb::launch_cast_f32_to_bf16(d_mid.data_ptr<float>(), dmb_local.data_ptr(), Ml * H, st), "cast");
+  sp.barrier();
+  sp.gather(dmb_ptrs, d_full, B, Sl);
+  g.run(d_full, attn, g_o, true, true, nullptr, nullptr);                   // dW o
+  Tensor d_attn = at::empty({M, hq * D}, bf);
+  g.run(d_full, w_o, d_attn, false, true, nullptr, nullptr);                // dX o (local heads)
+  Tensor d_qkv = at::empty({M, W}, bf), delta = at::empty({B, hq, S}, f32);
+  stb::AttnBwdCall bc{};
+  bc.qkv = qkv.data_ptr();
+  bc.out = attn.data_ptr();
+  bc.dout = d_attn.data_ptr();
+  bc.lse = lse.data_ptr<float>();
+  bc.delta = delta.data_ptr<float>();
+  bc.dqkv = d_qkv.data_ptr();
+  bc.dkv_accum = nullptr;
+  bc.key_mask = km;
+  bc.batch = static_cast<int>(B);
+  bc.seq = static_cast<int>(S);
+  bc.hq = static_cast<int>(hq);
+  bc.hkv = static_cast<int>(hkv);
+  bc.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)));
+  ok(stb::launch_attention_bwd(bc, g.status, st), "attention_bwd");
+  ok(stb::launch_rope(d_qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
+                      hkv, D, true, st), "rope inverse");
+  Tensor bias_partial = at::empty({64, W}, f32);
+  ok(stb::launch_colsum_bf16(d_qkv.data_ptr(), W, g_bias.data_ptr<float>(), M, W, false,
+                             bias_partial.data_ptr<float>(), 64, st), "bias colsum");
+  sp.gather(h1_ptrs, h_full, B, Sl);                                        // re-gather h1
+  g.run(d_qkv, h_full, g_qkv, true, true, nullptr, nullptr);                // dW q|k|v
+  g.scatter(d_qkv, w_qkv, true, push_ptrs, static_cast<int>(S));            // dX q|k|v partial
+  sp.barrier();
+  Tensor d_h1 = at::empty({Ml, H}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv.data_ptr<float>(), T, recv.stride(0), nullptr,
+                                  d_h1.data_ptr<float>(), nullptr, nullptr, nullptr, Ml, H, 0.f, st),
+     "slot sum");
+  Tensor dx = at::empty({Ml, H}, f32);
+  ok(stb::launch_rmsnorm_bwd(d_h1.data_ptr<float>(), x2.data_ptr<float>(), ln1.data_ptr<float>(),
+                             inv1.data_ptr<float>(), d_mid.data_ptr<float>(), dx.data_ptr<float>(),
+                             partial.data_ptr<float>(), kPartial, Ml, H, st), "rmsnorm_bwd");
+  ok(stb::launch_colsum_f32(partial.data_ptr<float>(), g_ln1.data_ptr<float>(), kPartial, H, false, st), "colsum");
+  return dx;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(stb, m) {
   m.def("layer_forward", &layer_forward);
   m.def("layer_backward", &layer_backward);
+  m.def("layer_forward_sp", &layer_forward_sp);
+  m.def("layer_backward_sp", &layer_backward_sp);
 }

@@ -101,12 +101,26 @@ __global__ void gather_params_kernel(PeerPtrs shards, int degree, SegTable tab,
 }
 
 // Rank `rank` owns elements [rank*q, rank*q + q) of each segment (zero beyond numel).
+// With a tensor-parallel axis (tp > 1) `full` lists the gradient slots of the whole mesh in rank
+// order (index f * tp + t).  A TP-split parameter is summed over the F ranks of this rank's TP
+// coordinate; a TP-replicated one (segment flag `pad`) over all F * tp ranks, scaled by
+// rep_scale -- the T-way sum that the reference issues as a separate all-reduce after its
+// reduce-scatter (src/sharded_runtime/runtime/materializer.py:228-233).
 template <bool ADAMW>
-__global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTable tab,
-                                      float* __restrict__ gshard, float* __restrict__ p,
-                                      float* __restrict__ m, float* __restrict__ v, float scale,
+__global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int tp, int tp_rank,
+                                      SegTable tab, float* __restrict__ gshard,
+                                      float* __restrict__ p, float* __restrict__ m,
+                                      float* __restrict__ v, float split_scale, float rep_scale,
                                       int accumulate, AdamWArgs a, int* __restrict__ flags) {
   const SegmentDesc sg = tab.s[blockIdx.y];
+  const bool replicated = tp > 1 && sg.pad != 0;
+  const int n_src = replicated ? degree * tp : degree;
+  // replicated segments use one fixed summation order so every TP replica computes bit-identical
+  // shard gradients (and updates); split segments rotate the order to spread the load
+  const int first = replicated ? 0 : rank;
+  const int stride = replicated ? 1 : tp;
+  const int offset = replicated ? 0 : tp_rank;
+  const float scale = replicated ? rep_scale : split_scale;
   const int64_t lo = static_cast<int64_t>(rank) * sg.q;
   const int64_t valid = max(static_cast<int64_t>(0), min(sg.q, sg.numel - lo));
   const bool vec = (sg.q % 4 == 0) && (sg.shard_off % 4 == 0) && (sg.full_off % 4 == 0);
@@ -124,8 +138,8 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
       const int cnt = vec ? 4 : 1;
       if (vec && i + 3 < valid) {
         // rotate the peer order by rank so the ranks do not all hit one peer at once
-        for (int d = 0; d < degree; ++d) {
-          const int src = (rank + d) % degree;
+        for (int d = 0; d < n_src; ++d) {
+          const int src = ((first + d) % n_src) * stride + offset;
           const float4 t =
               *reinterpret_cast<const float4*>(full.p[src] + sg.full_off + lo + i);
           acc[0] += t.x; acc[1] += t.y; acc[2] += t.z; acc[3] += t.w;
@@ -133,8 +147,8 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, SegTa
       } else {
         for (int j = 0; j < cnt; ++j) {
           if (i + j < valid) {
-            for (int d = 0; d < degree; ++d) {
-              const int src = (rank + d) % degree;
+            for (int d = 0; d < n_src; ++d) {
+              const int src = ((first + d) % n_src) * stride + offset;
               acc[j] += full.p[src][sg.full_off + lo + i + j];
             }
           }
@@ -319,19 +333,23 @@ cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc*
   return cudaGetLastError();
 }
 
+bool valid_mesh(int degree, int rank, TpAxis tp) {
+  return degree >= 1 && tp.degree >= 1 && degree * tp.degree <= kMaxPeers && rank >= 0 &&
+         rank < degree && tp.rank >= 0 && tp.rank < tp.degree;
+}
+
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        int* flags, cudaStream_t s) {
+                                        int* flags, cudaStream_t s, TpAxis tp) {
   (void)shard_total;
   SegTable tab;
-  if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree ||
-      !fill_table(&tab, segs, n_segs))
+  if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
     return cudaErrorInvalidValue;
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
-  reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(full_grads, degree, rank, tab, grad_shard,
-                                                    nullptr, nullptr, nullptr, scale,
-                                                    accumulate ? 1 : 0, AdamWArgs{}, flags);
+  reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(
+      full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, nullptr, nullptr, nullptr,
+      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags);
   return cudaGetLastError();
 }
 
@@ -339,15 +357,15 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
-                                        cudaStream_t s) {
+                                        cudaStream_t s, TpAxis tp) {
   (void)shard_total;
   SegTable tab;
-  if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree ||
-      !fill_table(&tab, segs, n_segs))
+  if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
     return cudaErrorInvalidValue;
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
-  reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(full_grads, degree, rank, tab, grad_shard, p, m,
-                                                   v, scale, accumulate ? 1 : 0, a, flags);
+  reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(
+      full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, p, m, v, scale,
+      tp.replicated_scale, accumulate ? 1 : 0, a, flags);
   return cudaGetLastError();
 }
 

@@ -381,8 +381,9 @@ class ShardedRuntime:
         opt = self.optimizer
         return bool(self.last_microstep and opt is not None
                     and getattr(opt, "fuse_into_reduction", False)
-                    and all(h.spec.tp_grad_reduce == "none" or self.tp.degree == 1
-                            for h in unit.handles))
+                    # the sm_100a reduction sums TP-replicated gradients over the mesh itself
+                    and (self.fused is not None or self.tp.degree == 1
+                         or all(h.spec.tp_grad_reduce == "none" for h in unit.handles)))
 
     def fused_optimizer_args(self):
         return self.optimizer.kernel_args()

@@ -24,9 +24,11 @@ import torch
 from torch.autograd.function import once_differentiable
 
 from shardtrain_b200 import ops as ops_module
-from shardtrain_b200.distributed.peer import PeerMemory
+from shardtrain_b200.distributed.peer import CHANNEL_SLOTS, PeerMemory
 from shardtrain_b200.runtime.layout import segment_table
 from shardtrain_b200.runtime.materializer import PeerMaterializer
+
+SP_FLAG_SLOT = CHANNEL_SLOTS["sp_ag"]    # barrier flag slot of the in-stream SP barriers
 
 _LAYER_ORDER = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
                 "gate_proj.weight", "up_proj.weight", "down_proj.weight",
@@ -115,7 +117,7 @@ def build_plan(unit) -> UnitPlan:
     plan.bf16_numel, plan.fp32_numel, plan.grad_numel = bf16_cursor, fp32_cursor, grad_cursor
     handles = [by_name[n] for n in ordered]
     plan.gather_table = segment_table(handles, plan.param_offsets, plan.fp32_names)
-    plan.reduce_table = segment_table(handles, plan.grad_offsets, set())
+    plan.reduce_table = segment_table(handles, plan.grad_offsets, set(), mark_replicated=True)
     return plan
 
 
@@ -175,7 +177,19 @@ class FusedExecutor:
         self.ops = ops_module.load()
         self.status = self.ops.status_tensor()
         self.peer = PeerMemory(mesh.fsdp_group if mesh else None, runtime.device, self.ops)
-        self.tp_peer = None
+        # With a TP axis: activations travel inside the TP group, gradient slots are visible to
+        # the whole mesh (TP-replicated parameters are summed over all of it).
+        self.tp_degree, self.tp_rank = runtime.tp.degree, runtime.tp.rank
+        if self.tp_degree > 1:
+            import torch.distributed as dist
+
+            self.tp_peer = PeerMemory(mesh.tp_group, runtime.device, self.ops)
+            self.reduce_peer = PeerMemory(dist.group.WORLD, runtime.device, self.ops)
+            if self.reduce_peer.degree != self.peer.degree * self.tp_degree:
+                raise ValueError("The mesh must cover the whole world (F * T ranks)")
+        else:
+            self.tp_peer, self.reduce_peer = None, self.peer
+        self._sp_buffers = {}
         self.exp_avg = self.exp_avg_sq = None
         self._shards_dirty = True
         self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
@@ -187,10 +201,10 @@ class FusedExecutor:
     # ------------------------------------------------------------------ allocation
     def allocate(self):
         rt = self.runtime
-        if rt.tp.degree > 1:
+        if rt.tp.degree > 1 and not rt.sp:
             raise NotImplementedError(
-                "The sm_100a executor currently covers FSDP-only meshes; use "
-                "communication_backend=nccl for TP/SP")
+                "The sm_100a executor covers FSDP-only and FSDP x TP/SP meshes; tensor "
+                "parallelism without sequence parallelism runs with communication_backend=nccl")
         portable = rt.materializer
         mat = PeerMaterializer(portable.group, rt.comm, self.peer)
         total = rt.plan.padded_total()
@@ -219,7 +233,7 @@ class FusedExecutor:
             if len(unit.handles) > 64:
                 raise ValueError("A unit may hold at most 64 parameters")
             plan.tokens = tuple(token_pool[base + i: base + i + 1] for i in range(len(unit.handles)))
-        self.ring = GradRing(self.peer, self.ops, _up(largest, 4), count=4)
+        self.ring = GradRing(self.reduce_peer, self.ops, _up(largest, 4), count=4)
         mat.bind(self.ops, self)
         ranges = rt.padding_ranges or [(0, 0)]
         self._pad_ranges = torch.tensor(ranges, dtype=torch.int64, device=rt.device).reshape(-1)
@@ -298,6 +312,41 @@ class FusedExecutor:
             )
         return views
 
+    def sp_buffers(self, batch, seq, layers):
+        """Peer-visible activation buffers of the sequence-parallel layers for one input shape:
+        per layer the bf16 h1 / h2 slices (read in place by the peers' gathers and by the
+        backward's re-gathers), two bf16 gradient slices, and T fp32 receive slots the row GEMMs'
+        epilogues scatter into.  Allocation is collective over the TP group (same order on every
+        member), happens once per shape and is never freed before shutdown."""
+        key = (batch, seq)
+        buf = self._sp_buffers.get(key)
+        if buf is None:
+            T, H, tp = self.tp_degree, self.cfg.hidden_size, self.tp_peer
+            rows = batch * (seq // T)
+            act_bytes, slot_bytes = rows * H * 2, rows * H * 4
+            acts = tp.alloc(layers * 2 * act_bytes)
+            grads = tp.alloc(2 * act_bytes)
+            recv = tp.alloc(T * slot_bytes)
+            bf = torch.bfloat16
+
+            def act(layer, which):
+                off = (layer * 2 + which) * act_bytes
+                return (acts.tensor(self.ops, rows * H, bf, off).view(rows, H),
+                        [p + off for p in acts.ptrs])
+
+            buf = dict(
+                h=[(act(i, 0), act(i, 1)) for i in range(layers)],
+                dob=(grads.tensor(self.ops, rows * H, bf, 0).view(rows, H), list(grads.ptrs)),
+                dmb=(grads.tensor(self.ops, rows * H, bf, act_bytes).view(rows, H),
+                     [p + act_bytes for p in grads.ptrs]),
+                recv=recv.tensor(self.ops, T * rows * H, torch.float32).view(T, rows, H),
+                # where this rank's partial rows for owner p go: p's slot number tp_rank
+                push=[p + self.tp_rank * slot_bytes for p in recv.ptrs],
+                flags=list(tp.flags.ptrs),
+            )
+            self._sp_buffers[key] = buf
+        return buf
+
     def launch_grad_check(self):
         self.ops.grad_check(self.grad, self._pad_ranges, self._flags)
 
@@ -315,18 +364,35 @@ class FusedExecutor:
         return t
 
     def rotary(self, position_ids, default_positions):
-        """cos/sin tables [S, D/2] (FP32) and, for caller-supplied positions, an int32 position
-        per (batch, token) row; `None` means positions 0..S-1."""
+        """cos/sin tables (FP32, [rows, D/2]) for the RoPE kernel and an optional int32 row index
+        per (batch, token).  Default positions 0..S-1 and a caller-supplied [1, S] row share one
+        table of S rows indexed by `token % S`; per-sample positions [B, S] get a table of B*S rows
+        indexed by the token's row.  Tables of caller-supplied positions are cached on the
+        tensor's identity and version, so a batch that repeats them pays once."""
         seq = position_ids.shape[-1]
-        if seq not in self._rope_cache:
-            pos = torch.arange(seq, device=self.runtime.device, dtype=torch.float32)
-            angle = pos[:, None] * self.runtime.inv_freq[None, :].float()
-            self._rope_cache[seq] = (angle.cos().contiguous(), angle.sin().contiguous())
-        cos, sin = self._rope_cache[seq]
-        positions = None
-        if not default_positions:
-            raise NotImplementedError("custom position_ids need a table covering their range")
-        return cos, sin, positions, seq
+        inv_freq = self.runtime.inv_freq.float()
+        if default_positions:
+            key = ("default", seq)
+            if key not in self._rope_cache:
+                pos = torch.arange(seq, device=self.runtime.device, dtype=torch.float32)
+                angle = pos[:, None] * inv_freq[None, :]
+                self._rope_cache[key] = (angle.cos().contiguous(), angle.sin().contiguous(), None)
+        else:
+            key = (position_ids.data_ptr(), position_ids._version, tuple(position_ids.shape))
+            if key not in self._rope_cache:
+                for stale in [k for k in self._rope_cache if k[0] != "default"][8:]:
+                    del self._rope_cache[stale]
+                pos = position_ids.to(self.runtime.device, torch.float32).reshape(-1)
+                angle = pos[:, None] * inv_freq[None, :]
+                rows = None
+                if position_ids.shape[0] != 1:
+                    rows = torch.arange(pos.numel(), device=self.runtime.device, dtype=torch.int32)
+                # the entry keeps `position_ids` alive, so its address cannot be handed to another
+                # tensor while the key exists
+                self._rope_cache[key] = (angle.cos().contiguous(), angle.sin().contiguous(), rows,
+                                         position_ids)
+        cos, sin, rows = self._rope_cache[key][:3]
+        return cos, sin, rows, seq
 
     # ------------------------------------------------------------------ unit math
     def embedding(self, unit, ids):
@@ -507,12 +573,28 @@ class FusedLayerFn(torch.autograd.Function):
         w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2 = (
             w["w_qkv"], w["b_qkv"], w["w_o"], w["w_gu"], w["w_down"], w["ln1"], w["ln2"])
         unit.prefetch_after_input(unit.forward_prefetch_handle, "FWD")
+        ctx.ex, ctx.unit, ctx.index, ctx.tables, ctx.mask = ex, unit, index, tables, mask
+        if ex.tp_degree > 1:
+            # sequence parallel: x is this rank's [B, S/T, H] slice of the residual stream
+            T, tp = ex.tp_degree, ex.tp_peer
+            S_full = S * T
+            buf = ex.sp_buffers(B, S_full, cfg.num_hidden_layers)
+            (h1, h1_ptrs), (h2, h2_ptrs) = buf["h"][index]
+            epoch = tp.epochs["sp_ag"]
+            inv1, qkv, attn, lse, x_mid, inv2, gu, out = ops.layer_forward_sp(
+                x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
+                ex.status, B, S_full, hq, hkv, cfg.rms_norm_eps, h1, h2, h1_ptrs, h2_ptrs,
+                buf["push"], buf["recv"], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
+                tp.max_spin)
+            tp.epochs["sp_ag"] = epoch + 4
+            ctx.dims = (B, S_full, H, inter)
+            ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu)
+            return out.view(B, S, H)
         # the 11 launches of the forward run from C++ (csrc/layer_executor.cpp)
         h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out = ops.layer_forward(
             x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask, ex.status,
             B, S, hq, hkv, cfg.rms_norm_eps)
 
-        ctx.ex, ctx.unit, ctx.index, ctx.tables, ctx.mask = ex, unit, index, tables, mask
         ctx.dims = (B, S, H, inter)
         ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu)
         return out.view(B, S, H)
@@ -525,6 +607,8 @@ class FusedLayerFn(torch.autograd.Function):
         plan = ex.runtime.materializer.plans[unit.unit_id]
         unit.annotate("BWD")
         unit.weight(plan.names[0])  # state / generation check of the backward materialisation
+        if ex.tp_degree > 1:
+            return FusedLayerFn._backward_sp(ctx, dout, plan)
         x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu = ctx.saved_tensors
         B, S, H, inter = ctx.dims
         M, D, hq, hkv = B * S, 128, ex.hq, ex.hkv
@@ -544,3 +628,30 @@ class FusedLayerFn(torch.autograd.Function):
             ln2, gv["down"], gv["gate_up"], gv["ln2"], gv["o"], gv["bias"], gv["qkv"], gv["ln1"], cos,
             sin, positions, ctx.mask, ex.status, B, S, hq, hkv)
         return (dx.view(B, S, H), None, None, None, None, None, *([ex.token_grad] * len(plan.names)))
+
+    @staticmethod
+    def _backward_sp(ctx, dout, plan):
+        ex, unit, index = ctx.ex, ctx.unit, ctx.index
+        ops, tp = ex.ops, ex.tp_peer
+        x2, inv1, qkv, attn, lse, x_mid, inv2, gu = ctx.saved_tensors
+        B, S_full, H, inter = ctx.dims
+        cos, sin, positions, _ = ctx.tables
+        w = ex.layer_operands(plan, index)
+        slot = ex.acquire_grad_slot(unit)
+        gv = ex.layer_gradients(plan, slot, index)
+        unit.prefetch_after_input(unit.backward_prefetch_handle, "BWD")
+        buf = ex.sp_buffers(B, S_full, ex.cfg.num_hidden_layers)
+        (_, h1_ptrs), (_, h2_ptrs) = buf["h"][index]
+        (dob, dob_ptrs), (dmb, dmb_ptrs) = buf["dob"], buf["dmb"]
+        rows = x2.shape[0]
+        d_out = dout.reshape(rows, H).contiguous()
+        epoch = tp.epochs["sp_ag"]
+        dx = ops.layer_backward_sp(
+            d_out, x2, inv1, qkv, attn, lse, x_mid, inv2, gu, w["w_qkv"], w["w_o"], w["w_gu"],
+            w["w_down"], w["ln1"], w["ln2"], gv["down"], gv["gate_up"], gv["ln2"], gv["o"],
+            gv["bias"], gv["qkv"], gv["ln1"], cos, sin, positions, ctx.mask, ex.status, B, S_full,
+            ex.hq, ex.hkv, dob, dmb, h1_ptrs, h2_ptrs, dob_ptrs, dmb_ptrs, buf["push"], buf["recv"],
+            buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT, tp.max_spin)
+        tp.epochs["sp_ag"] = epoch + 4
+        return (dx.view(B, S_full // ex.tp_degree, H), None, None, None, None, None,
+                *([ex.token_grad] * len(plan.names)))

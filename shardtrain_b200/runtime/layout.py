@@ -165,12 +165,15 @@ def padding_ranges(handles: Sequence[ShardedParameter], rank: int) -> list[tuple
 
 
 def segment_table(handles: Sequence[ShardedParameter], full_offsets: dict[str, int],
-                  keep_fp32: set[str]) -> Tensor:
-    """CPU int64 [n, 5] rows (shard_off, q, numel, full_off, keep_fp32) for the gather and
-    reduce-scatter kernels; offsets are in elements from the arena / full-buffer base."""
+                  keep_fp32: set[str], *, mark_replicated: bool = False) -> Tensor:
+    """CPU int64 [n, 5] rows (shard_off, q, numel, full_off, flags) for the gather and
+    reduce-scatter kernels; offsets are in elements from the arena / full-buffer base.  Flag bit 0:
+    keep FP32 when materialising; bit 1 (reduce tables, `mark_replicated`): the parameter is
+    replicated over the TP axis, so its gradient is summed over the whole mesh."""
     rows = [
         [h.arena_offset, h.spec.fsdp_shard_numel, h.spec.numel, full_offsets[h.spec.param_id],
-         1 if h.spec.param_id in keep_fp32 else 0]
+         (1 if h.spec.param_id in keep_fp32 else 0)
+         | (2 if mark_replicated and h.spec.tp_grad_reduce == "sum" else 0)]
         for h in handles
     ]
     return torch.tensor(rows, dtype=torch.int64).reshape(len(rows), 5)

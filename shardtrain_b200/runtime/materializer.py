@@ -323,18 +323,21 @@ class PeerMaterializer:
         fuse_adamw = runtime.fused_optimizer_armed(unit)
         arenas = self.arenas
 
+        # TP axis of the reduction: the slot table lists the whole mesh; TP-replicated
+        # parameters are summed over it (each TP rank saw its own sequence slice)
+        tp = (arenas.tp_degree, arenas.tp_rank, 1.0 / self.degree)
+
         def launch():
-            if self.degree > 1:
-                self.peer.barrier("fsdp_rs")
+            arenas.reduce_peer.barrier("fsdp_rs")     # no-op for a single member
             if fuse_adamw:
                 hp = runtime.fused_optimizer_args()
                 self.ops.reduce_scatter_adamw(
                     slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad, arenas.param,
                     arenas.exp_avg, arenas.exp_avg_sq, 1.0 / self.degree, not first, *hp,
-                    arenas.check_flags)
+                    arenas.check_flags, *tp)
             else:
                 self.ops.reduce_scatter(slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad,
-                                        1.0 / self.degree, not first, arenas.check_flags)
+                                        1.0 / self.degree, not first, arenas.check_flags, *tp)
 
         comm = self.comm
         ticket = comm.issue_kernel(

@@ -159,10 +159,10 @@ def _choose_executor(runtime):
     want = runtime.communication_backend
     if runtime.device.type != "cuda" or want == "nccl":
         return "portable"
-    if runtime.tp.degree > 1:
+    if runtime.tp.degree > 1 and not runtime.sp:
         if want == "peer":
-            raise NotImplementedError("The sm_100a executor covers FSDP-only meshes; TP/SP meshes "
-                                      "run with communication_backend=nccl")
+            raise NotImplementedError("The sm_100a executor covers FSDP-only and TP+SP meshes; "
+                                      "TP without SP runs with communication_backend=nccl")
         return "portable"
     if not ops.available():
         raise RuntimeError("CUDA device requested but torch.cuda is unavailable")

@@ -67,3 +67,26 @@ def test_adamw_training_reduces_loss_and_fuses_the_update(retain):
     per_micro = 2 * 2 + 2
     gathers = kinds.count("fsdp_ag_cast")
     assert gathers == (6 * 2 * per_micro if not retain else 6 * (2 + 2))
+
+
+def test_caller_supplied_position_ids_match_default_positions():
+    """Explicit positions 0..S-1, as one shared row and per sample, give the loss of the default;
+    stretched positions change it."""
+    from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+    from shardtrain_b200.runtime.engine import ShardedRuntime
+    from shardtrain_b200.training.qwen2_trainer import QwenTrainer
+
+    torch.manual_seed(3)
+    cfg = Qwen2ModelConfig(vocab_size=512, hidden_size=256, intermediate_size=512,
+                           num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1)
+    model = Qwen2CausalLM(cfg)
+    rt = ShardedRuntime(device="cuda").register(model)
+    trainer = QwenTrainer(model, rt, lr=0.0, dtype="bf16", optimizer="sgd")
+    ids = torch.randint(0, 512, (2, 128), device="cuda")
+    base = trainer.train_step(ids).loss
+    row = torch.arange(128, device="cuda").unsqueeze(0)
+    assert trainer.train_step(ids, position_ids=row).loss == pytest.approx(base, rel=1e-6)
+    assert trainer.train_step(ids, position_ids=row.expand(2, -1).contiguous()).loss == \
+        pytest.approx(base, rel=1e-6)
+    # a constant shift would not do: rotary attention depends on position differences only
+    assert abs(trainer.train_step(ids, position_ids=row * 3).loss - base) > 1e-4

@@ -264,3 +264,76 @@ def test_bounded_peer_wait_reports_instead_of_hanging(ops):
         module.check_status("test")
     assert ops.status_read() == 0
     assert torch.ones(4, device=DEV).sum().item() == 4
+
+
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gemm_scatter_epilogue_routes_rows_to_their_sequence_owner(ops, b_mn):
+    """Row-parallel GEMM -> sequence reduce-scatter: the epilogue writes row b*S + s into the
+    buffer of owner s // (S/T) at row b*(S/T) + s % (S/T).  The owners' buffers are emulated by
+    local tensors (plain stores, nothing waits on a peer)."""
+    B, S, T, N, K = 3, 256, 2, 512, 384
+    a = torch.randn(B * S, K, device=DEV).bfloat16()
+    w = (torch.randn(K, N, device=DEV) if b_mn else torch.randn(N, K, device=DEV)).bfloat16()
+    dest = [torch.full((B * S // T, N), float("nan"), device=DEV) for _ in range(T)]
+    ops.gemm_scatter(a, w, [d.data_ptr() for d in dest], S, False, b_mn, 0)
+    want = a.float() @ (w.float() if b_mn else w.float().t())
+    want = want.view(B, T, S // T, N)
+    for t in range(T):
+        torch.testing.assert_close(dest[t].view(B, S // T, N), want[:, t], atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_slot_sum_rmsnorm(ops, with_norm):
+    rows, cols, T = 300, 1536, 3
+    slots = torch.randn(T, rows, cols, device=DEV)
+    residual = torch.randn(rows, cols, device=DEV)
+    out = torch.empty(rows, cols, device=DEV)
+    if with_norm:
+        w = torch.randn(cols, device=DEV)
+        y = torch.empty(rows, cols, device=DEV, dtype=torch.bfloat16)
+        inv = torch.empty(rows, device=DEV)
+        ops.slot_sum_rmsnorm(slots, residual, out, w, y, inv, 1e-6)
+    else:
+        ops.slot_sum_rmsnorm(slots, None, out, None, None, None, 0.0)
+    want = slots.sum(0) + (residual if with_norm else 0)
+    torch.testing.assert_close(out, want, atol=1e-5, rtol=1e-5)
+    if with_norm:
+        r = torch.rsqrt(want.pow(2).mean(-1) + 1e-6)
+        torch.testing.assert_close(inv, r, atol=1e-5, rtol=1e-5)
+        assert rel(y, want * r[:, None] * w) < 5e-3
+
+
+def test_reduce_scatter_sums_replicated_segments_over_the_whole_mesh(ops):
+    """F=2 x T=2 mesh emulated on one GPU: a TP-split parameter is reduced over the two ranks
+    of its TP coordinate, a TP-replicated one (table flag 2) over all four, with its own scale;
+    both TP replicas must end with bit-identical replicated shards."""
+    F, T = 2, 2
+    numels, replicated = [4096 * 3, 1000], [False, True]
+    segs, shard_off, full_off = [], 0, 0
+    for n, rep in zip(numels, replicated):
+        q = -(-n // F)
+        segs.append([shard_off, q, n, full_off, 2 if rep else 0])
+        shard_off += -(-q // 4) * 4
+        full_off += -(-n // 4) * 4
+    table = torch.tensor(segs, dtype=torch.int64)
+    slots = [torch.randn(full_off, device=DEV) for _ in range(F * T)]     # index f * T + t
+    ptrs = [s.data_ptr() for s in slots]
+    results = {}
+    for f in range(F):
+        for t in range(T):
+            gs = torch.zeros(shard_off, device=DEV)
+            flags = torch.zeros(2, device=DEV, dtype=torch.int32)
+            ops.reduce_scatter(ptrs, f, table, gs, 1.0 / F, False, flags, T, t, 0.25)
+            results[f, t] = gs
+            assert flags.tolist() == [0, 0]
+            for (so, q, n, fo, flag) in segs:
+                keep = max(0, min(q, n - f * q))
+                piece = slice(fo + f * q, fo + f * q + keep)
+                if flag:
+                    want = 0.25 * sum(s[piece] for s in slots)
+                else:
+                    want = sum(slots[g * T + t][piece] for g in range(F)) / F
+                torch.testing.assert_close(gs[so:so + keep], want, atol=1e-6, rtol=1e-6)
+    so, q = segs[1][0], segs[1][1]
+    for f in range(F):
+        assert torch.equal(results[f, 0][so:so + q], results[f, 1][so:so + q])

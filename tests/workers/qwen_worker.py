@@ -29,7 +29,7 @@ def main():
     ap.add_argument("--tied", type=int, default=1)
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--mismatch", type=int, default=0)
-    ap.add_argument("--shape", default="tiny", choices=["tiny", "d128"])
+    ap.add_argument("--shape", default="tiny", choices=["tiny", "d128", "d128tp"])
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--optimizer", default="adamw")
     ap.add_argument("--backend", default="auto")
@@ -48,11 +48,15 @@ def main():
             cfg = Qwen2ModelConfig(vocab_size=2048, hidden_size=256, intermediate_size=512,
                                    num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
                                    tie_word_embeddings=bool(a.tied))
+        elif a.shape == "d128tp":   # head_dim 128 with 2 KV heads: divisible by TP 2
+            cfg = Qwen2ModelConfig(vocab_size=2048, hidden_size=512, intermediate_size=512,
+                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                   tie_word_embeddings=bool(a.tied))
         else:
             cfg = Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128,
                                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                                    tie_word_embeddings=bool(a.tied))
-        vocab, seq = cfg.vocab_size, (256 if a.shape == "d128" else 64)
+        vocab, seq = cfg.vocab_size, (256 if a.shape.startswith("d128") else 64)
         torch.manual_seed(7 + (worker.rank if a.mismatch else 0))
         dense = Qwen2CausalLM(cfg)
         import copy
