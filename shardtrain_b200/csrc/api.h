@@ -95,10 +95,12 @@ struct PeerPtrsMut {
   float* p[kMaxPeers];
 };
 // All-gather fused with the fp32 -> bf16 cast: every rank pulls the peers' fp32 shards over
-// NVLink with plain loads and lands the compute-dtype full parameters locally.
+// NVLink with plain loads and lands the compute-dtype full parameters locally.  With `shadows`
+// (one bf16 arena per peer, same element offsets as the fp32 shard arena, kept current by the
+// optimizer kernels) the bf16 segments are pulled from there instead: half the bytes on the wire.
 cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc* segs, int n_segs,
                                  void* full_bf16, float* full_fp32, int64_t total_full,
-                                 cudaStream_t s);
+                                 cudaStream_t s, const void* const* shadows = nullptr);
 // Tensor-parallel axis of a gradient reduction.  With degree > 1 the pointer table lists the
 // whole mesh (index f * degree + t); segments whose `pad` field is non-zero are TP-replicated
 // parameters, summed over every rank of the mesh and scaled by replicated_scale.
@@ -120,7 +122,8 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
-                                        cudaStream_t s, TpAxis tp = TpAxis{});
+                                        cudaStream_t s, TpAxis tp = TpAxis{},
+                                        void* shadow = nullptr);   // bf16 copy of p, same offsets
 // Embedding lookup straight from the (possibly remote) fp32 shards: no all-gather of the table.
 cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t q,
                                             const int64_t* ids, float* out, int rows, int cols,

@@ -376,14 +376,22 @@ stb::PeerPtrs peer_ptrs(c10::ArrayRef<int64_t> ptrs) {
 
 // A unit may hold more parameters than one launch's table; split into launches of <= 32.
 void gather_params(c10::ArrayRef<int64_t> shard_ptrs, const Tensor& segs, Tensor full_bf16,
-                   Tensor full_fp32) {
+                   Tensor full_fp32, c10::ArrayRef<int64_t> shadow_ptrs) {
+  need(full_bf16, at::kBFloat16, "full_bf16");
+  need(full_fp32, at::kFloat, "full_fp32");
+  TORCH_CHECK(shadow_ptrs.empty() || shadow_ptrs.size() == shard_ptrs.size(),
+              "one shadow arena per shard arena expected");
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(shard_ptrs);
+  std::vector<const void*> shadows(shadow_ptrs.size());
+  for (size_t i = 0; i < shadow_ptrs.size(); ++i)
+    shadows[i] = reinterpret_cast<const void*>(shadow_ptrs[i]);
   for (size_t i = 0; i < table.size(); i += 32) {
     const int n = static_cast<int>(std::min<size_t>(32, table.size() - i));
     check(stb::launch_gather_params(pp, static_cast<int>(shard_ptrs.size()), table.data() + i, n,
                                     full_bf16.data_ptr(), full_fp32.data_ptr<float>(),
-                                    full_bf16.numel(), cur_stream()),
+                                    full_bf16.numel(), cur_stream(),
+                                    shadows.empty() ? nullptr : shadows.data()),
           "gather_params");
   }
 }
@@ -429,10 +437,16 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
                           bool accumulate, double lr, double b1, double b2, double eps, double wd,
                           double bc1, double bc2, double gscale,
                           const c10::optional<Tensor>& flags, int64_t tp_degree, int64_t tp_rank,
-                          double rep_scale) {
+                          double rep_scale, const c10::optional<Tensor>& shadow) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
   const auto tp = tp_axis(full_ptrs, tp_degree, tp_rank, rep_scale);
+  void* shadow_ptr = nullptr;
+  if (shadow.has_value()) {
+    need(*shadow, at::kBFloat16, "shadow");
+    TORCH_CHECK(shadow->numel() == p.numel(), "shadow must mirror the parameter arena");
+    shadow_ptr = shadow->data_ptr();
+  }
   for (size_t i = 0; i < table.size(); i += 32) {
     const int n = static_cast<int>(std::min<size_t>(32, table.size() - i));
     check(stb::launch_reduce_scatter_adamw(
@@ -440,7 +454,8 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
               table.data() + i, n, grad_shard.data_ptr<float>(), p.data_ptr<float>(),
               m.data_ptr<float>(), v.data_ptr<float>(), grad_shard.numel(),
               static_cast<float>(scale), accumulate,
-              adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream(), tp),
+              adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream(), tp,
+              shadow_ptr),
           "reduce_scatter_adamw");
   }
 }
@@ -590,14 +605,16 @@ TORCH_LIBRARY(stb, m) {
   m.def("adamw", &adamw);
   m.def("sgd", &sgd);
   m.def("grad_check", &grad_check);
-  m.def("gather_params", &gather_params);
+  m.def("gather_params(int[] shard_ptrs, Tensor segs, Tensor full_bf16, Tensor full_fp32, "
+        "int[] shadow_ptrs=[]) -> ()",
+        &gather_params);
   m.def("reduce_scatter(int[] full_ptrs, int rank, Tensor segs, Tensor grad_shard, float scale, "
         "bool accumulate, Tensor? flags, int tp_degree=1, int tp_rank=0, float rep_scale=1.0) -> ()",
         &reduce_scatter);
   m.def("reduce_scatter_adamw(int[] full_ptrs, int rank, Tensor segs, Tensor grad_shard, Tensor p, "
         "Tensor m, Tensor v, float scale, bool accumulate, float lr, float b1, float b2, float eps, "
         "float wd, float bc1, float bc2, float gscale, Tensor? flags, int tp_degree=1, "
-        "int tp_rank=0, float rep_scale=1.0) -> ()",
+        "int tp_rank=0, float rep_scale=1.0, Tensor? shadow=None) -> ()",
         &reduce_scatter_adamw);
   m.def("embedding_gather_sharded", &embedding_gather_sharded);
   m.def("seq_gather", &seq_gather);

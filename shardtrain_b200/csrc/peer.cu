@@ -33,10 +33,63 @@ __device__ __forceinline__ uint32_t pk2(float a, float b) {
 // Work is tiled in chunks of kChunk elements of one segment; blockIdx.y = segment.
 constexpr int kChunk = 4096;
 
-__global__ void gather_params_kernel(PeerPtrs shards, int degree, SegTable tab,
-                                     __nv_bfloat16* __restrict__ full_bf16,
+struct ShadowPtrs {
+  const __nv_bfloat16* p[kMaxPeers];
+};
+
+// bf16 -> bf16 gather of one segment from the owners' compute-dtype shadow shards: the cast
+// already happened where the optimizer wrote the parameter, so only 2 bytes per element cross
+// NVLink instead of 4 (rounding before or after the transfer gives the same bits).
+constexpr int kChunkB = 8192;
+__device__ __forceinline__ void gather_shadow_segment(const ShadowPtrs& sh, const SegmentDesc& sg,
+                                                      __nv_bfloat16* __restrict__ full_bf16) {
+  const bool vec = (sg.q % 8 == 0) && (sg.shard_off % 8 == 0) && (sg.full_off % 8 == 0);
+  for (int64_t chunk = blockIdx.x; chunk * kChunkB < sg.numel; chunk += gridDim.x) {
+    const int64_t base = chunk * kChunkB;
+    if (vec && base + kChunkB <= sg.numel && blockDim.x * 8 * 4 == kChunkB) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + (u * blockDim.x + threadIdx.x) * 8;
+        const int r = static_cast<int>(i / sg.q);
+        v[u] = *reinterpret_cast<const uint4*>(sh.p[r] + sg.shard_off + (i - r * sg.q));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + (u * blockDim.x + threadIdx.x) * 8;
+        *reinterpret_cast<uint4*>(full_bf16 + sg.full_off + i) = v[u];
+      }
+    } else {
+      const int64_t end = min(base + kChunkB, sg.numel);
+      if (vec) {
+        for (int64_t i = base + threadIdx.x * 8; i < end; i += blockDim.x * 8) {
+          const int r = static_cast<int>(i / sg.q);
+          const __nv_bfloat16* src = sh.p[r] + sg.shard_off + (i - r * sg.q);
+          if (i + 7 < sg.numel) {
+            *reinterpret_cast<uint4*>(full_bf16 + sg.full_off + i) =
+                *reinterpret_cast<const uint4*>(src);
+          } else {
+            for (int64_t j = i; j < sg.numel; ++j) full_bf16[sg.full_off + j] = src[j - i];
+          }
+        }
+      } else {
+        for (int64_t i = base + threadIdx.x; i < end; i += blockDim.x) {
+          const int r = static_cast<int>(i / sg.q);
+          full_bf16[sg.full_off + i] = sh.p[r][sg.shard_off + (i - r * sg.q)];
+        }
+      }
+    }
+  }
+}
+
+__global__ void gather_params_kernel(PeerPtrs shards, ShadowPtrs shadows, int use_shadow, int degree,
+                                     SegTable tab, __nv_bfloat16* __restrict__ full_bf16,
                                      float* __restrict__ full_fp32) {
   const SegmentDesc sg = tab.s[blockIdx.y];
+  if (use_shadow && !sg.keep_fp32) {
+    gather_shadow_segment(shadows, sg, full_bf16);
+    return;
+  }
   const bool vec = (sg.q % 4 == 0) && (sg.shard_off % 4 == 0) && (sg.full_off % 4 == 0);
   for (int64_t chunk = blockIdx.x; chunk * kChunk < sg.numel; chunk += gridDim.x) {
     const int64_t base = chunk * kChunk;
@@ -111,7 +164,8 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int t
                                       SegTable tab, float* __restrict__ gshard,
                                       float* __restrict__ p, float* __restrict__ m,
                                       float* __restrict__ v, float split_scale, float rep_scale,
-                                      int accumulate, AdamWArgs a, int* __restrict__ flags) {
+                                      int accumulate, AdamWArgs a, int* __restrict__ flags,
+                                      __nv_bfloat16* __restrict__ shadow) {
   const SegmentDesc sg = tab.s[blockIdx.y];
   const bool replicated = tp > 1 && sg.pad != 0;
   const int n_src = replicated ? degree * tp : degree;
@@ -183,6 +237,12 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int t
             pp[j] -= step_size * mp[j] / (sqrtf(vp[j]) * inv_bc2_sqrt + a.eps);
           }
           *reinterpret_cast<float4*>(p + e) = pv;   // padding has p = g = m = v = 0 and stays 0
+          if (shadow != nullptr) {                   // compute-dtype copy for the next gather
+            uint2 pk;
+            pk.x = pk2(pv.x, pv.y);
+            pk.y = pk2(pv.z, pv.w);
+            *reinterpret_cast<uint2*>(shadow + e) = pk;
+          }
           *reinterpret_cast<float4*>(m + e) = mv;
           *reinterpret_cast<float4*>(v + e) = vv;
         }
@@ -202,6 +262,7 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int t
           p[e] = pj;
           m[e] = mj;
           v[e] = vj;
+          if (shadow != nullptr) shadow[e] = __float2bfloat16(pj);
         }
       }
     }
@@ -322,13 +383,20 @@ int chunks_for(const SegmentDesc* segs, int n, bool per_shard) {
 
 cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc* segs, int n_segs,
                                  void* full_bf16, float* full_fp32, int64_t total_full,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, const void* const* shadows) {
   (void)total_full;
   SegTable tab;
   if (degree < 1 || degree > kMaxPeers || !fill_table(&tab, segs, n_segs))
     return cudaErrorInvalidValue;
+  ShadowPtrs sh{};
+  if (shadows != nullptr)
+    for (int i = 0; i < degree; ++i) {
+      if (shadows[i] == nullptr || (reinterpret_cast<uintptr_t>(shadows[i]) & 15))
+        return cudaErrorInvalidValue;
+      sh.p[i] = reinterpret_cast<const __nv_bfloat16*>(shadows[i]);
+    }
   dim3 grid(chunks_for(segs, n_segs, false), n_segs);
-  gather_params_kernel<<<grid, 256, 0, s>>>(shards, degree, tab,
+  gather_params_kernel<<<grid, 256, 0, s>>>(shards, sh, shadows != nullptr ? 1 : 0, degree, tab,
                                             reinterpret_cast<__nv_bfloat16*>(full_bf16), full_fp32);
   return cudaGetLastError();
 }
@@ -349,7 +417,7 @@ cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int ran
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, nullptr, nullptr, nullptr,
-      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags);
+      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags, nullptr);
   return cudaGetLastError();
 }
 
@@ -357,7 +425,7 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
-                                        cudaStream_t s, TpAxis tp) {
+                                        cudaStream_t s, TpAxis tp, void* shadow) {
   (void)shard_total;
   SegTable tab;
   if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
@@ -365,7 +433,8 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, p, m, v, scale,
-      tp.replicated_scale, accumulate ? 1 : 0, a, flags);
+      tp.replicated_scale, accumulate ? 1 : 0, a, flags,
+      reinterpret_cast<__nv_bfloat16*>(shadow));
   return cudaGetLastError();
 }
 

@@ -397,7 +397,9 @@ class ShardedRuntime:
             event.record(torch.cuda.current_stream(self.device))
             self.parameter_shards_ready_event = event
             if self.fused is not None:
-                self.fused.shards_written()
+                current = source == "optimizer_update" and getattr(
+                    self.optimizer, "shadow_current", False)
+                self.fused.shards_written(shadow_current=current)
         self.comm.event("parameter_shards_ready", source=source,
                         parameter_version=self.parameter_shards_version)
 

@@ -221,6 +221,14 @@ class FusedExecutor:
         rt.allocate_arenas(allocator=make)
         self.param, self.grad = rt.param_arena, rt.grad_arena
         self.param_peer_ptrs = list(self._param_buffer.ptrs)
+        # compute-dtype shadow of the shard arena (same element offsets): written by the fused
+        # AdamW kernel next to the FP32 master, read by the peers' gather kernels
+        self._shadow_buffer = self.peer.alloc(total * 2)
+        self.shadow = (self._shadow_buffer.tensor(self.ops, total, torch.bfloat16)
+                       if self.peer.degree > 1
+                       else self._shadow_buffer.owner.view(torch.bfloat16)[:total])
+        self.shadow_peer_ptrs = list(self._shadow_buffer.ptrs)
+        self._shadow_stale = True
         largest = 0
         token_pool = torch.zeros(64 * max(1, len(rt.units)), dtype=torch.float32, device=rt.device)
         for unit in rt.units:
@@ -249,12 +257,20 @@ class FusedExecutor:
         return t
 
     # ------------------------------------------------------------------ runtime hooks
-    def shards_written(self):
+    def shards_written(self, shadow_current=False):
+        """The FP32 shards changed.  `shadow_current`: every write went through a kernel that
+        also wrote the bf16 shadow (the fused reduce-scatter + AdamW); otherwise the shadow is
+        rebuilt from the masters before the next gather."""
         self._shards_dirty = True
+        if not shadow_current:
+            self._shadow_stale = True
 
     def before_shard_read(self):
         """Runs on the gather stream before the first gather after the shards changed."""
         if self._shards_dirty:
+            if self._shadow_stale:
+                self.ops.cast_bf16(self.param, self.shadow)
+                self._shadow_stale = False
             self.peer.barrier("fsdp_ag")
             self._shards_dirty = False
 

@@ -21,7 +21,7 @@ from typing import Sequence
 import torch
 from torch import Tensor, nn
 
-ALIGN = 4  # elements; keeps every shard 16-byte aligned for vector loads
+ALIGN = 8  # elements; keeps fp32 shards 32-byte and their bf16 shadows 16-byte aligned
 
 
 @dataclass(frozen=True)

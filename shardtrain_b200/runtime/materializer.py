@@ -272,7 +272,8 @@ class PeerMaterializer:
             # the shards depend on the optimizer's writes (and on every peer having finished
             # its own), never on activations queued on the compute stream
             runtime.wait_parameter_shards_ready()
-            self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32)
+            self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32,
+                                   self.arenas.shadow_peer_ptrs)
 
         # a buffer may be re-gathered only after its last reader on the compute stream
         after = (plan.last_reader,) if plan.last_reader is not None else ()
@@ -334,7 +335,7 @@ class PeerMaterializer:
                 self.ops.reduce_scatter_adamw(
                     slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad, arenas.param,
                     arenas.exp_avg, arenas.exp_avg_sq, 1.0 / self.degree, not first, *hp,
-                    arenas.check_flags, *tp)
+                    arenas.check_flags, *tp, arenas.shadow)
             else:
                 self.ops.reduce_scatter(slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad,
                                         1.0 / self.degree, not first, arenas.check_flags, *tp)

@@ -21,6 +21,9 @@ class _ArenaOptimizer(torch.optim.Optimizer):
         self.arena_step = 0
         self.units_updated: set[int] = set()
         self.fuse_into_reduction = False
+        # True after a step in which every unit was updated by the fused reduce-scatter kernel,
+        # which writes the compute-dtype shadow of the shards next to the FP32 masters
+        self.shadow_current = False
 
     @property
     def _ops(self):
@@ -65,7 +68,9 @@ class ArenaAdamW(_ArenaOptimizer):
     def step(self, closure=None):
         rt = self.runtime
         args = self.kernel_args()
-        for lo, hi in self._pending_ranges():
+        pending = self._pending_ranges()
+        self.shadow_current = not pending and rt.fused is not None
+        for lo, hi in pending:
             p, g = rt.param_arena[lo:hi], rt.grad_arena[lo:hi]
             m, v = self.exp_avg[lo:hi], self.exp_avg_sq[lo:hi]
             if self._ops is not None:
@@ -90,6 +95,7 @@ class ArenaSGD(_ArenaOptimizer):
     def step(self, closure=None):
         rt = self.runtime
         lr = self.param_groups[0]["lr"]
+        self.shadow_current = False
         if self._ops is not None:
             self._ops.sgd(rt.param_arena, rt.grad_arena, lr)
         else:

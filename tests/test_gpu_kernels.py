@@ -216,7 +216,7 @@ def test_shard_gather_and_reduce_scatter_with_emulated_ranks(ops):
     for i, n in enumerate(numels):
         q = -(-n // F)
         segs.append([shard_off, q, n, full_off, 1 if i in (1, 3) else 0])
-        shard_off += -(-q // 4) * 4
+        shard_off += -(-q // 8) * 8
         full_off += -(-n // 8) * 8
     table = torch.tensor(segs, dtype=torch.int64)
     fulls = [torch.randn(n, device=DEV) for n in numels]
@@ -230,13 +230,21 @@ def test_shard_gather_and_reduce_scatter_with_emulated_ranks(ops):
     for (so, q, n, fo, k), f in zip(segs, fulls):
         got = ff[fo:fo + n] if k else fb[fo:fo + n].float()
         assert torch.equal(got, f if k else f.bfloat16().float())
+    # the same gather from the owners' bf16 shadow arenas: half the bytes, identical bits
+    shadows = [s.bfloat16() for s in shards]
+    fb2, ff2 = torch.zeros_like(fb), torch.zeros_like(ff)
+    ops.gather_params([s.data_ptr() for s in shards], table, fb2, ff2, [s.data_ptr() for s in shadows])
+    assert torch.equal(fb2, fb) and torch.equal(ff2, ff)
     grads = [torch.randn(full_off, device=DEV) for _ in range(F)]
     for r in range(F):
         gs = torch.ones(shard_off, device=DEV)
         p, m, v = torch.randn(shard_off, device=DEV), torch.zeros(shard_off, device=DEV), torch.zeros(shard_off, device=DEV)
         p0 = p.clone()
+        shadow = torch.zeros(shard_off, device=DEV, dtype=torch.bfloat16)
         ops.reduce_scatter_adamw([t.data_ptr() for t in grads], r, table, gs, p, m, v, 0.5, True,
-                                 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, None)
+                                 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, None, 1, 0, 1.0, shadow)
+        for (so, q, n, fo, k) in segs:
+            assert torch.equal(shadow[so:so + q], p[so:so + q].bfloat16())
         for (so, q, n, fo, k) in segs:
             keep = max(0, min(q, n - r * q))
             want = 1 + 0.5 * sum(t[fo + r * q:fo + r * q + keep] for t in grads)
