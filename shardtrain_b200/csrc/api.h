@@ -156,11 +156,16 @@ struct AttnBwdCall {
   const float* lse;
   float* delta;      // fp32 [B, hq, S] scratch
   void* dqkv;        // bf16 [B*S, (hq + 2 hkv) * 128]
-  float* dkv_accum;  // fp32 scratch [B*S, 2*hkv*128] for GQA accumulation
+  // Optional fp32 scratch of attention_bwd_parts(...) * B*S * 2*hkv*128 floats.  When given, the
+  // query heads of a GQA group are split over that many dK/dV CTAs per kv head (small batches
+  // would otherwise occupy few SMs) and the partial planes are added in a fixed order.
+  float* dkv_accum;
+  int64_t dkv_accum_floats;
   const uint8_t* key_mask;
   int batch, seq, hq, hkv;
   float scale;
 };
 cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t s);
+int attention_bwd_parts(int batch, int seq, int hq, int hkv);
 
 }  // namespace stb

@@ -305,6 +305,8 @@ struct BwdParams {
   int batch, seq, hq, hkv;
   float scale;
   int* status;
+  float* dkv_part;   // [parts, batch*seq, 2*hkv*128] fp32 partial dK|dV when the group is split
+  int parts;         // CTAs sharing one kv head's query-head group (1: write bf16 directly)
 };
 
 // ---------------------------------------------------------------------------- dQ
@@ -461,8 +463,11 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap map_qkv,
 }
 
 // ---------------------------------------------------------------------------- dK, dV
-// One CTA per (key block j, kv head, batch); loops over the query heads of the GQA group and the
-// query blocks i >= j, so dK / dV of the shared kv head accumulate in TMEM and are written once.
+// One CTA per (key block j, kv head x part, batch); loops over its share of the query heads of the
+// GQA group and the query blocks i >= j, so dK / dV accumulate in TMEM and are written once.
+// With parts == 1 the CTA owns the whole group and writes bf16 dK / dV; with parts > 1 (small
+// batches would otherwise leave most SMs idle) each part writes an fp32 partial plane and
+// attention_dkv_finish_kernel adds the planes in a fixed order.
 // Scores are formed transposed (rows = keys): S^T = K Q^T, dP^T = V dO^T, so each softmax thread
 // owns one key row and writes P^T / dS^T rows directly as K-major operands of
 //   dV += P^T dO,   dK += dS^T Q.
@@ -492,11 +497,13 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int kb = blockIdx.x, hk = blockIdx.y / p.parts, part = blockIdx.y % p.parts, b = blockIdx.z;
   const int group = p.hq / p.hkv;
+  const int heads_here = group / p.parts;   // parts divides group (checked on the host)
+  const int head0 = hk * group + part * heads_here;
   const int n_q = (p.seq + kBlk - 1) / kBlk;
   const int per_head = n_q - kb;          // query blocks kb .. n_q-1
-  const int iters = group * per_head;
+  const int iters = heads_here * per_head;
   const int row0 = b * p.seq;
 
   if (threadIdx.x == 0) {
@@ -524,7 +531,7 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
       load_tile(sK, &map_qkv, kv_full, (p.hq + hk) * kD, row0 + kb * kBlk);
       load_tile(sV, &map_qkv, kv_full, (p.hq + p.hkv + hk) * kD, row0 + kb * kBlk);
       for (int t = 0; t < iters; ++t) {
-        const int h = hk * group + t / per_head;
+        const int h = head0 + t / per_head;
         const int i = kb + t % per_head;
         if (!mbar_wait(q_empty, (t & 1) ^ 1, p.status, kErrAttnWait)) break;
         mbar_expect_tx(q_full, 2 * kTile);
@@ -560,7 +567,7 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
                        (p.key_mask == nullptr || p.key_mask[b * p.seq + min(kv_idx, p.seq - 1)] != 0);
     bool ok = true;
     for (int t = 0; t < iters; ++t) {
-      const int h = hk * group + t / per_head;
+      const int h = head0 + t / per_head;
       const int i = kb + t % per_head;
       softmax_bar();  // everyone finished reading the previous block's lse / delta
       {
@@ -615,13 +622,27 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
     __nv_bfloat16* krow = p.dqkv + (row0 + kv_idx) * width + (p.hq + hk) * kD;
     __nv_bfloat16* vrow = krow + p.hkv * kD;
     const bool store = ok && kv_idx < p.seq;
+    const int64_t pwidth = static_cast<int64_t>(2 * p.hkv) * kD;
+    float* pk_row = p.parts > 1
+                        ? p.dkv_part + (static_cast<int64_t>(part) * p.batch * p.seq + row0 + kv_idx) * pwidth +
+                              hk * kD
+                        : nullptr;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       uint32_t dk[32], dv[32];
       tmem_ld_32x32(tdK + lane_base + c * 32, dk);
       tmem_ld_32x32(tdV + lane_base + c * 32, dv);
       tmem_ld_wait();
-      if (store) {
+      if (store && p.parts > 1) {
+        float* pv_row = pk_row + p.hkv * kD;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          *reinterpret_cast<uint4*>(pk_row + c * 32 + g * 4) =
+              make_uint4(dk[4 * g], dk[4 * g + 1], dk[4 * g + 2], dk[4 * g + 3]);
+          *reinterpret_cast<uint4*>(pv_row + c * 32 + g * 4) =
+              make_uint4(dv[4 * g], dv[4 * g + 1], dv[4 * g + 2], dv[4 * g + 3]);
+        }
+      } else if (store) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 a, e;
@@ -644,6 +665,33 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
+  }
+}
+
+// dqkv[row, K|V columns] = bf16(sum over parts of the fp32 partial planes), fixed order.
+__global__ void attention_dkv_finish_kernel(const float* __restrict__ part, int parts,
+                                            int64_t rows, int hq, int hkv,
+                                            __nv_bfloat16* __restrict__ dqkv) {
+  const int64_t pwidth = static_cast<int64_t>(2 * hkv) * kD;     // floats per row of a plane
+  const int64_t vec = pwidth / 8;
+  const int64_t width = static_cast<int64_t>(hq + 2 * hkv) * kD;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < rows * vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / vec;
+    const int64_t col = (i - row * vec) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < parts; ++k) {
+      const float4* src = reinterpret_cast<const float4*>(part + (k * rows + row) * pwidth + col);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 pk;
+    pk.x = pack_bf16x2(acc[0], acc[1]);
+    pk.y = pack_bf16x2(acc[2], acc[3]);
+    pk.z = pack_bf16x2(acc[4], acc[5]);
+    pk.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(dqkv + row * width + static_cast<int64_t>(hq) * kD + col) = pk;
   }
 }
 
@@ -686,12 +734,35 @@ cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t
   attention_delta_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(c.out), reinterpret_cast<const __nv_bfloat16*>(c.dout),
       c.delta, c.batch, c.seq, c.hq);
-  BwdParams p{c.lse, c.delta, reinterpret_cast<__nv_bfloat16*>(c.dqkv), c.key_mask, c.batch, c.seq,
-              c.hq, c.hkv, c.scale, status};
   const int nblk = (c.seq + kBlk - 1) / kBlk;
-  attention_dkv_kernel<<<dim3(nblk, c.hkv, c.batch), kThreads, kDkvSmem, s>>>(map_qkv, map_do, p);
+  int parts = 1;
+  if (c.dkv_accum != nullptr) {
+    parts = attention_bwd_parts(c.batch, c.seq, c.hq, c.hkv);
+    const int64_t need = static_cast<int64_t>(parts) * rows * 2 * c.hkv * kD;
+    if (parts > 1 && c.dkv_accum_floats < need) return cudaErrorInvalidValue;
+  }
+  BwdParams p{c.lse, c.delta, reinterpret_cast<__nv_bfloat16*>(c.dqkv), c.key_mask, c.batch, c.seq,
+              c.hq, c.hkv, c.scale, status, parts > 1 ? c.dkv_accum : nullptr, parts};
+  attention_dkv_kernel<<<dim3(nblk, c.hkv * parts, c.batch), kThreads, kDkvSmem, s>>>(map_qkv,
+                                                                                     map_do, p);
   attention_dq_kernel<<<dim3(nblk, c.hq, c.batch), kThreads, kDqSmem, s>>>(map_qkv, map_do, p);
+  if (parts > 1) {
+    const int64_t work = rows * (2 * c.hkv * kD / 8);
+    const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, 148 * 8));
+    attention_dkv_finish_kernel<<<grid, 256, 0, s>>>(c.dkv_accum, parts, rows, c.hq, c.hkv,
+                                                     reinterpret_cast<__nv_bfloat16*>(c.dqkv));
+  }
   return cudaGetLastError();
+}
+
+int attention_bwd_parts(int batch, int seq, int hq, int hkv) {
+  // smallest split of the query-head group that puts at least one dK/dV CTA on every SM
+  const int group = hq / hkv;
+  const int nblk = (seq + kBlk - 1) / kBlk;
+  const int base = nblk * hkv * batch;
+  for (int parts = 1; parts <= group; ++parts)
+    if (group % parts == 0 && base * parts >= 148) return parts;
+  return group;
 }
 
 }  // namespace stb

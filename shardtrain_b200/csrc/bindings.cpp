@@ -569,7 +569,14 @@ void attention_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, con
   c.lse = lse.data_ptr<float>();
   c.delta = delta.data_ptr<float>();
   c.dqkv = dqkv.data_ptr();
-  c.dkv_accum = dkv_accum.defined() && dkv_accum.numel() ? dkv_accum.data_ptr<float>() : nullptr;
+  const int parts = stb::attention_bwd_parts(static_cast<int>(batch), static_cast<int>(seq),
+                                             static_cast<int>(hq), static_cast<int>(hkv));
+  const int64_t need = static_cast<int64_t>(parts) * batch * seq * 2 * hkv * 128;
+  // a scratch too small for the split (callers may pass any placeholder) keeps the unsplit path
+  const bool split = parts > 1 && dkv_accum.defined() && dkv_accum.scalar_type() == at::kFloat &&
+                     dkv_accum.numel() >= need;
+  c.dkv_accum = split ? dkv_accum.data_ptr<float>() : nullptr;
+  c.dkv_accum_floats = split ? dkv_accum.numel() : 0;
   c.key_mask = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
   c.batch = static_cast<int>(batch);
   c.seq = static_cast<int>(seq);

@@ -175,13 +175,23 @@ __global__ void rmsnorm_bwd_kernel(const float* __restrict__ dy, const float* __
 }
 
 // out[c] (+)= sum_r partial[r, c]; deterministic order.
+// out[c] = sum_r partial[r, c].  A CTA covers 32 columns with 8 row groups (blockDim 32 x 8): the
+// groups stride over the rows, then combine through shared memory in a fixed order.
 __global__ void colsum_f32_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                   int rows, int cols, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float part[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += partial[static_cast<int64_t>(r) * cols + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < cols)
+    for (int r = threadIdx.y; r < rows; r += 8) s += partial[static_cast<int64_t>(r) * cols + c];
+  part[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) t += part[g][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 // scratch[b, c] = sum over the rows handled by CTA row-group b of x[r, c] (bf16 input).
@@ -523,7 +533,7 @@ cudaError_t launch_rmsnorm_bwd(const float* dy, const float* x, const float* w, 
 
 cudaError_t launch_colsum_f32(const float* partial, float* out, int rows, int cols,
                               bool accumulate, cudaStream_t s) {
-  colsum_f32_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, out, rows, cols, accumulate);
+  colsum_f32_kernel<<<(cols + 31) / 32, dim3(32, 8), 0, s>>>(partial, out, rows, cols, accumulate);
   return cudaGetLastError();
 }
 
@@ -533,8 +543,8 @@ cudaError_t launch_colsum_bf16(const void* x, int64_t ldx, float* out, int rows,
   dim3 grid((cols / 2 + 127) / 128, scratch_rows);
   colsum_bf16_partial_kernel<<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
                                                   scratch, rows, cols);
-  colsum_f32_kernel<<<(cols + 127) / 128, 128, 0, s>>>(scratch, out, scratch_rows, cols,
-                                                       accumulate);
+  colsum_f32_kernel<<<(cols + 31) / 32, dim3(32, 8), 0, s>>>(scratch, out, scratch_rows, cols,
+                                                             accumulate);
   return cudaGetLastError();
 }
 

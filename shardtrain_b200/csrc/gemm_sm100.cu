@@ -156,7 +156,8 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
   if (c.scatter_degree > 1) {
     // the scatter epilogue writes fp32 rows; every destination must be 16-byte aligned and the
     // sequence must split evenly over the owners
-    if (!c.out_fp32 || c.accumulate || c.residual != nullptr || c.scatter_degree > 8 ||
+    if (!c.out_fp32 || c.accumulate || c.residual != nullptr || c.bias != nullptr ||
+        c.scatter_degree > 8 ||
         c.scatter_seq_local <= 0 || c.scatter_seq != c.scatter_seq_local * c.scatter_degree ||
         c.M % c.scatter_seq)
       return cudaErrorInvalidValue;

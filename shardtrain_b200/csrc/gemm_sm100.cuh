@@ -47,7 +47,10 @@ struct GemmSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   // tiles + barriers (full, empty, accumulator full/empty) + tmem pointer + abort flag, plus
   // 1 KB alignment slack
-  static constexpr int kTotal = kStages * kStageBytes + 1024 + 256;
+  // + 4 KB per epilogue warp to transpose scattered output rows into 128-byte row segments
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kScatterStageBytes = 4 * 4096;
+  static constexpr int kTotal = kStages * kStageBytes + 1024 + kBarrierBytes + kScatterStageBytes;
 };
 
 template <int BN, bool A_MN, bool B_MN>
@@ -215,7 +218,46 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         tmem_ld_32x32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= N) continue;
+        if (col0 >= N) continue;                         // warp-uniform
+        if (ep.scatter_degree > 1) {
+          // Sequence scatter.  A thread owns one accumulator row, so storing from registers
+          // would emit 16-byte pieces of 32 different rows per instruction -- fine for local
+          // L2, ruinous for stores that cross NVLink.  The warp's 32x32 block goes through
+          // shared memory (XOR-swizzled 16-byte slots, conflict free both ways) and leaves as
+          // four full 128-byte row segments per instruction.
+          float* stage = reinterpret_cast<float*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes) +
+                         q * 1024;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 x;
+            x.x = __uint_as_float(r[4 * j]) * ep.alpha;
+            x.y = __uint_as_float(r[4 * j + 1]) * ep.alpha;
+            x.z = __uint_as_float(r[4 * j + 2]) * ep.alpha;
+            x.w = __uint_as_float(r[4 * j + 3]) * ep.alpha;
+            *reinterpret_cast<float4*>(stage + lane * 32 + ((j ^ (lane & 7)) << 2)) = x;
+          }
+          __syncwarp();
+          const int seg = lane & 7;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int rr = k * 4 + (lane >> 3);
+            const float4 x =
+                *reinterpret_cast<const float4*>(stage + rr * 32 + ((seg ^ (rr & 7)) << 2));
+            const int64_t gr = static_cast<int64_t>(m0) + q * 32 + rr;
+            if (ok && gr < M && col0 + seg * 4 < N) {
+              const int64_t b = gr / ep.scatter_seq;
+              const int pos = static_cast<int>(gr - b * ep.scatter_seq);
+              const int owner = pos / ep.scatter_seq_local;
+              float* o = ep.scatter_out[owner] +
+                         (b * ep.scatter_seq_local + (pos - owner * ep.scatter_seq_local)) * ep.ldo +
+                         col0 + seg * 4;
+              *reinterpret_cast<float4*>(o) = x;
+            }
+          }
+          __syncwarp();
+          continue;
+        }
+        if (!row_ok) continue;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ep.alpha;
@@ -226,13 +268,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         if (ep.out_fp32) {
           float* o = reinterpret_cast<float*>(ep.out) + g_row * ep.ldo + col0;
-          if (ep.scatter_degree > 1) {
-            const int64_t b = g_row / ep.scatter_seq;
-            const int pos = static_cast<int>(g_row - b * ep.scatter_seq);
-            const int owner = pos / ep.scatter_seq_local;
-            o = ep.scatter_out[owner] +
-                (b * ep.scatter_seq_local + (pos - owner * ep.scatter_seq_local)) * ep.ldo + col0;
-          }
           const float* rs = ep.residual ? reinterpret_cast<const float*>(ep.residual) +
                                               g_row * ep.ldo + col0
                                         : nullptr;

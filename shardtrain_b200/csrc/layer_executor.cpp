@@ -193,7 +193,12 @@ Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1,
   bc.lse = lse.data_ptr<float>();
   bc.delta = delta.data_ptr<float>();
   bc.dqkv = d_qkv.data_ptr();
-  bc.dkv_accum = nullptr;
+  const int parts = stb::attention_bwd_parts(static_cast<int>(B), static_cast<int>(S),
+                                             static_cast<int>(hq), static_cast<int>(hkv));
+  Tensor dkv_parts;
+  if (parts > 1) dkv_parts = at::empty({parts, M, 2 * hkv * D}, f32);
+  bc.dkv_accum = parts > 1 ? dkv_parts.data_ptr<float>() : nullptr;
+  bc.dkv_accum_floats = parts > 1 ? dkv_parts.numel() : 0;
   bc.key_mask = km;
   bc.batch = static_cast<int>(B);
   bc.seq = static_cast<int>(S);
@@ -354,7 +359,12 @@ Tensor layer_backward_sp(
   bc.lse = lse.data_ptr<float>();
   bc.delta = delta.data_ptr<float>();
   bc.dqkv = d_qkv.data_ptr();
-  bc.dkv_accum = nullptr;
+  const int parts = stb::attention_bwd_parts(static_cast<int>(B), static_cast<int>(S),
+                                             static_cast<int>(hq), static_cast<int>(hkv));
+  Tensor dkv_parts;
+  if (parts > 1) dkv_parts = at::empty({parts, M, 2 * hkv * D}, f32);
+  bc.dkv_accum = parts > 1 ? dkv_parts.data_ptr<float>() : nullptr;
+  bc.dkv_accum_floats = parts > 1 ? dkv_parts.numel() : 0;
   bc.key_mask = km;
   bc.batch = static_cast<int>(B);
   bc.seq = static_cast<int>(S);

@@ -294,15 +294,29 @@ struct VoidPeers {
 __global__ void seq_gather_kernel(VoidPeers peers, int degree, uint4* __restrict__ out, int batch,
                                   int seq_local, int64_t row_vec) {
   const int64_t per_peer = static_cast<int64_t>(batch) * seq_local * row_vec;
+  const int64_t per_batch = seq_local * row_vec;
   const int64_t total = per_peer * degree;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / per_peer);
-    const int64_t j = i - r * per_peer;
-    const int64_t b = j / (seq_local * row_vec);
-    const int64_t rest = j - b * seq_local * row_vec;
-    const uint4 v = reinterpret_cast<const uint4*>(peers.p[r])[j];
-    out[(b * degree + r) * seq_local * row_vec + rest] = v;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // four independent 16-byte loads in flight per thread: remote latency is several microseconds
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total;
+       i0 += 4 * stride) {
+    uint4 v[4];
+    int64_t dst[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t i = i0 + u * stride;
+      dst[u] = -1;
+      if (i < total) {
+        const int r = static_cast<int>(i / per_peer);
+        const int64_t j = i - r * per_peer;
+        const int64_t b = j / per_batch;
+        v[u] = reinterpret_cast<const uint4*>(peers.p[r])[j];
+        dst[u] = (b * degree + r) * per_batch + (j - b * per_batch);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (dst[u] >= 0) out[dst[u]] = v[u];
   }
 }
 
@@ -452,7 +466,7 @@ cudaError_t launch_seq_gather(const void* const* peers, int degree, void* out, i
   VoidPeers vp;
   for (int i = 0; i < degree; ++i) vp.p[i] = peers[i];
   const int64_t total = static_cast<int64_t>(batch) * seq_local * (row_bytes / 16) * degree;
-  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 8));
+  const int grid = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, 148 * 8));
   seq_gather_kernel<<<grid, 256, 0, s>>>(vp, degree, reinterpret_cast<uint4*>(out), batch,
                                          seq_local, row_bytes / 16);
   return cudaGetLastError();

@@ -114,6 +114,15 @@ def test_attention_forward_backward(ops, B, S, hq, hkv, masked):
     ops.attention_bwd(qkv, out, dout, lse, delta, dqkv, delta, mask, B, S, hq, hkv, scale)
     for lo, hi in ((0, hq * D), (hq * D, (hq + hkv) * D), ((hq + hkv) * D, W)):
         assert rel(dqkv[:, lo:hi], want[:, lo:hi]) < 6e-3
+    # with a scratch large enough the query-head group is split over several dK/dV CTAs per kv
+    # head and the fp32 partial planes are added in a fixed order: same result, twice
+    scratch = torch.full(((hq // hkv) * B * S * 2 * hkv * D,), float("nan"), device=DEV)
+    split = [torch.zeros_like(dqkv), torch.zeros_like(dqkv)]
+    for target in split:
+        ops.attention_bwd(qkv, out, dout, lse, delta, target, scratch, mask, B, S, hq, hkv, scale)
+    assert torch.equal(split[0], split[1])
+    for lo, hi in ((0, hq * D), (hq * D, (hq + hkv) * D), ((hq + hkv) * D, W)):
+        assert rel(split[0][:, lo:hi], want[:, lo:hi]) < 6e-3
 
 
 def test_rmsnorm_rope_swiglu(ops):
@@ -345,3 +354,19 @@ def test_reduce_scatter_sums_replicated_segments_over_the_whole_mesh(ops):
     so, q = segs[1][0], segs[1][1]
     for f in range(F):
         assert torch.equal(results[f, 0][so:so + q], results[f, 1][so:so + q])
+
+
+@pytest.mark.parametrize("T,B,sl,cols", [(2, 3, 64, 512), (4, 1, 40, 1536), (1, 2, 7, 128)])
+def test_sequence_gather_and_pull_reduce_scatter(ops, T, B, sl, cols):
+    """Sequence all-gather / reduce-scatter kernels with the peers emulated by local tensors."""
+    parts = [torch.randn(B, sl, cols, device=DEV).bfloat16() for _ in range(T)]
+    out = torch.empty(B * T * sl, cols, device=DEV, dtype=torch.bfloat16)
+    ops.seq_gather([p.data_ptr() for p in parts], out, B, sl, cols * 2)
+    assert torch.equal(out.view(B, T * sl, cols), torch.cat(parts, dim=1))
+    partials = [torch.randn(B, T * sl, cols, device=DEV) for _ in range(T)]
+    residual = torch.randn(B, sl, cols, device=DEV)
+    for rank in range(T):
+        got = torch.empty(B, sl, cols, device=DEV)
+        ops.seq_reduce_scatter([p.data_ptr() for p in partials], rank, residual, got, B, sl)
+        want = residual + sum(p[:, rank * sl:(rank + 1) * sl] for p in partials)
+        torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
