@@ -166,13 +166,30 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
   }
   int bn = c.force_bn;
   if (bn == 0) {
+    // Persistent kernel, one CTA per SM: the run time is (waves of tiles) x (time of one tile),
+    // and a tile costs its width plus a fixed part (pipeline fill, epilogue hand-over) worth
+    // about 32 columns.  Pick the width with the smallest product; measured on B200 this is 256
+    // for the wide projections, 192 for N = 1536 at 2048..4096 rows (192 or 96 tiles of 256 would
+    // leave the last wave a third full), 128 once 256-wide tiles no longer fill the SMs.
+    static int sms = [] {
+      int dev = 0, n = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+      return n;
+    }();
     const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
-    const int ctas256 = m_tiles * ((c.N + 255) / 256);
-    // measured on B200: the 256-wide tile wins as soon as it still yields ~80 CTAs (e.g. 65 us
-    // against 107 us at 2048x1536x8960); below that the 128-wide tile's extra CTAs win
-    bn = (ctas256 >= 80) ? 256 : 128;
+    int64_t best = -1;
+    for (int cand : {256, 192, 128}) {
+      const int64_t tiles = static_cast<int64_t>(m_tiles) * ((c.N + cand - 1) / cand);
+      const int64_t cost = ((tiles + sms - 1) / sms) * (cand + 32);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = cand;
+      }
+    }
   }
   if (bn == 256) return dispatch_major<256>(c, status, stream);
+  if (bn == 192) return dispatch_major<192>(c, status, stream);
   if (bn == 128) return dispatch_major<128>(c, status, stream);
   return cudaErrorInvalidValue;
 }

@@ -43,7 +43,9 @@ template <int BN>
 struct GemmSmem {
   static constexpr int kABytes = kGemmBM * kGemmBK * 2;
   static constexpr int kBBytes = BN * kGemmBK * 2;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+  // TMEM allocations are powers of two: two 192-column accumulators live in a 512-column grant
+  static constexpr int kTmemCols = (2 * BN <= 256) ? 256 : 512;
   static constexpr int kStageBytes = kABytes + kBBytes;
   // tiles + barriers (full, empty, accumulator full/empty) + tmem pointer + abort flag, plus
   // 1 KB alignment slack
@@ -108,7 +110,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     prefetch_tensormap(&tma_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_ptr, 2 * BN);
+    tmem_alloc(tmem_ptr, S::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -323,7 +325,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, S::kTmemCols);
   }
 }
 

@@ -34,6 +34,10 @@ GEMM_CASES = [
     (2048, 1536, 512, True, True, True, False, False, True, 0),
     (1000, 520, 264, True, True, True, False, False, False, 256),
     (4096, 1536, 8960, False, False, False, False, False, False, 256),   # several tiles per CTA
+    (4096, 1536, 2048, False, False, True, False, True, False, 192),     # 192-wide tiles, 2 waves
+    (2048, 1536, 2048, False, True, True, False, False, False, 0),       # heuristic picks 192
+    (2048, 1536, 1024, True, True, True, False, False, False, 192),
+    (300, 584, 328, False, False, False, True, True, False, 192),        # ragged edges
 ]
 
 
