@@ -20,7 +20,8 @@ struct GemmCall {
   bool out_fp32;
   bool accumulate;
   float alpha;
-  int force_bn;  // 0 = heuristic, else 128 or 256
+  int force_bn;  // 0 = rule, else 128, 192 or 256
+  int split_k;   // K-split of the tail wave's tiles: 0 = rule, 1 = never, n = exactly n
   // Optional sequence scatter of an fp32 result (see GemmEpilogue): row b*seq + s is written to
   // scatter_out[s / seq_local] at row b*seq_local + s % seq_local; `out` is then unused.
   float* scatter_out[8];

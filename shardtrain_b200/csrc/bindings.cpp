@@ -44,7 +44,7 @@ Tensor status_tensor_op() { return status_tensor(); }
 
 void gemm(const Tensor& a, const Tensor& b, Tensor out, bool a_mn, bool b_mn,
           const c10::optional<Tensor>& bias, const c10::optional<Tensor>& residual,
-          bool accumulate, double alpha, int64_t force_bn) {
+          bool accumulate, double alpha, int64_t force_bn, int64_t split_k) {
   need(a, at::kBFloat16, "a");
   need(b, at::kBFloat16, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm operands must be 2-D");
@@ -71,6 +71,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, bool a_mn, bool b_mn,
   c.accumulate = accumulate;
   c.alpha = static_cast<float>(alpha);
   c.force_bn = static_cast<int>(force_bn);
+  c.split_k = static_cast<int>(split_k);
   if (bias.has_value()) {
     need(*bias, at::kFloat, "bias");
     TORCH_CHECK(bias->numel() == c.N, "bias length mismatch");
@@ -593,7 +594,9 @@ TORCH_LIBRARY(stb, m) {
   m.def("status_read", &status_read);
   m.def("status_reset", &status_reset);
   m.def("status_tensor", &status_tensor_op);
-  m.def("gemm", &gemm);
+  m.def("gemm(Tensor a, Tensor b, Tensor out, bool a_mn, bool b_mn, Tensor? bias, Tensor? residual, "
+        "bool accumulate, float alpha, int force_bn, int split_k=0) -> ()",
+        &gemm);
   m.def("gemm_scatter", &gemm_scatter);
   m.def("slot_sum_rmsnorm", &slot_sum_rmsnorm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

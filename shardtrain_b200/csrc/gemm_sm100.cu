@@ -85,6 +85,63 @@ bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int6
 
 namespace {
 
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v;
+  }();
+  return n;
+}
+
+// How the tail wave of `tiles` tiles is cut along K (see GemmSplit).  `want`: 0 = rule, 1 = never,
+// n > 1 = exactly n (tests).  Returns the split factor and fills full / kb_per.
+int plan_split(int tiles, int num_kb, int want, int* full, int* kb_per) {
+  const int sms = sm_count();
+  *full = (tiles / sms) * sms;
+  const int rem = tiles - *full;
+  *kb_per = num_kb;
+  if (rem == 0 || want == 1) return 1;
+  // parking and re-reading a partial tile costs about as much as 10 k-blocks: only splits that
+  // keep at least 32 k-blocks each pay off
+  int split = want > 1 ? want : std::min({sms / rem, 8, num_kb / 32});
+  split = std::min(split, sms / rem);
+  if (split < 2) return 1;
+  *kb_per = (num_kb + split - 1) / split;
+  return (num_kb + *kb_per - 1) / *kb_per;      // no empty K range
+}
+
+// Partial-tile workspace and tile counters of the tail split, one set per (device, stream): two
+// GEMMs can only overlap on different streams, and each stream then has its own set.
+struct SplitBuffers {
+  float* workspace = nullptr;
+  int* counters = nullptr;
+};
+std::mutex g_split_mutex;
+std::unordered_map<uint64_t, SplitBuffers> g_split_buffers;
+
+cudaError_t split_buffers(cudaStream_t stream, SplitBuffers* out) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint64_t key = (static_cast<uint64_t>(dev) << 56) ^ reinterpret_cast<uint64_t>(stream);
+  std::lock_guard<std::mutex> lock(g_split_mutex);
+  auto it = g_split_buffers.find(key);
+  if (it == g_split_buffers.end()) {
+    SplitBuffers b;
+    const size_t units = static_cast<size_t>(sm_count());
+    cudaError_t e = cudaMalloc(&b.workspace, units * kGemmBM * 256 * sizeof(float));
+    if (e != cudaSuccess) return e;
+    e = cudaMalloc(&b.counters, units * sizeof(int));
+    if (e != cudaSuccess) return e;
+    e = cudaMemset(b.counters, 0, units * sizeof(int));
+    if (e != cudaSuccess) return e;
+    it = g_split_buffers.emplace(key, b).first;
+  }
+  *out = it->second;
+  return cudaSuccess;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
@@ -123,14 +180,22 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   if (attr_err != cudaSuccess) return attr_err;
   const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
   const int n_tiles = (c.N + BN - 1) / BN;
-  static int sm_count = [] {
-    int dev = 0, n = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
-  }();
-  const int grid = std::min(m_tiles * n_tiles, sm_count);   // persistent: one CTA per SM
-  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, ep, c.M, c.N, c.K, status);
+  const int tiles = m_tiles * n_tiles;
+  const int num_kb = (c.K + kGemmBK - 1) / kGemmBK;
+  GemmSplit sp{};
+  sp.split = plan_split(tiles, num_kb, c.split_k, &sp.full_tiles, &sp.kb_per_split);
+  if (sp.split > 1) {
+    SplitBuffers buffers;
+    const cudaError_t e = split_buffers(stream, &buffers);
+    if (e != cudaSuccess) return e;
+    sp.workspace = buffers.workspace;
+    sp.counters = buffers.counters;
+  } else {
+    sp.full_tiles = tiles;
+  }
+  sp.total_units = sp.full_tiles + (tiles - sp.full_tiles) * sp.split;
+  const int grid = std::min(sp.total_units, sm_count());   // persistent: one CTA per SM
+  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, ep, sp, c.M, c.N, c.K, status);
   return cudaGetLastError();
 }
 
@@ -166,22 +231,23 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
   }
   int bn = c.force_bn;
   if (bn == 0) {
-    // Persistent kernel, one CTA per SM: the run time is (waves of tiles) x (time of one tile),
-    // and a tile costs its width plus a fixed part (pipeline fill, epilogue hand-over) worth
-    // about 32 columns.  Pick the width with the smallest product; measured on B200 this is 256
-    // for the wide projections, 192 for N = 1536 at 2048..4096 rows (192 or 96 tiles of 256 would
-    // leave the last wave a third full), 128 once 256-wide tiles no longer fill the SMs.
-    static int sms = [] {
-      int dev = 0, n = 148;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-      return n;
-    }();
+    // Persistent kernel, one CTA per SM: the run time is (waves of tiles) x (time of one tile).
+    // Measured on B200, a k-block of a 128 x BN tile is bound by the shared-memory operand reads
+    // of the MMAs, i.e. its time goes with 128 + BN, not with BN; the tail wave counts 1/split
+    // when its tiles are cut along K.  Pick the width with the smallest product.
+    const int sms = sm_count();
     const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
-    int64_t best = -1;
+    const int num_kb = (c.K + kGemmBK - 1) / kGemmBK;
+    double best = -1.0;
     for (int cand : {256, 192, 128}) {
-      const int64_t tiles = static_cast<int64_t>(m_tiles) * ((c.N + cand - 1) / cand);
-      const int64_t cost = ((tiles + sms - 1) / sms) * (cand + 32);
+      const int tiles = m_tiles * ((c.N + cand - 1) / cand);
+      int full, kb_per;
+      const int split = plan_split(tiles, num_kb, c.split_k, &full, &kb_per);
+      // whole waves + the tail wave (shortened by its K split, plus the cost of parking and
+      // re-reading the partial tiles)
+      double waves = full / sms;
+      if (tiles > full) waves += 1.0 / split + (split > 1 ? 0.06 : 0.0);
+      const double cost = waves * (kGemmBM + cand);
       if (best < 0 || cost < best) {
         best = cost;
         bn = cand;

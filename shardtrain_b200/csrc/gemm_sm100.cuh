@@ -35,6 +35,21 @@ struct GemmEpilogue {
   int scatter_seq_local;
 };
 
+// Tail split.  A persistent grid of G CTAs runs floor(tiles / G) full waves of whole tiles; the
+// `tiles % G` tiles left over would occupy only part of the machine for a whole tile time, so
+// each of them is cut along K into `split` units (rem * split <= G).  A split unit stores its raw
+// fp32 accumulator tile in `workspace`; the unit that arrives last at the tile's counter adds the
+// `split` partial tiles in index order (so the result does not depend on arrival order) and runs
+// the normal epilogue.  Nothing waits on another CTA.
+struct GemmSplit {
+  int full_tiles;     // tiles [0, full_tiles) are whole-K units
+  int split;          // K-splits per remaining tile (1: no tail split)
+  int kb_per_split;   // k-blocks per split unit
+  int total_units;
+  float* workspace;   // [rem_tiles * split][128][BN] fp32
+  int* counters;      // [rem_tiles], zero between launches
+};
+
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;
 constexpr int kGemmThreads = 192;
@@ -58,8 +73,8 @@ struct GemmSmem {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
-                         const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep, int M, int N,
-                         int K, int* __restrict__ status) {
+                         const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep, GemmSplit sp,
+                         int M, int N, int K, int* __restrict__ status) {
   // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
   // double buffered in TMEM (2 x BN columns) so the epilogue of one tile overlaps the MMAs of the
   // next; the shared-memory operand pipeline runs across tile boundaries without draining.
@@ -87,6 +102,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   // Grouped rasterisation: walk up to 8 M-tiles before moving to the next N-tile so that the
   // CTAs resident at one time share operand tiles in L2.
+  // unit -> (tile, k-block range, split index or -1 for a whole tile)
+  auto unit_work = [&](int unit, int& tile, int& kb0, int& kb1, int& part) {
+    if (unit < sp.full_tiles) {
+      tile = unit; kb0 = 0; kb1 = num_kb; part = -1;
+    } else {
+      const int r = unit - sp.full_tiles;
+      tile = sp.full_tiles + r / sp.split;
+      part = sp.split > 1 ? r % sp.split : -1;
+      kb0 = sp.split > 1 ? part * sp.kb_per_split : 0;
+      kb1 = sp.split > 1 ? min(num_kb, kb0 + sp.kb_per_split) : num_kb;
+    }
+  };
   auto tile_origin = [&](int tile, int& m0, int& n0) {
     const int first_m = (tile / group_span) * GROUP;
     const int gm = min(m_tiles - first_m, GROUP);
@@ -122,10 +149,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     if (lane == 0) {
       int it = 0;  // k-blocks issued so far, across tiles
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int m0, n0;
+      for (int unit = blockIdx.x; unit < sp.total_units && ok; unit += gridDim.x) {
+        int tile, kb0, kb1, part, m0, n0;
+        unit_work(unit, tile, kb0, kb1, part);
         tile_origin(tile, m0, n0);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, status, kErrProducerEmptyWait)) {
@@ -163,7 +191,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       constexpr uint32_t idesc = make_idesc_bf16(kGemmBM, BN, A_MN, B_MN);
       int it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int unit = blockIdx.x; unit < sp.total_units && ok; unit += gridDim.x, ++local) {
+        int tile, kb0, kb1, part;
+        unit_work(unit, tile, kb0, kb1, part);
         const int ab = local & 1;
         // the epilogue must have drained this accumulator buffer (two tiles ago)
         if (!mbar_wait(&acc_empty[ab], ((local >> 1) & 1) ^ 1, status, kErrMmaFullWait)) {
@@ -172,7 +202,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + ab * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, status, kErrMmaFullWait)) {
@@ -192,7 +222,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                      : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
                                      : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            tc_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_f16(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         }
@@ -205,8 +235,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     const int row = q * 32 + lane;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      int m0, n0;
+    int* last_flag = reinterpret_cast<int*>(tmem_ptr + 2);   // shared: "this CTA reduces the tile"
+    for (int unit = blockIdx.x; unit < sp.total_units; unit += gridDim.x, ++local) {
+      int tile, kb0, kb1, part, m0, n0;
+      unit_work(unit, tile, kb0, kb1, part);
       tile_origin(tile, m0, n0);
       const int ab = local & 1;
       if (ok) ok = mbar_wait(&acc_full[ab], (local >> 1) & 1, status, kErrEpilogueAccumWait);
@@ -214,13 +246,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       const uint32_t tmem_d = tmem_base + ab * BN;
       const int64_t g_row = static_cast<int64_t>(m0) + row;
       const bool row_ok = ok && g_row < M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
-        tmem_ld_wait();
+      // one 32-column chunk of this thread's accumulator row -> output (all epilogue variants)
+      auto emit = [&](uint32_t (&r)[32], int c) {
         const int col0 = n0 + c * 32;
-        if (col0 >= N) continue;                         // warp-uniform
+        if (col0 >= N) return;                         // warp-uniform
         if (ep.scatter_degree > 1) {
           // Sequence scatter.  A thread owns one accumulator row, so storing from registers
           // would emit 16-byte pieces of 32 different rows per instruction -- fine for local
@@ -257,9 +286,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
             }
           }
           __syncwarp();
-          continue;
+          return;
         }
-        if (!row_ok) continue;
+        if (!row_ok) return;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ep.alpha;
@@ -314,10 +343,69 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
             *reinterpret_cast<uint4*>(o + i) = pk;
           }
         }
+      };
+      if (part < 0) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
+          tmem_ld_wait();
+          emit(r, c);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&acc_empty[ab]);   // TMEM reads complete: hand the buffer back to the MMA warp
+        continue;
       }
-      // this thread's TMEM reads of the buffer are complete: hand it back to the MMA warp
+      // ---- K-split unit: park the raw partial tile, the last arrival reduces
+      // Workspace layout per partial tile: [BN / 4 column quads][128 rows][4 floats], so the 32
+      // lanes of a warp (consecutive rows) touch consecutive 16-byte words both when parking
+      // and when reducing; the thread that reduces a row is the one that owns it in every unit.
+      const int rem_tile = tile - sp.full_tiles;
+      constexpr int64_t kTileFloats = static_cast<int64_t>(kGemmBM) * BN;
+      float* mine = sp.workspace + (static_cast<int64_t>(rem_tile) * sp.split + part) * kTileFloats +
+                    row * 4;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(mine + (c * 8 + j) * (kGemmBM * 4)) =
+              make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+      }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[ab]);
+      __threadfence();                              // partial tile visible before the count
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int seen = atomicAdd(sp.counters + rem_tile, 1);
+        *last_flag = (seen == sp.split - 1) ? 1 : 0;
+        if (seen == sp.split - 1) sp.counters[rem_tile] = 0;   // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag == 0) continue;
+      __threadfence();
+      const float* first = sp.workspace + static_cast<int64_t>(rem_tile) * sp.split * kTileFloats +
+                           row * 4;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float acc[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+        for (int sidx = 0; sidx < sp.split; ++sidx) {
+          const float* src = first + sidx * kTileFloats;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(src + (c * 8 + j) * (kGemmBM * 4)));
+            acc[4 * j] += t.x; acc[4 * j + 1] += t.y; acc[4 * j + 2] += t.z; acc[4 * j + 3] += t.w;
+          }
+        }
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(acc[i]);
+        emit(r, c);
+      }
     }
   }
 

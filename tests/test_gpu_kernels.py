@@ -64,6 +64,38 @@ def test_tcgen05_gemm(ops, case):
     assert rel(out, ref) < (2e-5 if out_fp32 else 4e-3)
 
 
+SPLIT_CASES = [
+    # M, N, K, a_mn, b_mn, out_fp32, bias, residual, force_bn, split_k
+    (512, 1536, 8960, False, False, True, False, True, 256, 0),     # 24 tiles -> 6-way split
+    (4096, 1536, 4096, False, True, True, False, False, 256, 0),    # 148 whole + 44 tiles x 3
+    (640, 520, 1104, False, False, False, True, True, 128, 4),      # ragged, bf16 out, bias
+    (1024, 1536, 2048, True, True, True, False, False, 0, 0),
+]
+
+
+@pytest.mark.parametrize("case", SPLIT_CASES, ids=[f"{c[0]}x{c[1]}x{c[2]}_s{c[9]}" for c in SPLIT_CASES])
+def test_gemm_tail_split_is_deterministic_and_matches_unsplit(ops, case):
+    """Tail tiles cut along K, reduced by the last arriving CTA in split order: equal (to fp32
+    rounding) to the unsplit kernel, bit-identical run to run, and the counters reset themselves."""
+    M, N, K, a_mn, b_mn, out_fp32, bias, residual, bn, split = case
+    torch.manual_seed(1)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV).bfloat16()
+    dtype = torch.float32 if out_fp32 else torch.bfloat16
+    bias_t = torch.randn(N, device=DEV) if bias else None
+    res = torch.randn(M, N, device=DEV).to(dtype) if residual else None
+    outs = []
+    for split_k in (1, split, split):
+        out = torch.empty(M, N, device=DEV, dtype=dtype)
+        ops.gemm(a, b, out, a_mn, b_mn, bias_t, res, False, 1.0, bn, split_k)
+        outs.append(out)
+    assert torch.equal(outs[1], outs[2])
+    assert rel(outs[1], outs[0]) < (1e-5 if out_fp32 else 4e-3)
+    want = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    want = want + (bias_t if bias else 0) + (res.float() if residual else 0)
+    assert rel(outs[1], want) < 5e-3
+
+
 def test_gemm_rejects_bad_arguments(ops):
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
