@@ -83,13 +83,16 @@ def build(verbose: bool = False) -> Path:
         objects.append(obj)
     if _newer(OUT, objects):
         libdirs = cpp_extension.library_paths(device_type="cuda")
-        link = ["g++", "-shared", "-o", str(OUT), *map(str, objects)]
+        # link beside the target and rename: a reader never sees a half-written library
+        staged = OUT.with_name(OUT.name + ".link")
+        link = ["g++", "-shared", "-o", str(staged), *map(str, objects)]
         for d in libdirs:
             link += [f"-L{d}", f"-Wl,-rpath,{d}"]
         link += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"]
         if verbose:
             print("link", OUT.name, flush=True)
         _run(link)
+        os.replace(staged, OUT)
     return OUT
 
 

@@ -140,6 +140,15 @@ cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree,
 cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank, uint32_t epoch,
                                 int slot, int* status, uint32_t max_spin, cudaStream_t s);
 
+// All-reduce of up to 16 doubles over peer memory in one launch (the per-step metrics: valid-label
+// count, loss numerator, finite vote).  Element i is summed, or minimised when bit i of min_mask
+// is set; every rank combines the contributions in rank order.  inboxes[r]: rank r's
+// [2][8][16]-double inbox.  Bounded wait, status word on expiry.
+cudaError_t launch_peer_allreduce_small(uint32_t* const* flag_pads, double* const* inboxes, int degree,
+                                        int rank, uint32_t epoch, int slot, const double* in,
+                                        double* out, int n, uint32_t min_mask, int* status,
+                                        uint32_t max_spin, cudaStream_t s);
+
 // ------------------------------------------------------------------ attention (attention_sm100.cu)
 struct AttnCall {
   const void* qkv;   // bf16 [B*S, (hq + 2 hkv) * 128], rope already applied

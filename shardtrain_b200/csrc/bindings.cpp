@@ -508,6 +508,28 @@ void peer_barrier(c10::ArrayRef<int64_t> pad_ptrs, int64_t rank, int64_t epoch, 
         "peer_barrier");
 }
 
+void peer_allreduce_small(c10::ArrayRef<int64_t> pad_ptrs, c10::ArrayRef<int64_t> inbox_ptrs,
+                          int64_t rank, int64_t epoch, int64_t slot, const Tensor& in, Tensor out,
+                          int64_t min_mask, int64_t max_spin) {
+  need(in, at::kDouble, "in");
+  need(out, at::kDouble, "out");
+  TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.numel() == out.numel() &&
+                  pad_ptrs.size() == inbox_ptrs.size(),
+              "peer_allreduce_small: mismatched arguments");
+  std::vector<uint32_t*> pads(pad_ptrs.size());
+  std::vector<double*> inboxes(inbox_ptrs.size());
+  for (size_t i = 0; i < pad_ptrs.size(); ++i) {
+    pads[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
+    inboxes[i] = reinterpret_cast<double*>(inbox_ptrs[i]);
+  }
+  check(stb::launch_peer_allreduce_small(
+            pads.data(), inboxes.data(), static_cast<int>(pads.size()), static_cast<int>(rank),
+            static_cast<uint32_t>(epoch), static_cast<int>(slot), in.data_ptr<double>(),
+            out.data_ptr<double>(), static_cast<int>(in.numel()), static_cast<uint32_t>(min_mask),
+            status_ptr(), static_cast<uint32_t>(max_spin), cur_stream()),
+        "peer_allreduce_small");
+}
+
 // ------------------------------------------------------------------ peer memory (CUDA IPC)
 int64_t peer_alloc(int64_t nbytes) {
   void* p = nullptr;
@@ -630,6 +652,7 @@ TORCH_LIBRARY(stb, m) {
   m.def("seq_gather", &seq_gather);
   m.def("seq_reduce_scatter", &seq_reduce_scatter);
   m.def("peer_barrier", &peer_barrier);
+  m.def("peer_allreduce_small", &peer_allreduce_small);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);
   m.def("ipc_handle", &ipc_handle);

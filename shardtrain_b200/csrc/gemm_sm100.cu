@@ -134,7 +134,8 @@ cudaError_t split_buffers(cudaStream_t stream, SplitBuffers* out) {
     if (e != cudaSuccess) return e;
     e = cudaMalloc(&b.counters, units * sizeof(int));
     if (e != cudaSuccess) return e;
-    e = cudaMemset(b.counters, 0, units * sizeof(int));
+    // ordered on the launching stream: the first kernel that uses the counters runs there
+    e = cudaMemsetAsync(b.counters, 0, units * sizeof(int), stream);
     if (e != cudaSuccess) return e;
     it = g_split_buffers.emplace(key, b).first;
   }

@@ -1,5 +1,5 @@
 // Native executor of one Qwen2 decoder layer: the whole forward (11 launches) or backward
-// (27 launches) sequence is issued from C++ in one call, so the host cost per layer is a few
+// (26 launches) sequence is issued from C++ in one call, so the host cost per layer is a few
 // microseconds per launch instead of a Python round trip per kernel.  The math and the launch
 // order are those documented in shardtrain_b200/runtime/fused.py (FusedLayerFn); this file only
 // moves the sequencing off the interpreter.
@@ -101,7 +101,8 @@ SpLink make_link(cudaStream_t st, int* status, c10::ArrayRef<int64_t> pads, int6
   return l;
 }
 
-// x2 [M,H] fp32 -> {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out}
+// x2 [M,H] fp32 -> {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm}; hm = silu(gate) * up
+// is kept for the backward (73 MB per layer at the headline shape) instead of being recomputed
 std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const Tensor& b_qkv,
                                   const Tensor& w_o, const Tensor& w_gu, const Tensor& w_down,
                                   const Tensor& ln1, const Tensor& ln2, const Tensor& cos,
@@ -140,13 +141,14 @@ std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const T
   ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu");
   Tensor out = at::empty({M, H}, f32);
   g.run(hm, w_down, out, false, false, nullptr, &x_mid);
-  return {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out};
+  return {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm};
 }
 
 // Gradient views (down, gate_up, ln2, o, bias, qkv, ln1) point into the unit's gradient slot.
 Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1, const Tensor& h1,
                       const Tensor& qkv, const Tensor& attn, const Tensor& lse, const Tensor& x_mid,
-                      const Tensor& inv2, const Tensor& h2, const Tensor& gu, const Tensor& w_qkv,
+                      const Tensor& inv2, const Tensor& h2, const Tensor& gu, const Tensor& hm,
+                      const Tensor& w_qkv,
                       const Tensor& w_o, const Tensor& w_gu, const Tensor& w_down, const Tensor& ln1,
                       const Tensor& ln2, Tensor g_down, Tensor g_gate_up, Tensor g_ln2, Tensor g_o,
                       Tensor g_bias, Tensor g_qkv, Tensor g_ln1, const Tensor& cos, const Tensor& sin,
@@ -164,8 +166,6 @@ Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1,
 
   Tensor d_out_b = at::empty({M, H}, bf);
   ok(stb::launch_cast_f32_to_bf16(d_out.data_ptr<float>(), d_out_b.data_ptr(), M * H, st), "cast");
-  Tensor hm = at::empty({M, inter}, bf);
-  ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu recompute");
   g.run(d_out_b, hm, g_down, true, true, nullptr, nullptr);                 // dW down
   Tensor d_hm = at::empty({M, inter}, bf);
   g.run(d_out_b, w_down, d_hm, false, true, nullptr, nullptr);              // dX down
@@ -231,7 +231,7 @@ Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1,
 // h1 / h2 / bf16 output gradients live in peer-visible buffers so the peers' gathers (and the
 // backward's re-gathers) read them in place.
 //
-// x2 [B*S/T, H] fp32 -> {inv1, qkv, attn, lse, x_mid, inv2, gu, out}; uses 4 barrier epochs.
+// x2 [B*S/T, H] fp32 -> {inv1, qkv, attn, lse, x_mid, inv2, gu, out, hm}; uses 4 barrier epochs.
 std::vector<Tensor> layer_forward_sp(
     const Tensor& x2, const Tensor& w_qkv, const Tensor& b_qkv, const Tensor& w_o,
     const Tensor& w_gu, const Tensor& w_down, const Tensor& ln1, const Tensor& ln2,
@@ -290,7 +290,7 @@ std::vector<Tensor> layer_forward_sp(
   ok(stb::launch_slot_sum_rmsnorm(recv.data_ptr<float>(), T, recv.stride(0),
                                   x_mid.data_ptr<float>(), out.data_ptr<float>(), nullptr, nullptr,
                                   nullptr, Ml, H, feps, st), "slot sum");
-  return {inv1, qkv, attn, lse, x_mid, inv2, gu, out};
+  return {inv1, qkv, attn, lse, x_mid, inv2, gu, out, hm};
 }
 
 // Backward of the layer above; uses 4 barrier epochs.  d_out / d_mid travel as bf16 through the
@@ -299,7 +299,7 @@ std::vector<Tensor> layer_forward_sp(
 Tensor layer_backward_sp(
     const Tensor& d_out, const Tensor& x2, const Tensor& inv1, const Tensor& qkv,
     const Tensor& attn, const Tensor& lse, const Tensor& x_mid, const Tensor& inv2,
-    const Tensor& gu, const Tensor& w_qkv, const Tensor& w_o, const Tensor& w_gu,
+    const Tensor& gu, const Tensor& hm, const Tensor& w_qkv, const Tensor& w_o, const Tensor& w_gu,
     const Tensor& w_down, const Tensor& ln1, const Tensor& ln2, Tensor g_down, Tensor g_gate_up,
     Tensor g_ln2, Tensor g_o, Tensor g_bias, Tensor g_qkv, Tensor g_ln1, const Tensor& cos,
     const Tensor& sin, const c10::optional<Tensor>& positions, const c10::optional<Tensor>& mask,
@@ -324,8 +324,6 @@ Tensor layer_backward_sp(
   sp.barrier();
   Tensor d_full = at::empty({M, H}, bf), h_full = at::empty({M, H}, bf);
   sp.gather(dob_ptrs, d_full, B, Sl);
-  Tensor hm = at::empty({M, inter}, bf);
-  ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), M, inter, st), "swiglu recompute");
   g.run(d_full, hm, g_down, true, true, nullptr, nullptr);                  // dW down
   Tensor d_hm = at::empty({M, inter}, bf);
   g.run(d_full, w_down, d_hm, false, true, nullptr, nullptr);               // dX down (local cols)

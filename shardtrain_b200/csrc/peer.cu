@@ -377,6 +377,56 @@ __global__ void peer_barrier_kernel(FlagPeers pads, int degree, int rank, uint32
   __threadfence_system();
 }
 
+// Small all-reduce (at most kMetricWidth doubles) in one kernel: thread t pushes this rank's
+// vector into peer t's inbox and publishes the epoch, waits (bounded) for peer t's epoch, then
+// the first n threads combine the inbox rows in rank order -- every rank computes the same bits.
+// Element i is a SUM, or a MIN when bit i of min_mask is set.  Inboxes are double buffered on
+// the epoch's parity: a rank can run at most one reduction ahead of its slowest peer.
+// Inbox layout: [2][kMaxPeers][kMetricWidth] doubles.
+constexpr int kMetricWidth = 16;
+struct InboxPeers {
+  double* p[kMaxPeers];
+};
+
+__global__ void peer_allreduce_small_kernel(FlagPeers pads, InboxPeers inboxes, int degree, int rank,
+                                            uint32_t epoch, int slot, const double* __restrict__ in,
+                                            double* __restrict__ out, int n, uint32_t min_mask,
+                                            int* status, uint32_t max_spin) {
+  const int t = threadIdx.x;
+  const int parity = static_cast<int>(epoch & 1u);
+  if (t < degree) {
+    double* dst = inboxes.p[t] + (static_cast<int64_t>(parity) * kMaxPeers + rank) * kMetricWidth;
+    for (int i = 0; i < n; ++i) dst[i] = in[i];
+    __threadfence_system();
+    uint32_t* remote = pads.p[t] + slot * kMaxPeers + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const uint32_t* mine = pads.p[rank] + slot * kMaxPeers + t;
+    bool seen = false;
+    for (uint32_t i = 0; i < max_spin; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) {
+        seen = true;
+        break;
+      }
+      __nanosleep(64);
+    }
+    if (!seen && status != nullptr) atomicCAS(status, kOk, kErrPeerFlagWait);
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (t < n) {
+    const volatile double* rows =
+        inboxes.p[rank] + static_cast<int64_t>(parity) * kMaxPeers * kMetricWidth;
+    double acc = rows[t];
+    for (int r = 1; r < degree; ++r) {
+      const double v = rows[r * kMetricWidth + t];
+      acc = ((min_mask >> t) & 1u) ? fmin(acc, v) : acc + v;
+    }
+    out[t] = acc;
+  }
+}
+
 bool fill_table(SegTable* t, const SegmentDesc* segs, int n) {
   if (n < 1 || n > kMaxSegs) return false;
   for (int i = 0; i < n; ++i) t->s[i] = segs[i];
@@ -482,6 +532,23 @@ cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree,
   const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 8));
   seq_reduce_scatter_kernel<<<grid, 256, 0, s>>>(fp, degree, rank, residual, out, batch, seq_local,
                                                  cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_allreduce_small(uint32_t* const* flag_pads, double* const* inboxes, int degree,
+                                        int rank, uint32_t epoch, int slot, const double* in,
+                                        double* out, int n, uint32_t min_mask, int* status,
+                                        uint32_t max_spin, cudaStream_t s) {
+  if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree || n < 1 || n > kMetricWidth)
+    return cudaErrorInvalidValue;
+  FlagPeers fp;
+  InboxPeers ip;
+  for (int i = 0; i < degree; ++i) {
+    fp.p[i] = flag_pads[i];
+    ip.p[i] = inboxes[i];
+  }
+  peer_allreduce_small_kernel<<<1, 32, 0, s>>>(fp, ip, degree, rank, epoch, slot, in, out, n,
+                                               min_mask, status, max_spin);
   return cudaGetLastError();
 }
 

@@ -21,7 +21,9 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 
-CHANNEL_SLOTS = {"fsdp_ag": 0, "fsdp_rs": 1, "sp_ag": 2, "sp_rs": 3, "step": 4, "misc": 5}
+CHANNEL_SLOTS = {"fsdp_ag": 0, "fsdp_rs": 1, "sp_ag": 2, "sp_rs": 3, "step": 4, "misc": 5,
+                 "metrics": 6}
+METRIC_WIDTH = 16            # doubles per small all-reduce (csrc/peer.cu: kMetricWidth)
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.uint8: 3}
 
 
@@ -47,6 +49,8 @@ class PeerMemory:
         self._allocations: list[PeerBuffer] = []
         self._opened: list[int] = []
         self.flags = self.alloc(4096) if self.degree > 1 else None
+        # inbox of the small all-reduce: [2 parities][8 senders][METRIC_WIDTH] doubles
+        self.inbox = self.alloc(2 * 8 * METRIC_WIDTH * 8) if self.degree > 1 else None
 
     def alloc(self, nbytes: int) -> PeerBuffer:
         nbytes = -(-int(nbytes) // 512) * 512
@@ -78,6 +82,21 @@ class PeerMemory:
         self.epochs[channel] += 1
         self.ops.peer_barrier(self.flags.ptrs, self.rank, self.epochs[channel],
                               CHANNEL_SLOTS[channel], self.max_spin)
+
+    def all_reduce_small(self, values: torch.Tensor, min_mask: int = 0) -> torch.Tensor:
+        """SUM (or MIN where bit i of `min_mask` is set) of a float64 vector of at most
+        METRIC_WIDTH elements over the group, in one kernel on the current stream; every member
+        gets bit-identical results.  Members must call in the same order."""
+        if values.dtype != torch.float64 or values.numel() > METRIC_WIDTH:
+            raise ValueError("all_reduce_small takes at most 16 float64 values")
+        if self.degree == 1:
+            return values.clone()
+        out = torch.empty_like(values)
+        self.epochs["metrics"] += 1
+        self.ops.peer_allreduce_small(self.flags.ptrs, self.inbox.ptrs, self.rank,
+                                      self.epochs["metrics"], CHANNEL_SLOTS["metrics"],
+                                      values.contiguous(), out, min_mask, self.max_spin)
+        return out
 
     def close(self) -> None:
         if self.degree == 1:

@@ -39,7 +39,7 @@ class UnitMaterialize(torch.autograd.Function):
         comm = unit.runtime.comm
         if comm.streams and comm.diagnostics_enabled:
             comm.event("bridge_backward_stream",
-                       cuda_stream=torch.cuda.current_stream(unit.runtime.device).cuda_stream)
+                       cuda_stream=unit.runtime.comm.current_stream().cuda_stream)
         unit.reduce(grads)
         return (None,) * (1 + len(unit.handles))
 

@@ -133,6 +133,11 @@ class CommunicationCoordinator:
         self._group_info: dict[int, tuple] = {}
         self._log_file = None
         self._log_written = 0
+        # stream_id -> the registered Stream object, for current_stream() below
+        self._stream_by_id = {st.stream_id: st for st in self.streams.values()} if self.streams else {}
+        self._device_index = self.device.index if self.device.type == "cuda" else None
+        if self._device_index is None and self.device.type == "cuda":
+            self._device_index = torch.cuda.current_device()
         if self.streams and diagnostics_enabled:
             self.event(
                 "cuda_stream_registry",
@@ -142,10 +147,22 @@ class CommunicationCoordinator:
             )
 
     # ------------------------------------------------------------------ streams
+    def current_stream(self):
+        """The current CUDA stream of this device.  Inside a step it is almost always one of the
+        runtime's own streams; those are returned from a table keyed by stream id, which skips
+        the device-index normalisation and object construction of `torch.cuda.current_stream`
+        (about a thousand lookups per optimizer step)."""
+        probe = getattr(torch._C, "_cuda_getCurrentStream", None)
+        if probe is not None and self._stream_by_id:
+            known = self._stream_by_id.get(probe(self._device_index)[0])
+            if known is not None:
+                return known
+        return torch.cuda.current_stream(self.device)
+
     def stream_name(self, stream=None) -> str:
         if not self.streams:
             return "cpu"
-        handle = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        handle = (stream or self.current_stream()).cuda_stream
         for name, registered in self.streams.items():
             if registered.cuda_stream == handle:
                 return name
@@ -164,7 +181,7 @@ class CommunicationCoordinator:
     def wait_event(self, event, *, dependency_type, stream=None, **fields):
         if dependency_type not in DEPENDENCY_TYPES:
             raise ValueError("Unknown dependency type")
-        stream = stream or torch.cuda.current_stream(self.device)
+        stream = stream or self.current_stream()
         if not self.diagnostics_enabled:
             stream.wait_event(event)
             return
@@ -282,7 +299,7 @@ class CommunicationCoordinator:
             raise RuntimeError(f"Unknown buffer lease {lease.buffer_id}")
         if self._users.get(lease.buffer_id):
             raise RuntimeError(f"Premature buffer retirement {lease.buffer_id}")
-        stream = torch.cuda.current_stream(self.device) if self.streams else None
+        stream = self.current_stream() if self.streams else None
         if self.diagnostics_enabled:
             if stream is not None:
                 lease.ready_event = torch.cuda.Event()
@@ -417,9 +434,9 @@ class CommunicationCoordinator:
             self.consume(previous, dependency_type="PG_ORDER", consumer_ticket=ticket.op_id,
                          consumer=kind)
         produced = torch.cuda.Event()
-        produced.record(torch.cuda.current_stream(self.device))
+        produced.record(self.current_stream())
         with self.stream_context(channel):
-            here = torch.cuda.current_stream(self.device)
+            here = self.current_stream()
             if self.diagnostics_enabled:
                 self.wait_event(produced, dependency_type="DATA_DEP", consumer_ticket=ticket.op_id,
                                 consumer="collective_input",

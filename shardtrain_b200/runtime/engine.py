@@ -75,7 +75,7 @@ class UnitState:
         comm = self.runtime.comm
         if comm.streams:
             self.lease.fullparam_last_consumer_event = torch.cuda.Event()
-            self.lease.fullparam_last_consumer_event.record(torch.cuda.current_stream(self.runtime.device))
+            self.lease.fullparam_last_consumer_event.record(self.runtime.comm.current_stream())
         notify = getattr(self.runtime.materializer, "released", None)
         if notify is not None:
             notify(self, self.lease.fullparam_last_consumer_event)
@@ -345,7 +345,7 @@ class ShardedRuntime:
         if self.comm.streams:
             handle.grad_ready_event = ticket.ready_event if ticket is not None else torch.cuda.Event()
             if ticket is None:
-                handle.grad_ready_event.record(torch.cuda.current_stream(self.device))
+                handle.grad_ready_event.record(self.comm.current_stream())
         self.comm.event("leaf_grad_committed", param_id=handle.spec.param_id,
                         unit_id=handle.spec.unit_id)
 
@@ -394,7 +394,7 @@ class ShardedRuntime:
     def publish_parameter_shards_ready(self, source):
         if self.comm.streams:
             event = torch.cuda.Event()
-            event.record(torch.cuda.current_stream(self.device))
+            event.record(self.comm.current_stream())
             self.parameter_shards_ready_event = event
             if self.fused is not None:
                 current = source == "optimizer_update" and getattr(
@@ -525,7 +525,7 @@ class ShardedRuntime:
         if not self.comm.streams:
             yield
             return
-        caller = torch.cuda.current_stream(self.device)
+        caller = self.comm.current_stream()
         compute = self.comm.streams["compute"]
         entered = torch.cuda.Event()
         entered.record(caller)

@@ -276,7 +276,7 @@ class FusedExecutor:
 
     def acquire_grad_slot(self, unit):
         if getattr(unit, "grad_slot", None) is None:
-            unit.grad_slot = self.ring.acquire(unit.unit_id, torch.cuda.current_stream(self.runtime.device))
+            unit.grad_slot = self.ring.acquire(unit.unit_id, self.runtime.comm.current_stream())
         return unit.grad_slot
 
     def grad_slot(self, unit):
@@ -597,22 +597,22 @@ class FusedLayerFn(torch.autograd.Function):
             buf = ex.sp_buffers(B, S_full, cfg.num_hidden_layers)
             (h1, h1_ptrs), (h2, h2_ptrs) = buf["h"][index]
             epoch = tp.epochs["sp_ag"]
-            inv1, qkv, attn, lse, x_mid, inv2, gu, out = ops.layer_forward_sp(
+            inv1, qkv, attn, lse, x_mid, inv2, gu, out, hm = ops.layer_forward_sp(
                 x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
                 ex.status, B, S_full, hq, hkv, cfg.rms_norm_eps, h1, h2, h1_ptrs, h2_ptrs,
                 buf["push"], buf["recv"], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
                 tp.max_spin)
             tp.epochs["sp_ag"] = epoch + 4
             ctx.dims = (B, S_full, H, inter)
-            ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu)
+            ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm)
             return out.view(B, S, H)
         # the 11 launches of the forward run from C++ (csrc/layer_executor.cpp)
-        h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out = ops.layer_forward(
+        h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm = ops.layer_forward(
             x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask, ex.status,
             B, S, hq, hkv, cfg.rms_norm_eps)
 
         ctx.dims = (B, S, H, inter)
-        ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu)
+        ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm)
         return out.view(B, S, H)
 
     @staticmethod
@@ -625,7 +625,7 @@ class FusedLayerFn(torch.autograd.Function):
         unit.weight(plan.names[0])  # state / generation check of the backward materialisation
         if ex.tp_degree > 1:
             return FusedLayerFn._backward_sp(ctx, dout, plan)
-        x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu = ctx.saved_tensors
+        x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm = ctx.saved_tensors
         B, S, H, inter = ctx.dims
         M, D, hq, hkv = B * S, 128, ex.hq, ex.hkv
         cos, sin, positions, _ = ctx.tables
@@ -638,9 +638,9 @@ class FusedLayerFn(torch.autograd.Function):
         unit.prefetch_after_input(unit.backward_prefetch_handle, "BWD")
 
         d_out = dout.reshape(M, H).contiguous()
-        # the 27 launches of the backward run from C++ (csrc/layer_executor.cpp)
+        # the 26 launches of the backward run from C++ (csrc/layer_executor.cpp)
         dx = ops.layer_backward(
-            d_out, x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, w_qkv, w_o, w_gu, w_down, ln1,
+            d_out, x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm, w_qkv, w_o, w_gu, w_down, ln1,
             ln2, gv["down"], gv["gate_up"], gv["ln2"], gv["o"], gv["bias"], gv["qkv"], gv["ln1"], cos,
             sin, positions, ctx.mask, ex.status, B, S, hq, hkv)
         return (dx.view(B, S, H), None, None, None, None, None, *([ex.token_grad] * len(plan.names)))
@@ -649,7 +649,7 @@ class FusedLayerFn(torch.autograd.Function):
     def _backward_sp(ctx, dout, plan):
         ex, unit, index = ctx.ex, ctx.unit, ctx.index
         ops, tp = ex.ops, ex.tp_peer
-        x2, inv1, qkv, attn, lse, x_mid, inv2, gu = ctx.saved_tensors
+        x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm = ctx.saved_tensors
         B, S_full, H, inter = ctx.dims
         cos, sin, positions, _ = ctx.tables
         w = ex.layer_operands(plan, index)
@@ -663,7 +663,7 @@ class FusedLayerFn(torch.autograd.Function):
         d_out = dout.reshape(rows, H).contiguous()
         epoch = tp.epochs["sp_ag"]
         dx = ops.layer_backward_sp(
-            d_out, x2, inv1, qkv, attn, lse, x_mid, inv2, gu, w["w_qkv"], w["w_o"], w["w_gu"],
+            d_out, x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm, w["w_qkv"], w["w_o"], w["w_gu"],
             w["w_down"], w["ln1"], w["ln2"], gv["down"], gv["gate_up"], gv["ln2"], gv["o"],
             gv["bias"], gv["qkv"], gv["ln1"], cos, sin, positions, ctx.mask, ex.status, B, S_full,
             ex.hq, ex.hkv, dob, dmb, h1_ptrs, h2_ptrs, dob_ptrs, dmb_ptrs, buf["push"], buf["recv"],

@@ -119,7 +119,7 @@ class Materializer:
         lease.weights = weights
         if self.comm.streams:
             lease.copy_out_ready_event = torch.cuda.Event()
-            lease.copy_out_ready_event.record(torch.cuda.current_stream(self.comm.device))
+            lease.copy_out_ready_event.record(self.comm.current_stream())
         self.comm.event("copy_out_ready", unit_id=unit.unit_id)
         # nothing keeps the packed buffer alive past copy-out
         self.comm.retire(lease.ag_storage)
@@ -137,7 +137,7 @@ class Materializer:
         if self.degree == 1:
             output.copy_(packed)
             if self.comm.streams:
-                here = torch.cuda.current_stream(self.comm.device)
+                here = self.comm.current_stream()
                 packed.record_stream(here)
                 output.record_stream(here)
                 ready = torch.cuda.Event()
@@ -176,7 +176,7 @@ class Materializer:
             output.copy_(packed.narrow(0, self.rank * output.numel(), output.numel()))
         output.div_(self.degree)  # the one FSDP average of every parameter
         if self.comm.streams:
-            output.record_stream(torch.cuda.current_stream(self.comm.device))
+            output.record_stream(self.comm.current_stream())
         self.comm.retire(state["source"])
         self.comm.event("gradient_bucket_consumed", bucket=bucket,
                         producer_ticket=ticket.op_id if ticket else None)
@@ -220,7 +220,7 @@ class Materializer:
                     runtime.commit_gradient(unit.handles[i], shard_grad)
                 if bucket == "norm" and self.comm.streams:
                     done = torch.cuda.Event()
-                    done.record(torch.cuda.current_stream(self.comm.device))
+                    done.record(self.comm.current_stream())
                     self.comm.wait_event(done, dependency_type="DATA_DEP",
                                          stream=self.comm.streams["fsdp_rs"] if runtime.async_grad_rs else None,
                                          consumer=f"autograd_norm_shard/U{unit.unit_id}",

@@ -356,6 +356,15 @@ def sequence_input(runtime, tensor):
 
 def sum_metric(runtime, value, kind):
     """SUM of a scalar over the SP group (when SP) and the FSDP group."""
+    fused = getattr(runtime, "fused", None)
+    if fused is not None and fused.reduce_peer.degree > 1:
+        # sm_100a executor: one kernel over peer memory covers the whole mesh (with SP the TP
+        # ranks hold different sequence slices, so the sum runs over F x T; without a TP axis the
+        # mesh is the FSDP group)
+        total = fused.reduce_peer.all_reduce_small(value.detach().to(torch.float64).reshape(1))
+        if runtime.comm.diagnostics_enabled:
+            runtime.comm.event("metric_allreduce", kind=kind, backend="peer_kernel")
+        return total[0].to(value.dtype)
     result = value.detach().clone()
     hops = []
     if runtime.sp:

@@ -80,6 +80,10 @@ class QwenTrainer:
             finite = torch.isfinite(runtime.grad_arena).all().to(torch.int32)
         finite.mul_(torch.isfinite(reported).to(torch.int32))
         runtime.comm.unit_id, runtime.comm.phase = None, "AMP"
+        if runtime.fused is not None and runtime.fused.reduce_peer.degree > 1:
+            voted = runtime.fused.reduce_peer.all_reduce_small(
+                finite.to(torch.float64).reshape(1), min_mask=1)
+            return voted[0].to(torch.int32)
         m = runtime.materializer
         for role, group, degree, channel in (("tp", runtime.tp.process_group, runtime.tp.degree, "sp_rs"),
                                              ("fsdp", m.group, m.degree, "fsdp_rs")):

@@ -59,3 +59,31 @@ def test_arena_plan_alignment_and_tables():
                                           (handles[1].arena_offset + 4, handles[1].arena_offset + 5)]
     table = segment_table(handles, {"p0": 0, "p1": 8, "p2": 24}, {"p0"})
     assert table.shape == (3, 5) and table[0].tolist() == [0, 3, 5, 0, 1]
+
+
+def test_arena_offsets_keep_bf16_shadows_16_byte_aligned():
+    """Shard offsets are multiples of 8 elements: 32 bytes in the FP32 arenas and 16 bytes in
+    the bf16 shadow arena that mirrors them (vector loads of the gather kernel)."""
+    plan = ArenaPlan()
+    for spec in specs_for([(5,), (3, 3), (2,), (17, 3)], 2):
+        assert plan.add(spec) % 8 == 0
+    assert plan.padded_total() % 8 == 0
+
+
+def test_reduce_table_marks_tp_replicated_parameters():
+    """Flag bit 1 of a reduce table row tells the reduce-scatter kernel to sum that parameter
+    over the whole F x T mesh; gather tables never carry it."""
+    split = ParameterSpec.create("w", 0, torch.empty(4, 6), (8, 6), "column", 2)
+    repl = ParameterSpec.create("norm", 0, torch.empty(6), (6,), "replicated", 2)
+    handles = []
+    plan = ArenaPlan()
+    for spec in (split, repl):
+        h = ShardedParameter(spec, None)
+        h.arena_offset = plan.add(spec)
+        handles.append(h)
+    offsets_ = {"w": 0, "norm": 24}
+    reduce = segment_table(handles, offsets_, set(), mark_replicated=True)
+    assert reduce[:, 4].tolist() == [0, 2]
+    gather = segment_table(handles, offsets_, {"norm"})
+    assert gather[:, 4].tolist() == [0, 1]
+    assert reduce[1].tolist()[:4] == [handles[1].arena_offset, 3, 6, 24]
