@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "api.h"
 #include "common.cuh"
@@ -434,13 +435,24 @@ bool fill_table(SegTable* t, const SegmentDesc* segs, int n) {
   return true;
 }
 
+int g_ctas_per_sm = 0;   // 0: read STB_COLLECTIVE_CTAS_PER_SM once (default below)
 int chunks_for(const SegmentDesc* segs, int n, bool per_shard) {
+  if (g_ctas_per_sm == 0) {
+    const char* env = getenv("STB_COLLECTIVE_CTAS_PER_SM");
+    g_ctas_per_sm = env != nullptr ? std::max(1, atoi(env)) : 48;   // measured: 8..48 equal, 4 slower
+  }
+  const int kCtasPerSm = g_ctas_per_sm;
+  // grid.x of a (chunks, segments) grid.  The kernels loop over chunks, so the grid only has to
+  // be large enough to keep the memory system busy; STB_COLLECTIVE_CTAS_PER_SM bounds the total
+  // (CTAs per SM over all segments).  The compute stream has the higher priority, so a larger
+  // grid does not keep GEMMs launched meanwhile from being placed.
   int64_t most = 1;
   for (int i = 0; i < n; ++i) {
     const int64_t len = per_shard ? segs[i].q : segs[i].numel;
     most = std::max<int64_t>(most, (len + kChunk - 1) / kChunk);
   }
-  return static_cast<int>(std::min<int64_t>(most, 148 * 4));
+  const int64_t budget = std::max<int64_t>(1, (148 * kCtasPerSm) / std::max(1, n));
+  return static_cast<int>(std::min<int64_t>(most, budget));
 }
 
 }  // namespace

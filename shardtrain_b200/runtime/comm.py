@@ -105,8 +105,12 @@ class CommunicationCoordinator:
         self.communication_policy = communication_policy
         self.diagnostics_enabled = diagnostics_enabled
         self.device, self.rank = torch.device(device), rank
+        # The compute stream gets the higher hardware priority: a collective kernel that is
+        # already running on a side stream then cannot keep a newly launched GEMM waiting until
+        # every one of its own pending thread blocks has been placed.
         self.streams = (
-            {name: torch.cuda.Stream(device=self.device) for name in CHANNELS}
+            {name: torch.cuda.Stream(device=self.device, priority=-1 if name == "compute" else 0)
+             for name in CHANNELS}
             if self.device.type == "cuda" else {}
         )
         self.directory = Path(directory) if directory else None
