@@ -95,6 +95,26 @@ def _locked(method):
     return call
 
 
+class StreamScope:
+    """`with` block that makes one of the coordinator's streams current on its device.  Same
+    effect as `torch.cuda.stream(...)` for a stream of the current device, without that
+    helper's device-index lookups (several hundred scopes are entered per optimizer step)."""
+
+    __slots__ = ("coordinator", "stream", "previous")
+
+    def __init__(self, coordinator, stream):
+        self.coordinator, self.stream, self.previous = coordinator, stream, None
+
+    def __enter__(self):
+        self.previous = self.coordinator.current_stream()
+        torch.cuda.set_stream(self.stream)
+        return self.stream
+
+    def __exit__(self, *exc):
+        torch.cuda.set_stream(self.previous)
+        return False
+
+
 class CommunicationCoordinator:
     channels = CHANNELS
 
@@ -173,7 +193,7 @@ class CommunicationCoordinator:
         return "caller"
 
     def stream_context(self, channel):
-        return torch.cuda.stream(self.streams[channel]) if self.streams else nullcontext()
+        return StreamScope(self, self.streams[channel]) if self.streams else nullcontext()
 
     def dependency(self, dependency_type, *, producer_ticket=None, consumer_ticket=None, **fields):
         if dependency_type not in DEPENDENCY_TYPES:
@@ -218,10 +238,13 @@ class CommunicationCoordinator:
         return rows
 
     # ------------------------------------------------------------------ event log
-    @_locked
     def event(self, event_type, **fields):
-        if not self.diagnostics_enabled:
+        if not self.diagnostics_enabled:     # the common case takes no lock
             return
+        self._record_event(event_type, **fields)
+
+    @_locked
+    def _record_event(self, event_type, **fields):
         row = dict(step_id=self.step_id, rank=self.rank, unit_id=self.unit_id, phase=self.phase,
                    materialization_generation=self.generation, CPU_timestamp=time.monotonic(),
                    event_type=event_type, generation=self.generation, **EVENT_DEFAULTS)
@@ -521,7 +544,7 @@ class CommunicationCoordinator:
                                     consumer="collective_input", wait_stream=channel, producer_stream=name)
             for event in after_events:
                 stream.wait_event(event)
-            with torch.cuda.stream(stream):
+            with StreamScope(self, stream):
                 launch()
             if self.diagnostics_enabled:
                 self.event("work_issued", op_id=ticket.op_id, work_issued=False, issue_stream=channel)
