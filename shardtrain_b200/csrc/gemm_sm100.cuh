@@ -246,6 +246,25 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       const uint32_t tmem_d = tmem_base + ab * BN;
       const int64_t g_row = static_cast<int64_t>(m0) + row;
       const bool row_ok = ok && g_row < M;
+      // Scatter epilogue: after the shared-memory transpose lane l stores rows 4k + l/8 (k = 0..7)
+      // of its warp's 32-row band; their destinations (owner buffer, row inside it) do not
+      // depend on the column chunk, so they are resolved once per tile.
+      float* scatter_row[8];
+      if (ep.scatter_degree > 1) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int gr = m0 + q * 32 + k * 4 + (lane >> 3);
+          scatter_row[k] = nullptr;
+          if (ok && gr < M) {
+            const int b = gr / ep.scatter_seq;
+            const int pos = gr - b * ep.scatter_seq;
+            const int owner = pos / ep.scatter_seq_local;
+            scatter_row[k] = ep.scatter_out[owner] +
+                             (static_cast<int64_t>(b) * ep.scatter_seq_local +
+                              (pos - owner * ep.scatter_seq_local)) * ep.ldo;
+          }
+        }
+      }
       // one 32-column chunk of this thread's accumulator row -> output (all epilogue variants)
       auto emit = [&](uint32_t (&r)[32], int c) {
         const int col0 = n0 + c * 32;
@@ -274,16 +293,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
             const int rr = k * 4 + (lane >> 3);
             const float4 x =
                 *reinterpret_cast<const float4*>(stage + rr * 32 + ((seg ^ (rr & 7)) << 2));
-            const int64_t gr = static_cast<int64_t>(m0) + q * 32 + rr;
-            if (ok && gr < M && col0 + seg * 4 < N) {
-              const int64_t b = gr / ep.scatter_seq;
-              const int pos = static_cast<int>(gr - b * ep.scatter_seq);
-              const int owner = pos / ep.scatter_seq_local;
-              float* o = ep.scatter_out[owner] +
-                         (b * ep.scatter_seq_local + (pos - owner * ep.scatter_seq_local)) * ep.ldo +
-                         col0 + seg * 4;
-              *reinterpret_cast<float4*>(o) = x;
-            }
+            if (scatter_row[k] != nullptr && col0 + seg * 4 < N)
+              *reinterpret_cast<float4*>(scatter_row[k] + col0 + seg * 4) = x;
           }
           __syncwarp();
           return;

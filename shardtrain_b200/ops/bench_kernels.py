@@ -51,13 +51,16 @@ def timed(fn, warmup, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "reduce_scatter_adamw", "gather_params", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_scatter", "attention", "reduce_scatter_adamw",
+                                       "gather_params", "gather_shadow", "rmsnorm"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=17920)
     ap.add_argument("--k", type=int, default=1536)
     ap.add_argument("--a-mn", type=int, default=0)
     ap.add_argument("--b-mn", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--owners", type=int, default=2, help="gemm_scatter: sequence owners (local buffers)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--hq", type=int, default=12)
@@ -74,11 +77,23 @@ def main():
         A = torch.randn(a.k if a.a_mn else a.m, a.m if a.a_mn else a.k, device=dev).bfloat16()
         B = torch.randn(a.k if a.b_mn else a.n, a.n if a.b_mn else a.k, device=dev).bfloat16()
         C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
-        ms = timed(lambda: ops.gemm(A, B, C, bool(a.a_mn), bool(a.b_mn), None, None, False, 1.0, a.bn),
-                   a.warmup, a.iters, flush=False)
+        ms = timed(lambda: ops.gemm(A, B, C, bool(a.a_mn), bool(a.b_mn), None, None, False, 1.0, a.bn,
+                                    a.split_k), a.warmup, a.iters, flush=False)
         tflops = 2 * a.m * a.n * a.k / ms / 1e9
         out.update(shape=[a.m, a.n, a.k], a_mn=a.a_mn, b_mn=a.b_mn, ms=ms, tflops=tflops,
                    frac_of_burst_cublas=tflops / burst, frac_of_sustained_cublas=tflops / sustained)
+    elif a.kernel == "gemm_scatter":
+        # row-parallel GEMM with the sequence-scatter epilogue; the owners' receive buffers are
+        # local tensors here (the multi-GPU path passes peer pointers to the same kernel)
+        A = torch.randn(a.m, a.k, device=dev).bfloat16()
+        B = torch.randn(a.k if a.b_mn else a.n, a.n if a.b_mn else a.k, device=dev).bfloat16()
+        dest = [torch.empty(a.m // a.owners, a.n, device=dev) for _ in range(a.owners)]
+        ptrs = [d.data_ptr() for d in dest]
+        ms = timed(lambda: ops.gemm_scatter(A, B, ptrs, a.seq, False, bool(a.b_mn), a.bn), a.warmup,
+                   a.iters, flush=False)
+        tflops = 2 * a.m * a.n * a.k / ms / 1e9
+        out.update(shape=[a.m, a.n, a.k], owners=a.owners, seq=a.seq, ms=ms, tflops=tflops,
+                   output_gbs=a.m * a.n * 4 / ms / 1e6, frac_of_sustained_cublas=tflops / sustained)
     elif a.kernel == "attention":
         D, W = 128, (a.hq + 2 * a.hkv) * 128
         rows = a.batch * a.seq
@@ -87,15 +102,27 @@ def main():
         do = torch.randn_like(o)
         lse = torch.empty(a.batch, a.hq, a.seq, device=dev)
         delta, dqkv = torch.empty_like(lse), torch.empty_like(qkv)
+        # scratch for the dK/dV head-group split (same sizing as the layer executor)
+        scratch = torch.empty((a.hq // a.hkv) * rows * 2 * a.hkv * D, device=dev)
         scale = 1 / math.sqrt(D)
         fwd = timed(lambda: ops.attention_fwd(qkv, o, lse, None, a.batch, a.seq, a.hq, a.hkv, scale),
                     a.warmup, a.iters, flush=True)
-        bwd = timed(lambda: ops.attention_bwd(qkv, o, do, lse, delta, dqkv, delta, None, a.batch, a.seq,
+        bwd = timed(lambda: ops.attention_bwd(qkv, o, do, lse, delta, dqkv, scratch, None, a.batch, a.seq,
                                               a.hq, a.hkv, scale), a.warmup, a.iters, flush=True)
         flops = 4 * a.batch * a.hq * a.seq * a.seq * D / 2      # causal: half the score matrix
         out.update(batch=a.batch, seq=a.seq, hq=a.hq, hkv=a.hkv, fwd_ms=fwd, bwd_ms=bwd,
                    fwd_tflops=flops / fwd / 1e9, bwd_tflops=2.5 * flops / bwd / 1e9,
                    fwd_frac_of_burst_cublas=flops / fwd / 1e9 / burst)
+    elif a.kernel == "gather_shadow":
+        n = a.numel // 8 * 8
+        table = torch.tensor([[0, n, n, 0, 0]], dtype=torch.int64)
+        shard = torch.randn(n, device=dev)
+        shadow = shard.bfloat16()
+        fb, ff = torch.empty(n, device=dev, dtype=torch.bfloat16), torch.empty(4, device=dev)
+        ms = timed(lambda: ops.gather_params([shard.data_ptr()], table, fb, ff, [shadow.data_ptr()]),
+                   a.warmup, a.iters, True)
+        moved = n * (2 + 2)
+        out.update(numel=n, ms=ms, gbs=moved / ms / 1e6, frac_of_copy_peak=moved / ms / 1e6 / hbm)
     elif a.kernel in ("reduce_scatter_adamw", "gather_params"):
         n = a.numel // 4 * 4
         table = torch.tensor([[0, n, n, 0, 0]], dtype=torch.int64)
