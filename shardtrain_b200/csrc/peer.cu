@@ -452,7 +452,8 @@ int chunks_for(const SegmentDesc* segs, int n, bool per_shard) {
     most = std::max<int64_t>(most, (len + kChunk - 1) / kChunk);
   }
   const int64_t budget = std::max<int64_t>(1, (148 * kCtasPerSm) / std::max(1, n));
-  return static_cast<int>(std::min<int64_t>(most, budget));
+  // and never more than four CTAs per SM for one segment: more only adds scheduling work
+  return static_cast<int>(std::min<int64_t>({most, budget, static_cast<int64_t>(148 * 4)}));
 }
 
 }  // namespace
