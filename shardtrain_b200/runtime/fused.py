@@ -234,7 +234,17 @@ class FusedExecutor:
         for unit in rt.units:
             plan = mat.plans[unit.unit_id] = build_plan(unit)
             largest = max(largest, plan.grad_numel)
-            plan.full_bf16 = torch.empty(max(plan.bf16_numel, 8), dtype=torch.bfloat16, device=rt.device)
+            if self._alias_shadow(unit, plan):
+                # FSDP degree 1: a "gathered" matrix is the shard itself, and the shadow arena
+                # already holds it in bf16 at the offsets the kernels want -- the unit's weight
+                # buffer is a window of the shadow, only the FP32 vectors are still copied
+                lo = rt.plan.unit_ranges[unit.unit_id][0]
+                plan.full_bf16 = self.shadow.narrow(0, lo, max(plan.bf16_numel, 8))
+                keep = plan.gather_table[:, 4].bitwise_and(1).ne(0)
+                plan.gather_table = plan.gather_table[keep].contiguous()
+            else:
+                plan.full_bf16 = torch.empty(max(plan.bf16_numel, 8), dtype=torch.bfloat16,
+                                             device=rt.device)
             plan.full_fp32 = torch.empty(max(plan.fp32_numel, 4), dtype=torch.float32, device=rt.device)
             plan.weights = plan.views(plan.full_bf16, plan.full_fp32)
             base = 64 * unit.unit_id
@@ -245,6 +255,16 @@ class FusedExecutor:
         mat.bind(self.ops, self)
         ranges = rt.padding_ranges or [(0, 0)]
         self._pad_ranges = torch.tensor(ranges, dtype=torch.int64, device=rt.device).reshape(-1)
+
+    def _alias_shadow(self, unit, plan) -> bool:
+        """True when the unit's bf16 matrices sit in the shard arena exactly as in its fused
+        weight buffer (single FSDP member, matrices first and in fused order)."""
+        if self.peer.degree != 1:
+            return False
+        lo = self.runtime.plan.unit_ranges[unit.unit_id][0]
+        matrices = [h for h in unit.handles if h.spec.param_id not in plan.fp32_names]
+        return bool(matrices) and all(
+            h.arena_offset - lo == plan.param_offsets[h.spec.param_id] for h in matrices)
 
     def finish_registration(self):
         rt = self.runtime

@@ -272,8 +272,9 @@ class PeerMaterializer:
             # the shards depend on the optimizer's writes (and on every peer having finished
             # its own), never on activations queued on the compute stream
             runtime.wait_parameter_shards_ready()
-            self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32,
-                                   self.arenas.shadow_peer_ptrs)
+            if plan.gather_table.numel():     # empty when the unit's buffer aliases the shadow
+                self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32,
+                                       self.arenas.shadow_peer_ptrs)
 
         # a buffer may be re-gathered only after its last reader on the compute stream
         after = (plan.last_reader,) if plan.last_reader is not None else ()

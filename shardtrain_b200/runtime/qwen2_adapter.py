@@ -128,6 +128,19 @@ def verify_same_source(runtime, model):
                          "use the same seed/checkpoint/weights")
 
 
+_FUSED_ORDER = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
+                "gate_proj.weight", "up_proj.weight", "down_proj.weight",
+                "q_proj.bias", "k_proj.bias", "v_proj.bias",
+                "input_layernorm.weight", "post_attention_layernorm.weight")
+
+
+def _fused_rank(name):
+    for position, suffix in enumerate(_FUSED_ORDER):
+        if name.endswith(suffix):
+            return position
+    return len(_FUSED_ORDER)
+
+
 def _plan_parameters(model, tied):
     """(unit kind, [(hf name, owning module, attribute, tp dim)]) for every unit, in unit order."""
     core = model.model
@@ -146,6 +159,10 @@ def _plan_parameters(model, tied):
                 entries.append((f"{prefix}{parent_name}.{n}.weight", linear, "weight", dim))
                 if linear.bias is not None:
                     entries.append((f"{prefix}{parent_name}.{n}.bias", linear, "bias", 0))
+        # shard arena order inside the unit = the fused layout of the sm_100a executor (matrices
+        # q|k|v, o, gate|up, down, then the vectors): with FSDP degree 1 the bf16 shadow of the
+        # arena then *is* the unit's materialised weight buffer and nothing has to be gathered
+        entries.sort(key=lambda e: _fused_rank(e[0]))
         plan.append(("layer", entries))
     plan.append(("norm", [("model.norm.weight", core.norm, "weight", None)]))
     if not tied:
