@@ -1,0 +1,286 @@
+"""PyTorch-native comparison engine: the same Qwen2 model trained with `fully_shard` (FSDP2) only.
+
+Nothing of this package's runtime, kernels or collectives is used here -- parameter ownership,
+all-gathers and gradient reduce-scatters are PyTorch's -- so a run of this module next to
+`qwen2_benchmark` separates "what the model costs on this machine" from "what the runtime adds".
+It follows the reference's native baseline (`src/sharded_runtime/training/qwen2_native_baseline.py:
+281-344, 392-505, 558-790`): one FSDP group per decoder layer (resharded after forward), the final
+norm and the root (tied embedding / head owner) kept unsharded after forward, FP32 parameters and
+FP32 gradient reduction (`MixedPrecisionPolicy(param_dtype=None, reduce_dtype=float32)`), explicit
+forward / backward prefetch lists, autocast compute, AdamW(foreach=False), the same name-stable
+initialisation, the same synthetic batch and the same record layout (`benchmark.rank{r}.json`,
+`"engine": "native_fsdp2"`).
+
+Scope: FSDP meshes (T = 1).  The reference's DTensor tensor/sequence-parallel plan is not
+reproduced; a TP mesh is refused with a configuration error.
+"""
+
+from __future__ import annotations
+
+import argparse
+import math
+import time
+from dataclasses import asdict, dataclass
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from shardtrain_b200.config import Config, ConfigError, load_config
+from shardtrain_b200.distributed.context import WorkerEnvironment
+from shardtrain_b200.launch.bootstrap import WorkerSession
+from shardtrain_b200.models.qwen2 import causal_lm_loss_parts, rotary_inverse_frequencies
+from shardtrain_b200.models.qwen2_factory import build_qwen_model
+from shardtrain_b200.observability.metadata import write_json
+from shardtrain_b200.runtime.qwen2_adapter import source_tensor
+from shardtrain_b200.training.performance import qwen_performance_summary
+from shardtrain_b200.training.qwen2_benchmark import (memory_counters, percentile,
+                                                      software_versions)
+from shardtrain_b200.training.qwen2_precision import resolve_qwen_compute_dtype
+
+
+def materialize_same_source(model, device) -> None:
+    """Replace the meta parameters by the name-stable values the sharded runtime would shard
+    (one CPU tensor at a time), keeping the tied embedding / head alias."""
+    tied = model.lm_head.weight is model.model.embed_tokens.weight
+    for name, parameter in list(model.named_parameters()):
+        value = source_tensor(model, name, parameter).to(device=device, dtype=torch.float32)
+        owner = model
+        *path, leaf = name.split(".")
+        for part in path:
+            owner = getattr(owner, part)
+        owner._parameters[leaf] = torch.nn.Parameter(value)
+    if tied:
+        model.lm_head._parameters["weight"] = model.model.embed_tokens.weight
+    # the only buffer of the model: the rotary inverse frequencies, a pure function of the config
+    rotary = model.model.rotary_emb
+    rotary.register_buffer("inv_freq", rotary_inverse_frequencies(
+        model.config.head_dim, model.config.rope_theta, device), persistent=False)
+    for name, buffer in list(model.named_buffers()):
+        if buffer.device.type == "meta":
+            raise RuntimeError(f"Buffer {name} cannot be materialised from a meta tensor")
+
+
+def shard_with_fsdp2(model, mesh, *, reshard_after_forward, forward_prefetch, backward_prefetch):
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    policy = MixedPrecisionPolicy(param_dtype=None, reduce_dtype=torch.float32)
+    layers = list(model.model.layers)
+    for layer in layers:
+        fully_shard(layer, mesh=mesh, reshard_after_forward=reshard_after_forward, mp_policy=policy)
+    fully_shard(model.model.norm, mesh=mesh, reshard_after_forward=False, mp_policy=policy)
+    fully_shard(model, mesh=mesh, reshard_after_forward=False, mp_policy=policy)
+    if forward_prefetch and layers:
+        model.set_modules_to_forward_prefetch([layers[0]])
+        for current, following in zip(layers, layers[1:] + [model.model.norm]):
+            current.set_modules_to_forward_prefetch([following])
+    if backward_prefetch and layers:
+        model.model.norm.set_modules_to_backward_prefetch([layers[-1]])
+        for index in range(1, len(layers)):
+            layers[index].set_modules_to_backward_prefetch([layers[index - 1]])
+    return {
+        "parameter_materialization_dtype": "torch.float32",
+        "gradient_reduce_dtype": "torch.float32",
+        "decoder_units": len(layers),
+        "decoder_reshard_after_forward": reshard_after_forward,
+        "final_norm_reshard_after_forward": False,
+        "root_reshard_after_forward": False,
+        "explicit_forward_prefetch": forward_prefetch,
+        "explicit_backward_prefetch": backward_prefetch,
+        "differences": [
+            "native FSDP shards dimension 0 of every parameter; this package pads the flattened "
+            "TP-local tensor",
+            "native FSDP2 owns its communication streams and its backward prefetch order",
+        ],
+    }
+
+
+@dataclass
+class NativeStepResult:
+    step: int
+    loss: float
+    valid_tokens: int
+    overflow: bool
+    accumulation_steps: int
+
+
+class NativeQwenTrainer:
+    """Gradient accumulation with a global-token loss denominator, finite vote, AdamW."""
+
+    def __init__(self, model, lr, *, dtype, optimizer, accumulation_steps, device, group):
+        self.model, self.device, self.group = model, device, group
+        self.accumulation_steps, self.step_id = accumulation_steps, 0
+        self.compute_dtype = resolve_qwen_compute_dtype(dtype, device)
+        if dtype == "fp16":
+            raise ConfigError("The native baseline runs fp32 or bf16 (no loss scaler)")
+        make = {"adamw": lambda p: torch.optim.AdamW(p, lr=lr, foreach=False),
+                "sgd": lambda p: torch.optim.SGD(p, lr=lr, foreach=False)}
+        if optimizer not in make:
+            raise ConfigError("Qwen optimizer must be sgd or adamw")
+        self.optimizer = make[optimizer](model.parameters())
+
+    def _sum(self, value):
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(value, group=self.group)
+        return value
+
+    def train_step(self, input_ids, labels, *, attention_mask=None, position_ids=None):
+        batch = input_ids.shape[0]
+        if batch % self.accumulation_steps:
+            raise ValueError("batch must divide accumulation_steps")
+        micro = batch // self.accumulation_steps
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        count = self._sum(labels[:, 1:].ne(-100).sum().to(torch.float64)).clamp_min(1)
+        self.optimizer.zero_grad(set_to_none=True)
+        total = torch.zeros((), device=self.device, dtype=torch.float64)
+        enabled = self.compute_dtype != torch.float32
+        for index in range(self.accumulation_steps):
+            lo, hi = index * micro, (index + 1) * micro
+            mask = attention_mask[lo:hi] if attention_mask is not None else None
+            with torch.autocast(self.device.type, dtype=self.compute_dtype, enabled=enabled):
+                out = self.model(input_ids[lo:hi], attention_mask=mask, position_ids=position_ids)
+            part, _ = causal_lm_loss_parts(out.logits, labels[lo:hi])
+            # FSDP averages gradients over the group: scale so the result is the global mean
+            (part * world / count.to(part.dtype)).backward()
+            total += part.detach().to(torch.float64)
+        loss = self._sum(total) / count
+        finite = torch.isfinite(loss).to(torch.float64)
+        for parameter in self.model.parameters():
+            grad = parameter.grad
+            if grad is not None:
+                local = grad.to_local() if hasattr(grad, "to_local") else grad
+                finite = finite * torch.isfinite(local).all().to(torch.float64)
+        if dist.is_initialized() and world > 1:
+            dist.all_reduce(finite, op=dist.ReduceOp.MIN, group=self.group)
+        row = torch.stack([finite, loss, count]).cpu().tolist()
+        overflow = not bool(row[0])
+        if not overflow:
+            self.optimizer.step()
+        self.step_id += 1
+        return NativeStepResult(self.step_id, float(row[1]), int(row[2]), overflow,
+                                self.accumulation_steps)
+
+
+def run(config: Config, *, warmup: int = 0, peak_tflops_per_gpu: float | None = None) -> dict:
+    """Train with FSDP2 and write `benchmark.rank{r}.json` (same timing protocol as
+    `qwen2_benchmark.run`: barrier, host wall time including the device synchronise, max over
+    ranks reduced outside the timer, CUDA-event span)."""
+    if config.model.model_type != "qwen2":
+        raise ConfigError("The native baseline requires model.model_type=qwen2")
+    if config.parallel.tp_degree != 1 or config.parallel.sp_enabled:
+        raise ConfigError("The native baseline covers FSDP meshes only (tp_degree 1, no SP)")
+    if type(warmup) is not int or warmup < 0:
+        raise ConfigError("warmup must be a nonnegative integer")
+    rank = WorkerEnvironment.read().rank
+    if (Path(config.debug.output_dir) / f"benchmark.rank{rank}.json").exists():
+        raise ConfigError(f"Output directory already contains rank {rank} experiment records; "
+                          "choose a new --debug.output_dir")
+    with WorkerSession(config, "runtime") as session:
+        from torch.distributed.device_mesh import init_device_mesh
+
+        ctx, tc, rc = session.context, config.training, config.runtime
+        device, world = ctx.device, session.worker.world_size
+        torch.manual_seed(tc.seed + rank)
+        payload = {
+            "engine": "native_fsdp2", "status": "initializing", "rank": rank, "world_size": world,
+            "versions": software_versions(), "device": str(device), "dtype": tc.dtype,
+            "optimizer": tc.optimizer, "micro_batch": tc.local_batch_size,
+            "global_batch": tc.local_batch_size * tc.accumulation_steps * config.parallel.fsdp_degree,
+            "sequence_length": config.model.seq_len, "accumulation_steps": tc.accumulation_steps,
+            "warmup": warmup, "steady_steps_requested": tc.steps, "errors": [],
+        }
+        rows, failure = [], None
+        try:
+            model = build_qwen_model(config.model, tc.seed)
+            parameters = sum(p.numel() for p in model.parameters())
+            materialize_same_source(model, device)
+            if session.worker.launched:
+                mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("fsdp",))
+                payload["sharding"] = shard_with_fsdp2(
+                    model, mesh, reshard_after_forward=rc.reshard_after_forward,
+                    forward_prefetch=rc.forward_prefetch, backward_prefetch=rc.backward_prefetch)
+            trainer = NativeQwenTrainer(model, tc.lr, dtype=tc.dtype, optimizer=tc.optimizer,
+                                        accumulation_steps=tc.accumulation_steps, device=device,
+                                        group=dist.group.WORLD if session.worker.launched else None)
+            draw = torch.Generator().manual_seed(tc.seed + ctx.coordinate.fsdp)
+            ids = torch.randint(model.config.vocab_size,
+                                (tc.local_batch_size * tc.accumulation_steps, config.model.seq_len),
+                                generator=draw).to(device)
+            labels, mask = ids.clone(), torch.ones_like(ids)
+            positions = torch.arange(config.model.seq_len, device=device).unsqueeze(0)
+            for _ in range(warmup):
+                trainer.train_step(ids, labels, attention_mask=mask, position_ids=positions)
+            if device.type == "cuda":
+                torch.cuda.synchronize(device)
+                torch.cuda.reset_peak_memory_stats(device)
+            payload["status"] = "running"
+            for index in range(tc.steps):
+                if dist.is_initialized():
+                    dist.barrier()
+                span = None
+                if device.type == "cuda":
+                    span = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    span[0].record()
+                t0 = time.perf_counter()
+                result = trainer.train_step(ids, labels, attention_mask=mask, position_ids=positions)
+                if span is not None:
+                    span[1].record()
+                    torch.cuda.synchronize(device)
+                seconds = time.perf_counter() - t0
+                slowest = torch.tensor(seconds, dtype=torch.float64, device=device)
+                if dist.is_initialized() and world > 1:
+                    dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+                if not math.isfinite(result.loss):
+                    raise FloatingPointError("Nonfinite native baseline loss")
+                rows.append({**asdict(result), "measured_step": index, "seconds": seconds,
+                             "max_rank_seconds": float(slowest),
+                             "cuda_elapsed_ms": span[0].elapsed_time(span[1]) if span else None,
+                             "tokens_per_second": result.valid_tokens / float(slowest),
+                             **memory_counters(device)})
+                session.logger.info("native step=%d loss=%.8f tokens=%d max_rank_seconds=%.6f",
+                                    result.step, result.loss, result.valid_tokens, float(slowest))
+            payload["status"] = "completed"
+        except BaseException as exc:  # noqa: BLE001 - recorded, then re-raised
+            failure = exc
+            payload["status"] = "failed"
+            payload["errors"].append(repr(exc))
+        finally:
+            durations = [r["max_rank_seconds"] for r in rows]
+            payload.update({
+                "steps": rows, "steady_steps_completed": len(rows),
+                "step_seconds_p50": percentile(durations, 0.5),
+                "step_seconds_p95": percentile(durations, 0.95),
+                "tokens_per_second": (sum(r["valid_tokens"] for r in rows) / sum(durations)
+                                      if durations else None),
+                **memory_counters(device),
+            })
+            if rows:
+                cfg = model.config
+                payload["performance"] = qwen_performance_summary(
+                    parameter_numel=parameters, layers=cfg.num_hidden_layers,
+                    hidden_size=cfg.hidden_size, sequence_length=config.model.seq_len,
+                    global_batch=payload["global_batch"], steps=rows, world_size=world,
+                    peak_tflops_per_gpu=peak_tflops_per_gpu)
+            write_json(session.directory / f"benchmark.rank{rank}.json", payload)
+        if failure is not None:
+            raise failure
+        return payload
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.splitlines()[0], allow_abbrev=False,
+                                     epilog="Config overrides: --section.field value")
+    parser.add_argument("--config", default="configs/qwen25_tiny.yaml")
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--peak-tflops-per-gpu", type=float, default=None)
+    args, overrides = parser.parse_known_args(argv)
+    try:
+        run(load_config(args.config, overrides), warmup=args.warmup,
+            peak_tflops_per_gpu=args.peak_tflops_per_gpu)
+    except ConfigError as exc:
+        parser.error(str(exc))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -155,3 +155,40 @@ def test_qwen_benchmark_two_ranks_fsdp(tmp_path):
     assert all(r["status"] == "completed" and r["global_batch"] == 4 for r in records)
     assert records[0]["steps"][0]["max_rank_seconds"] == records[1]["steps"][0]["max_rank_seconds"]
     assert records[0]["steps"][1]["loss"] == pytest.approx(records[1]["steps"][1]["loss"])
+
+
+def test_native_fsdp2_baseline_matches_the_sharded_runtime_single_rank(tmp_path):
+    """Same model, same name-stable initialisation, same batch: the PyTorch-native engine and
+    this package's runtime report the same losses step by step."""
+    from shardtrain_b200.training import qwen2_native_baseline
+
+    overrides = ["--training.steps", "3"]
+    ours = qwen2_benchmark.run(load_config(
+        CONFIGS / "qwen25_tiny.yaml", overrides + ["--debug.output_dir", str(tmp_path / "ours")]))
+    native = qwen2_native_baseline.run(load_config(
+        CONFIGS / "qwen25_tiny.yaml", overrides + ["--debug.output_dir", str(tmp_path / "native")]))
+    assert native["engine"] == "native_fsdp2" and native["status"] == "completed"
+    for a, b in zip(ours["steps"], native["steps"]):
+        assert a["loss"] == pytest.approx(b["loss"], rel=1e-5)
+        assert a["valid_tokens"] == b["valid_tokens"]
+    assert native["performance"]["model_unique_parameters"] == \
+        ours["performance"]["model_unique_parameters"]
+    with pytest.raises(ConfigError, match="FSDP meshes only"):
+        qwen2_native_baseline.run(load_config(CONFIGS / "qwen25_tiny.yaml",
+                                              ["--parallel.tp_degree", "2"]))
+
+
+@pytest.mark.distributed
+def test_native_fsdp2_baseline_two_ranks_matches_runtime(tmp_path):
+    common = ["--config", CONFIGS / "qwen25_tiny.yaml", "--warmup", "0", "--parallel.fsdp_degree", "2",
+              "--training.steps", "2", "--runtime.forward_prefetch", "true",
+              "--runtime.backward_prefetch", "true"]
+    losses = {}
+    for module in ("qwen2_native_baseline", "qwen2_benchmark"):
+        out = tmp_path / module
+        code, log = run_workers(f"shardtrain_b200.training.{module}", 2, common + ["--debug.output_dir", out])
+        assert code == 0, log[-3000:]
+        record = json.loads((out / "benchmark.rank0.json").read_text())
+        assert record["status"] == "completed"
+        losses[module] = [row["loss"] for row in record["steps"]]
+    assert losses["qwen2_native_baseline"] == pytest.approx(losses["qwen2_benchmark"], rel=1e-5)
