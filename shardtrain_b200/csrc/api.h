@@ -22,6 +22,11 @@ struct GemmCall {
   float alpha;
   int force_bn;  // 0 = rule, else 128, 192 or 256
   int split_k;   // K-split of the tail wave's tiles: 0 = rule, 1 = never, n = exactly n
+  // Gated (SwiGLU) forward: b = fused [2 * gated_inter, K] gate|up weight (K-major), out = [M, 2 *
+  // gated_inter] bf16 (gate|up), gated_out = [M, gated_inter] bf16 = silu(gate) * up.  N must be
+  // 2 * gated_inter.
+  void* gated_out;
+  int gated_inter;
   // Optional sequence scatter of an fp32 result (see GemmEpilogue): row b*seq + s is written to
   // scatter_out[s / seq_local] at row b*seq_local + s % seq_local; `out` is then unused.
   float* scatter_out[8];

@@ -134,6 +134,35 @@ void gemm_scatter(const Tensor& a, const Tensor& b, c10::ArrayRef<int64_t> dest_
   check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm_scatter");
 }
 
+// gate|up projection with the SwiGLU epilogue: gu [M, 2*inter] and h = silu(gate) * up [M, inter]
+void gemm_swiglu(const Tensor& a, const Tensor& w_gu, Tensor gu, Tensor h) {
+  need(a, at::kBFloat16, "a");
+  need(w_gu, at::kBFloat16, "w_gu");
+  need(gu, at::kBFloat16, "gu");
+  need(h, at::kBFloat16, "h");
+  TORCH_CHECK(a.dim() == 2 && w_gu.dim() == 2 && a.stride(1) == 1 && w_gu.stride(1) == 1 &&
+                  gu.is_contiguous() && h.is_contiguous() && w_gu.size(0) % 2 == 0 &&
+                  a.size(1) == w_gu.size(1) && gu.size(0) == a.size(0) &&
+                  gu.size(1) == w_gu.size(0) && h.size(0) == a.size(0) &&
+                  h.size(1) * 2 == w_gu.size(0),
+              "gemm_swiglu: shape mismatch");
+  const c10::cuda::CUDAGuard guard(a.device());
+  stb::GemmCall c{};
+  c.M = static_cast<int>(a.size(0));
+  c.K = static_cast<int>(a.size(1));
+  c.N = static_cast<int>(w_gu.size(0));
+  c.a = a.data_ptr();
+  c.b = w_gu.data_ptr();
+  c.out = gu.data_ptr();
+  c.lda = a.stride(0);
+  c.ldb = w_gu.stride(0);
+  c.ldo = gu.stride(0);
+  c.alpha = 1.f;
+  c.gated_out = h.data_ptr();
+  c.gated_inter = static_cast<int>(h.size(1));
+  check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm_swiglu");
+}
+
 void slot_sum_rmsnorm(const Tensor& slots, const c10::optional<Tensor>& residual, Tensor sum_out,
                       const c10::optional<Tensor>& w, const c10::optional<Tensor>& y,
                       const c10::optional<Tensor>& inv, double eps) {
@@ -620,6 +649,7 @@ TORCH_LIBRARY(stb, m) {
         "bool accumulate, float alpha, int force_bn, int split_k=0) -> ()",
         &gemm);
   m.def("gemm_scatter", &gemm_scatter);
+  m.def("gemm_swiglu", &gemm_swiglu);
   m.def("slot_sum_rmsnorm", &slot_sum_rmsnorm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

@@ -152,7 +152,7 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   else
     ok = make_bf16_tensor_map(&ta, c.a, c.K, c.M, c.lda, 64, 64);
   if (!B_MN)
-    ok = ok && make_bf16_tensor_map(&tb, c.b, c.N, c.K, c.ldb, 64, BN);
+    ok = ok && make_bf16_tensor_map(&tb, c.b, c.N, c.K, c.ldb, 64, c.gated_inter > 0 ? BN / 2 : BN);
   else
     ok = ok && make_bf16_tensor_map(&tb, c.b, c.K, c.N, c.ldb, 64, 64);
   if (!ok) return cudaErrorInvalidValue;
@@ -166,6 +166,8 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   ep.out_fp32 = c.out_fp32 ? 1 : 0;
   ep.accumulate = c.accumulate ? 1 : 0;
   ep.alpha = c.alpha;
+  ep.gated_out = c.gated_out;
+  ep.gated_inter = c.gated_inter > 0 ? c.gated_inter : 0;
   ep.scatter_degree = c.scatter_degree > 1 ? c.scatter_degree : 0;
   ep.scatter_seq = c.scatter_seq;
   ep.scatter_seq_local = c.scatter_seq_local;
@@ -180,11 +182,12 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   });
   if (attr_err != cudaSuccess) return attr_err;
   const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
-  const int n_tiles = (c.N + BN - 1) / BN;
+  const int n_tiles = c.gated_inter > 0 ? (c.gated_inter + BN / 2 - 1) / (BN / 2) : (c.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int num_kb = (c.K + kGemmBK - 1) / kGemmBK;
   GemmSplit sp{};
-  sp.split = plan_split(tiles, num_kb, c.split_k, &sp.full_tiles, &sp.kb_per_split);
+  sp.split = plan_split(tiles, num_kb, c.gated_inter > 0 ? 1 : c.split_k, &sp.full_tiles,
+                        &sp.kb_per_split);
   if (sp.split > 1) {
     SplitBuffers buffers;
     const cudaError_t e = split_buffers(stream, &buffers);
@@ -229,6 +232,14 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
       return cudaErrorInvalidValue;
     for (int i = 0; i < c.scatter_degree; ++i)
       if (c.scatter_out[i] == nullptr || !aligned16(c.scatter_out[i])) return cudaErrorInvalidValue;
+  }
+  if (c.gated_inter > 0) {
+    // SwiGLU epilogue: 256-wide tiles (128 gate + 128 up columns), forward operand order, bf16
+    if (c.a_mn || c.b_mn || c.out_fp32 || c.accumulate || c.bias != nullptr ||
+        c.residual != nullptr || c.scatter_degree > 1 || c.gated_out == nullptr ||
+        !aligned16(c.gated_out) || c.N != 2 * c.gated_inter || c.gated_inter % 8)
+      return cudaErrorInvalidValue;
+    return dispatch_major<256>(c, status, stream);
   }
   int bn = c.force_bn;
   if (bn == 0) {

@@ -29,6 +29,13 @@ struct GemmEpilogue {
   // that owns sequence position s, scatter_out[s / scatter_seq_local], at row
   // b * scatter_seq_local + s % scatter_seq_local.  The buffers may be peer memory: the partial
   // sums cross NVLink tile by tile from this epilogue, while later tiles are still in the MMAs.
+  // Gated (SwiGLU) mode, gated_inter > 0: B is the fused [2 * inter, K] gate|up weight.  A tile
+  // takes 128 gate rows and the 128 up rows of the same intermediate indices, so accumulator
+  // columns 0..127 / 128..255 hold gate / up of one index range; the epilogue writes both halves
+  // to `out` ([M, 2 * inter] bf16, gate|up as stored) and silu(gate) * up to `gated_out`
+  // ([M, inter] bf16).
+  void* gated_out;
+  int gated_inter;
   float* scatter_out[8];
   int scatter_degree;
   int scatter_seq;
@@ -94,7 +101,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
-  const int n_tiles = (N + BN - 1) / BN;
+  const bool gated = ep.gated_inter > 0;
+  const int tile_cols = gated ? BN / 2 : BN;          // output columns (per half) covered by a tile
+  const int n_span = gated ? ep.gated_inter : N;
+  const int n_tiles = (n_span + tile_cols - 1) / tile_cols;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + kGemmBK - 1) / kGemmBK;
   constexpr int GROUP = 8;
@@ -118,7 +128,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     const int first_m = (tile / group_span) * GROUP;
     const int gm = min(m_tiles - first_m, GROUP);
     m0 = (first_m + (tile % group_span) % gm) * kGemmBM;
-    n0 = ((tile % group_span) / gm) * BN;
+    n0 = ((tile % group_span) / gm) * tile_cols;
   };
 
   if (threadIdx.x == 0) {
@@ -172,7 +182,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
               tma_load_2d(sa + c * 8192, &tma_a, &full_bar[s], m0 + c * 64, kb * kGemmBK);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[s], kb * kGemmBK, n0);
+            if (gated) {   // box of BN / 2 rows: gate rows, then the matching up rows
+              tma_load_2d(sb, &tma_b, &full_bar[s], kb * kGemmBK, n0);
+              tma_load_2d(sb + (BN / 2) * 128, &tma_b, &full_bar[s], kb * kGemmBK,
+                          ep.gated_inter + n0);
+            } else {
+              tma_load_2d(sb, &tma_b, &full_bar[s], kb * kGemmBK, n0);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -355,6 +371,49 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
           }
         }
       };
+      if (gated) {
+        // SwiGLU epilogue: columns c*32.. of the gate half pair with the same columns of the up
+        // half.  Both are rounded to bf16 first (that is what the backward reads back), then
+        // h = bf16(silu(gate)) * up is rounded once more.
+        __nv_bfloat16* gu_row = reinterpret_cast<__nv_bfloat16*>(ep.out) + g_row * ep.ldo;
+        __nv_bfloat16* h_row =
+            reinterpret_cast<__nv_bfloat16*>(ep.gated_out) + g_row * ep.gated_inter;
+        const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(tmem_d + lane_base + c * 32, rg);
+          tmem_ld_32x32(tmem_d + lane_base + BN / 2 + c * 32, ru);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (!row_ok || col0 >= ep.gated_inter) continue;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (col0 + i >= ep.gated_inter) break;
+            uint4 pg, pu, ph;
+            uint32_t* wg = &pg.x;
+            uint32_t* wu = &pu.x;
+            uint32_t* wh = &ph.x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              wg[j] = pack_bf16x2(__uint_as_float(rg[i + 2 * j]), __uint_as_float(rg[i + 2 * j + 1]));
+              wu[j] = pack_bf16x2(__uint_as_float(ru[i + 2 * j]), __uint_as_float(ru[i + 2 * j + 1]));
+              const float2 g = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&wg[j]));
+              const float2 u = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&wu[j]));
+              // silu(gate) is rounded to bf16 before the product, as under bf16 autocast
+              const float sx = __bfloat162float(__float2bfloat16(g.x / (1.f + __expf(-g.x))));
+              const float sy = __bfloat162float(__float2bfloat16(g.y / (1.f + __expf(-g.y))));
+              wh[j] = pack_bf16x2(sx * u.x, sy * u.y);
+            }
+            *reinterpret_cast<uint4*>(gu_row + col0 + i) = pg;
+            *reinterpret_cast<uint4*>(gu_row + ep.gated_inter + col0 + i) = pu;
+            *reinterpret_cast<uint4*>(h_row + col0 + i) = ph;
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&acc_empty[ab]);
+        continue;
+      }
       if (part < 0) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {

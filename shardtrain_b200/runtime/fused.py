@@ -626,7 +626,7 @@ class FusedLayerFn(torch.autograd.Function):
             ctx.dims = (B, S_full, H, inter)
             ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm)
             return out.view(B, S, H)
-        # the 11 launches of the forward run from C++ (csrc/layer_executor.cpp)
+        # the 10 launches of the forward run from C++ (csrc/layer_executor.cpp)
         h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm = ops.layer_forward(
             x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask, ex.status,
             B, S, hq, hkv, cfg.rms_norm_eps)

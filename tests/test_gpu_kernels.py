@@ -406,3 +406,21 @@ def test_sequence_gather_and_pull_reduce_scatter(ops, T, B, sl, cols):
         ops.seq_reduce_scatter([p.data_ptr() for p in partials], rank, residual, got, B, sl)
         want = residual + sum(p[:, rank * sl:(rank + 1) * sl] for p in partials)
         torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("M,inter,K", [(512, 1024, 256), (300, 8960, 1536), (4096, 328, 192)])
+def test_gate_up_gemm_with_swiglu_epilogue(ops, M, inter, K):
+    """One kernel for gu = x @ [Wg; Wu]^T and h = bf16(silu(gate)) * up, against the separate
+    GEMM + SwiGLU kernels (bit-identical) and an fp32 reference."""
+    torch.manual_seed(5)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * inter, K, device=DEV) / math.sqrt(K)).bfloat16()
+    gu, h = torch.empty(M, 2 * inter, device=DEV, dtype=torch.bfloat16), torch.empty(M, inter, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_swiglu(x, w, gu, h)
+    gu2, h2 = torch.empty_like(gu), torch.empty_like(h)
+    ops.gemm(x, w, gu2, False, False, None, None, False, 1.0, 256, 1)
+    ops.swiglu_fwd(gu2, h2)
+    assert torch.equal(gu, gu2) and torch.equal(h, h2)
+    ref = x.float() @ w.float().t()
+    assert rel(gu, ref) < 5e-3
+    assert rel(h, torch.nn.functional.silu(ref[:, :inter]) * ref[:, inter:]) < 1e-2
