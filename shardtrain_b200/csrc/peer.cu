@@ -352,6 +352,16 @@ struct FlagPeers {
   uint32_t* p[kMaxPeers];
 };
 
+// First expiry wins the status block: {code, silent peer, epoch waited for, epoch last seen}.
+__device__ __forceinline__ void report_flag_timeout(int* status, int peer, uint32_t expected,
+                                                    const uint32_t* flag) {
+  if (atomicCAS(status, kOk, kErrPeerFlagWait) == kOk) {
+    status[1] = peer;
+    status[2] = static_cast<int>(expected);
+    status[3] = static_cast<int>(*reinterpret_cast<const volatile uint32_t*>(flag));
+  }
+}
+
 // Thread t tells peer t "rank `rank` reached `epoch`" and then waits until peer t says the same.
 // Pad layout: pad[slot * kMaxPeers + source_rank].  The spin is bounded; on expiry the status
 // word is set and the kernel returns.
@@ -374,7 +384,7 @@ __global__ void peer_barrier_kernel(FlagPeers pads, int degree, int rank, uint32
     }
     __nanosleep(64);
   }
-  if (!seen && status != nullptr) atomicCAS(status, kOk, kErrPeerFlagWait);
+  if (!seen && status != nullptr) report_flag_timeout(status, t, epoch, mine);
   __threadfence_system();
 }
 
@@ -412,7 +422,7 @@ __global__ void peer_allreduce_small_kernel(FlagPeers pads, InboxPeers inboxes, 
       }
       __nanosleep(64);
     }
-    if (!seen && status != nullptr) atomicCAS(status, kOk, kErrPeerFlagWait);
+    if (!seen && status != nullptr) report_flag_timeout(status, t, epoch, mine);
     __threadfence_system();
   }
   __syncthreads();

@@ -86,6 +86,7 @@ def check_status(where: str = "") -> None:
     """Synchronise and raise if any kernel recorded a bounded-wait expiry or a bad argument."""
     code = int(load().status_read())
     if code != 0:
+        block = load().status_tensor().cpu().tolist()     # {code, peer, expected, observed}
         load().status_reset()
         names = {
             1: "TMA producer gave up waiting for a free pipeline stage",
@@ -96,4 +97,9 @@ def check_status(where: str = "") -> None:
             6: "attention pipeline wait expired",
             7: "kernel rejected its arguments",
         }
-        raise RuntimeError(f"sm_100a kernel status {code} ({names.get(code, 'unknown')}) {where}")
+        detail = ""
+        if code == 5:
+            _, peer, expected, observed = block
+            detail = f" [group member {peer} silent: waited for epoch {expected}, last saw {observed}]"
+        raise RuntimeError(
+            f"sm_100a kernel status {code} ({names.get(code, 'unknown')}){detail} {where}")

@@ -139,7 +139,12 @@ class QwenTrainer:
                     total.add_(runtime.qwen_numerator)
                     with training_range("backward", runtime.device):
                         self.scaler.scale(out.loss).backward()
-                        runtime.finalize_backward(allow_nonfinite=self.scaler.is_enabled())
+                        # A non-finite shard gradient is not raised here, on the one rank that
+                        # happens to hold it: that rank would leave the step before the metric
+                        # collectives and its peers would only learn of it from a broken
+                        # connection or a timeout.  The finite vote below makes every rank raise
+                        # (bf16 / fp32) or skip the update (fp16) in the same step.
+                        runtime.finalize_backward(allow_nonfinite=True)
                     if not runtime.last_microstep:
                         runtime.end_step()
                     del out

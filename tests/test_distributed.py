@@ -63,3 +63,35 @@ def test_wrong_world_size_fails_fast(tmp_path):
     code, log = run_workers("tests.workers.qwen_worker", 2, ["--out", tmp_path, "--fsdp", 4], timeout=120)
     assert code != 0
     assert "world size" in log.lower()
+
+
+def test_nonfinite_gradient_on_one_rank_fails_every_rank_in_the_same_step(tmp_path):
+    """Host-side fault injection: rank 1 poisons one shard gradient in step 1.  The finite vote
+    makes every rank raise in that step, the runtime is FAILED everywhere and refuses the next
+    step instead of continuing with diverged collective order."""
+    import json
+
+    code, log = run_workers("tests.workers.qwen_worker", 2,
+                            ["--out", tmp_path, "--fsdp", 2, "--optimizer", "sgd",
+                             "--inject-inf-rank", 1])
+    assert code == 0, log[-3000:]
+    for rank in range(2):
+        record = json.loads((tmp_path / f"failure.rank{rank}.json").read_text())
+        assert record["step"] == 1 and "Nonfinite" in record["error"]
+        assert record["failed"] and record["refused_again"]
+    assert not list(tmp_path.glob("result.rank*.json"))
+
+
+def test_rank_skew_does_not_change_results(tmp_path):
+    """One rank is 50 ms late (host sleep) before every step, with every overlap switch on: the
+    consumer-ordered waits absorb the skew and training still matches the dense model."""
+    import json
+
+    code, log = run_workers("tests.workers.qwen_worker", 2,
+                            ["--out", tmp_path, "--fsdp", 2, "--optimizer", "sgd", "--flags", "111",
+                             "--delay-rank", 0])
+    assert code == 0, log[-3000:]
+    for rank in range(2):
+        record = json.loads((tmp_path / f"result.rank{rank}.json").read_text())
+        assert record["param_err"] < 1e-5
+        assert all(abs(row["loss"] - row["ref"]) < 1e-4 for row in record["rows"])

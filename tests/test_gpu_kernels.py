@@ -313,10 +313,24 @@ def test_bounded_peer_wait_reports_instead_of_hanging(ops):
     assert ops.status_read() == 0
     ops.peer_barrier([pad_a.data_ptr(), pad_b.data_ptr()], 0, 5, 1, 2000)   # "peer 1" never signals
     torch.cuda.synchronize()
-    with pytest.raises(RuntimeError, match="peer flag wait expired"):
+    with pytest.raises(RuntimeError, match="peer flag wait expired") as info:
         module.check_status("test")
+    # who was silent, which epoch was awaited, what was last seen
+    assert "group member 1 silent: waited for epoch 5, last saw 0" in str(info.value)
     assert ops.status_read() == 0
     assert torch.ones(4, device=DEV).sum().item() == 4
+    # the small all-reduce has the same bounded wait; a single member never waits
+    pads, inbox = [pad_a.data_ptr(), pad_b.data_ptr()], torch.zeros(2, 2 * 8 * 16, device=DEV,
+                                                                   dtype=torch.float64)
+    values, out = torch.tensor([1.5, 2.0], device=DEV, dtype=torch.float64), torch.zeros(2, device=DEV, dtype=torch.float64)
+    ops.peer_allreduce_small(pads, [inbox[0].data_ptr(), inbox[1].data_ptr()], 0, 9, 6, values, out, 0, 2000)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="waited for epoch 9"):
+        module.check_status("test")
+    ops.peer_allreduce_small(pads[:1], [inbox[0].data_ptr()], 0, 10, 6, values, out, 0, 2000)
+    torch.cuda.synchronize()
+    module.check_status("test")
+    assert out.tolist() == [1.5, 2.0]
 
 
 @pytest.mark.parametrize("b_mn", [False, True])

@@ -33,6 +33,10 @@ def main():
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--optimizer", default="adamw")
     ap.add_argument("--backend", default="auto")
+    ap.add_argument("--inject-inf-rank", type=int, default=-1,
+                    help="this rank poisons one shard gradient with inf in step 1 (host-side injection)")
+    ap.add_argument("--delay-rank", type=int, default=-1,
+                    help="this rank sleeps 50 ms on the host before every step (rank skew)")
     a = ap.parse_args()
     worker = WorkerEnvironment.read()
     out = Path(a.out)
@@ -74,12 +78,37 @@ def main():
         opt = (torch.optim.AdamW if a.optimizer == "adamw" else torch.optim.SGD)(dense.parameters(), lr=lr)
         batch = 2 * a.accum
         rows = []
+        if a.inject_inf_rank >= 0:
+            finalize = rt.finalize_backward
+
+            def poisoned(*args, **kwargs):
+                if worker.rank == a.inject_inf_rank and tr.step_id == 1:
+                    rt.grad_arena[3] = float("inf")
+                return finalize(*args, **kwargs)
+
+            rt.finalize_backward = poisoned
         for step in range(a.steps):
             gen = torch.Generator().manual_seed(100 + step)
             # every FSDP coordinate trains on its own batch; TP ranks of a replica share it
             all_ids = torch.randint(0, vocab, (a.fsdp, batch, seq), generator=gen)
             ids = all_ids[ctx.coordinate.fsdp].to(ctx.device)
-            res = tr.train_step(ids)
+            if worker.rank == a.delay_rank:
+                import time
+                time.sleep(0.05)
+            try:
+                res = tr.train_step(ids)
+            except RuntimeError as exc:
+                if a.inject_inf_rank < 0:
+                    raise
+                # every rank must refuse the poisoned step, and the runtime must stay failed
+                refused_again = False
+                try:
+                    tr.train_step(ids)
+                except RuntimeError:
+                    refused_again = True
+                (out / f"failure.rank{worker.rank}.json").write_text(json.dumps(dict(
+                    step=step, error=str(exc), failed=rt.failed, refused_again=refused_again)))
+                return
             opt.zero_grad()
             flat = all_ids.reshape(-1, seq).to(ctx.device)
             with torch.autocast(ctx.device.type, dtype=torch.bfloat16, enabled=a.dtype == "bf16"):
