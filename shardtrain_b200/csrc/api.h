@@ -33,6 +33,7 @@ struct GemmCall {
   int scatter_degree;  // 0 or 1: plain output
   int scatter_seq;
   int scatter_seq_local;
+  int scatter_broadcast;  // 1: store every row into all scatter_out buffers (all-reduce push)
 };
 cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream);
 

@@ -163,6 +163,35 @@ void gemm_swiglu(const Tensor& a, const Tensor& w_gu, Tensor gu, Tensor h) {
   check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm_swiglu");
 }
 
+// Row-parallel GEMM whose fp32 result is stored into every destination (all-reduce push).
+void gemm_broadcast(const Tensor& a, const Tensor& b, c10::ArrayRef<int64_t> dest_ptrs, bool b_mn) {
+  need(a, at::kBFloat16, "a");
+  need(b, at::kBFloat16, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1,
+              "gemm operands must be 2-D with a contiguous inner dimension");
+  TORCH_CHECK(dest_ptrs.size() >= 2 && dest_ptrs.size() <= 8, "2..8 destinations expected");
+  const c10::cuda::CUDAGuard guard(a.device());
+  stb::GemmCall c{};
+  c.M = static_cast<int>(a.size(0));
+  c.K = static_cast<int>(a.size(1));
+  c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == c.K, "gemm reduction sizes differ");
+  c.a = a.data_ptr();
+  c.b = b.data_ptr();
+  c.lda = a.stride(0);
+  c.ldb = b.stride(0);
+  c.ldo = c.N;
+  c.b_mn = b_mn;
+  c.out_fp32 = true;
+  c.alpha = 1.f;
+  c.scatter_degree = static_cast<int>(dest_ptrs.size());
+  c.scatter_broadcast = 1;
+  for (size_t i = 0; i < dest_ptrs.size(); ++i)
+    c.scatter_out[i] = reinterpret_cast<float*>(dest_ptrs[i]);
+  c.out = c.scatter_out[0];
+  check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm_broadcast");
+}
+
 void slot_sum_rmsnorm(const Tensor& slots, const c10::optional<Tensor>& residual, Tensor sum_out,
                       const c10::optional<Tensor>& w, const c10::optional<Tensor>& y,
                       const c10::optional<Tensor>& inv, double eps) {
@@ -650,6 +679,7 @@ TORCH_LIBRARY(stb, m) {
         &gemm);
   m.def("gemm_scatter", &gemm_scatter);
   m.def("gemm_swiglu", &gemm_swiglu);
+  m.def("gemm_broadcast", &gemm_broadcast);
   m.def("slot_sum_rmsnorm", &slot_sum_rmsnorm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

@@ -171,6 +171,7 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   ep.scatter_degree = c.scatter_degree > 1 ? c.scatter_degree : 0;
   ep.scatter_seq = c.scatter_seq;
   ep.scatter_seq_local = c.scatter_seq_local;
+  ep.scatter_broadcast = c.scatter_broadcast ? 1 : 0;
   for (int i = 0; i < 8; ++i) ep.scatter_out[i] = i < ep.scatter_degree ? c.scatter_out[i] : nullptr;
 
   auto kernel = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
@@ -227,8 +228,9 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
     // sequence must split evenly over the owners
     if (!c.out_fp32 || c.accumulate || c.residual != nullptr || c.bias != nullptr ||
         c.scatter_degree > 8 ||
-        c.scatter_seq_local <= 0 || c.scatter_seq != c.scatter_seq_local * c.scatter_degree ||
-        c.M % c.scatter_seq)
+        (!c.scatter_broadcast &&
+         (c.scatter_seq_local <= 0 || c.scatter_seq != c.scatter_seq_local * c.scatter_degree ||
+          c.M % c.scatter_seq)))
       return cudaErrorInvalidValue;
     for (int i = 0; i < c.scatter_degree; ++i)
       if (c.scatter_out[i] == nullptr || !aligned16(c.scatter_out[i])) return cudaErrorInvalidValue;

@@ -40,6 +40,9 @@ struct GemmEpilogue {
   int scatter_degree;
   int scatter_seq;
   int scatter_seq_local;
+  // Broadcast variant (tensor parallelism without sequence parallelism: the partial sums are
+  // all-reduced, every rank needs every row): row m is stored at row m of *every* scatter_out.
+  int scatter_broadcast;
 };
 
 // Tail split.  A persistent grid of G CTAs runs floor(tiles / G) full waves of whole tiles; the
@@ -272,12 +275,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
           const int gr = m0 + q * 32 + k * 4 + (lane >> 3);
           scatter_row[k] = nullptr;
           if (ok && gr < M) {
-            const int b = gr / ep.scatter_seq;
-            const int pos = gr - b * ep.scatter_seq;
-            const int owner = pos / ep.scatter_seq_local;
-            scatter_row[k] = ep.scatter_out[owner] +
-                             (static_cast<int64_t>(b) * ep.scatter_seq_local +
-                              (pos - owner * ep.scatter_seq_local)) * ep.ldo;
+            if (ep.scatter_broadcast) {
+              // the row inside destination 0; the other destinations use the same offset
+              scatter_row[k] = ep.scatter_out[0] + static_cast<int64_t>(gr) * ep.ldo;
+            } else {
+              const int b = gr / ep.scatter_seq;
+              const int pos = gr - b * ep.scatter_seq;
+              const int owner = pos / ep.scatter_seq_local;
+              scatter_row[k] = ep.scatter_out[owner] +
+                               (static_cast<int64_t>(b) * ep.scatter_seq_local +
+                                (pos - owner * ep.scatter_seq_local)) * ep.ldo;
+            }
           }
         }
       }
@@ -309,8 +317,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
             const int rr = k * 4 + (lane >> 3);
             const float4 x =
                 *reinterpret_cast<const float4*>(stage + rr * 32 + ((seg ^ (rr & 7)) << 2));
-            if (scatter_row[k] != nullptr && col0 + seg * 4 < N)
-              *reinterpret_cast<float4*>(scatter_row[k] + col0 + seg * 4) = x;
+            if (scatter_row[k] != nullptr && col0 + seg * 4 < N) {
+              if (ep.scatter_broadcast) {
+                const int64_t off = (scatter_row[k] - ep.scatter_out[0]) + col0 + seg * 4;
+                for (int o = 0; o < ep.scatter_degree; ++o)
+                  *reinterpret_cast<float4*>(ep.scatter_out[o] + off) = x;
+              } else {
+                *reinterpret_cast<float4*>(scatter_row[k] + col0 + seg * 4) = x;
+              }
+            }
           }
           __syncwarp();
           return;

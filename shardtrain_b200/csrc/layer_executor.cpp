@@ -62,6 +62,26 @@ struct Gemm {
     c.gated_inter = static_cast<int>(hm.size(1));
     ok(stb::launch_gemm_bf16(c, status, stream), "gemm swiglu");
   }
+  // fp32 partial rows pushed into every TP rank's receive slot (all-reduce without SP)
+  void broadcast(const Tensor& a, const Tensor& b, bool b_mn, c10::ArrayRef<int64_t> dest) const {
+    stb::GemmCall c{};
+    c.M = static_cast<int>(a.size(0));
+    c.K = static_cast<int>(a.size(1));
+    c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+    c.a = a.data_ptr();
+    c.b = b.data_ptr();
+    c.lda = a.stride(0);
+    c.ldb = b.stride(0);
+    c.ldo = c.N;
+    c.b_mn = b_mn;
+    c.out_fp32 = true;
+    c.alpha = 1.f;
+    c.scatter_degree = static_cast<int>(dest.size());
+    c.scatter_broadcast = 1;
+    for (size_t i = 0; i < dest.size(); ++i) c.scatter_out[i] = reinterpret_cast<float*>(dest[i]);
+    c.out = c.scatter_out[0];
+    ok(stb::launch_gemm_bf16(c, status, stream), "gemm broadcast");
+  }
   // gate|up projection followed by SwiGLU.  Measured on B200: with the SwiGLU in the GEMM
   // epilogue the tile's output grows by half and the epilogue becomes the bottleneck of this
   // short-K GEMM at 2048+ rows (240 us against 190 + 39 us at 4096 rows); at 1024 rows and below
@@ -417,6 +437,158 @@ Tensor layer_backward_sp(
   return dx;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Tensor parallel layer without sequence parallelism: activations are replicated over the TP
+// group, column-parallel GEMMs need no communication, and the partial sums of the row-parallel
+// GEMMs (forward o_proj / down_proj, backward dX of q|k|v and gate|up) are all-reduced: the GEMM
+// epilogue pushes its fp32 rows into slot `tp_rank` of every member's receive set and the next
+// kernel adds the T slots.  Two receive sets alternate, so one barrier per all-reduce is enough
+// (a set is overwritten two all-reduces later, after a barrier that every reader has passed).
+// push_a / push_b: per member, the address of this rank's slot in that member's set A / B.
+// Uses 2 barrier epochs per call.
+std::vector<Tensor> layer_forward_tp(
+    const Tensor& x2, const Tensor& w_qkv, const Tensor& b_qkv, const Tensor& w_o,
+    const Tensor& w_gu, const Tensor& w_down, const Tensor& ln1, const Tensor& ln2,
+    const Tensor& cos, const Tensor& sin, const c10::optional<Tensor>& positions,
+    const c10::optional<Tensor>& mask, Tensor status, int64_t B, int64_t S, int64_t hq,
+    int64_t hkv, double eps, c10::ArrayRef<int64_t> push_a, c10::ArrayRef<int64_t> push_b,
+    Tensor recv_a, Tensor recv_b, c10::ArrayRef<int64_t> flag_ptrs, int64_t tp_rank,
+    int64_t epoch, int64_t flag_slot, int64_t max_spin) {
+  const int64_t T = static_cast<int64_t>(push_a.size());
+  const int64_t M = B * S, H = x2.size(1), D = 128;
+  const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
+  TORCH_CHECK(recv_a.dim() == 3 && recv_a.size(0) == T && recv_a.size(1) == M && recv_a.size(2) == H &&
+                  recv_b.sizes() == recv_a.sizes(), "tensor-parallel layer: receive sets mismatch");
+  auto bf = x2.options().dtype(at::kBFloat16);
+  auto f32 = x2.options().dtype(at::kFloat);
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  Gemm g{st, status.data_ptr<int>()};
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
+  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const float feps = static_cast<float>(eps);
+
+  Tensor h1 = at::empty({M, H}, bf), inv1 = at::empty({M}, f32);
+  ok(stb::launch_rmsnorm_fwd(x2.data_ptr<float>(), ln1.data_ptr<float>(), h1.data_ptr(),
+                             inv1.data_ptr<float>(), M, H, feps, false, st), "rmsnorm");
+  Tensor qkv = at::empty({M, W}, bf);
+  g.run(h1, w_qkv, qkv, false, false, b_qkv.data_ptr<float>(), nullptr);
+  ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
+                      hkv, D, false, st), "rope");
+  Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
+  stb::AttnCall ac{qkv.data_ptr(), attn.data_ptr(), lse.data_ptr<float>(), km, static_cast<int>(B),
+                   static_cast<int>(S), static_cast<int>(hq), static_cast<int>(hkv),
+                   static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)))};
+  ok(stb::launch_attention_fwd(ac, g.status, st), "attention_fwd");
+  g.broadcast(attn, w_o, false, push_a);
+  sp.barrier();
+  Tensor x_mid = at::empty({M, H}, f32), h2 = at::empty({M, H}, bf), inv2 = at::empty({M}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv_a.data_ptr<float>(), T, recv_a.stride(0),
+                                  x2.data_ptr<float>(), x_mid.data_ptr<float>(),
+                                  ln2.data_ptr<float>(), h2.data_ptr(), inv2.data_ptr<float>(), M, H,
+                                  feps, st), "slot sum + rmsnorm");
+  Tensor gu = at::empty({M, 2 * inter}, bf), hm = at::empty({M, inter}, bf);
+  g.gate_up(h2, w_gu, gu, hm, st);
+  g.broadcast(hm, w_down, false, push_b);
+  sp.barrier();
+  Tensor out = at::empty({M, H}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv_b.data_ptr<float>(), T, recv_b.stride(0),
+                                  x_mid.data_ptr<float>(), out.data_ptr<float>(), nullptr, nullptr,
+                                  nullptr, M, H, feps, st), "slot sum");
+  return {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm};
+}
+
+
+// Backward of the layer above (d_out is replicated over the TP group); 2 barrier epochs.
+Tensor layer_backward_tp(
+    const Tensor& d_out, const Tensor& x2, const Tensor& inv1, const Tensor& h1, const Tensor& qkv,
+    const Tensor& attn, const Tensor& lse, const Tensor& x_mid, const Tensor& inv2, const Tensor& h2,
+    const Tensor& gu, const Tensor& hm, const Tensor& w_qkv, const Tensor& w_o, const Tensor& w_gu,
+    const Tensor& w_down, const Tensor& ln1, const Tensor& ln2, Tensor g_down, Tensor g_gate_up,
+    Tensor g_ln2, Tensor g_o, Tensor g_bias, Tensor g_qkv, Tensor g_ln1, const Tensor& cos,
+    const Tensor& sin, const c10::optional<Tensor>& positions, const c10::optional<Tensor>& mask,
+    Tensor status, int64_t B, int64_t S, int64_t hq, int64_t hkv, c10::ArrayRef<int64_t> push_a,
+    c10::ArrayRef<int64_t> push_b, Tensor recv_a, Tensor recv_b, c10::ArrayRef<int64_t> flag_ptrs,
+    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t max_spin) {
+  const int64_t T = static_cast<int64_t>(push_a.size());
+  const int64_t M = B * S, H = x2.size(1), D = 128;
+  const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
+  auto bf = x2.options().dtype(at::kBFloat16);
+  auto f32 = x2.options().dtype(at::kFloat);
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  Gemm g{st, status.data_ptr<int>()};
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
+  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  constexpr int kPartial = 592;
+
+  Tensor d_out_b = at::empty({M, H}, bf);
+  ok(stb::launch_cast_f32_to_bf16(d_out.data_ptr<float>(), d_out_b.data_ptr(), M * H, st), "cast");
+  g.run(d_out_b, hm, g_down, true, true, nullptr, nullptr);                 // dW down (local cols)
+  Tensor d_hm = at::empty({M, inter}, bf);
+  g.run(d_out_b, w_down, d_hm, false, true, nullptr, nullptr);              // dX down (local cols)
+  Tensor d_gu = at::empty({M, 2 * inter}, bf);
+  ok(stb::launch_swiglu_bwd(d_hm.data_ptr(), gu.data_ptr(), d_gu.data_ptr(), M, inter, st), "swiglu_bwd");
+  g.run(d_gu, h2, g_gate_up, true, true, nullptr, nullptr);                 // dW gate|up
+  g.broadcast(d_gu, w_gu, true, push_a);                                    // dX gate|up partial
+  sp.barrier();
+  Tensor d_h2 = at::empty({M, H}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv_a.data_ptr<float>(), T, recv_a.stride(0), nullptr,
+                                  d_h2.data_ptr<float>(), nullptr, nullptr, nullptr, M, H, 0.f, st),
+     "slot sum");
+  Tensor d_mid = at::empty({M, H}, f32), partial = at::empty({kPartial, H}, f32);
+  ok(stb::launch_rmsnorm_bwd(d_h2.data_ptr<float>(), x_mid.data_ptr<float>(), ln2.data_ptr<float>(),
+                             inv2.data_ptr<float>(), d_out.data_ptr<float>(), d_mid.data_ptr<float>(),
+                             partial.data_ptr<float>(), kPartial, M, H, st), "rmsnorm_bwd");
+  ok(stb::launch_colsum_f32(partial.data_ptr<float>(), g_ln2.data_ptr<float>(), kPartial, H, false, st), "colsum");
+
+  Tensor d_mid_b = at::empty({M, H}, bf);
+  ok(stb::launch_cast_f32_to_bf16(d_mid.data_ptr<float>(), d_mid_b.data_ptr(), M * H, st), "cast");
+  g.run(d_mid_b, attn, g_o, true, true, nullptr, nullptr);                  // dW o
+  Tensor d_attn = at::empty({M, hq * D}, bf);
+  g.run(d_mid_b, w_o, d_attn, false, true, nullptr, nullptr);               // dX o (local heads)
+  Tensor d_qkv = at::empty({M, W}, bf), delta = at::empty({B, hq, S}, f32);
+  stb::AttnBwdCall bc{};
+  bc.qkv = qkv.data_ptr();
+  bc.out = attn.data_ptr();
+  bc.dout = d_attn.data_ptr();
+  bc.lse = lse.data_ptr<float>();
+  bc.delta = delta.data_ptr<float>();
+  bc.dqkv = d_qkv.data_ptr();
+  const int parts = stb::attention_bwd_parts(static_cast<int>(B), static_cast<int>(S),
+                                             static_cast<int>(hq), static_cast<int>(hkv));
+  Tensor dkv_parts;
+  if (parts > 1) dkv_parts = at::empty({parts, M, 2 * hkv * D}, f32);
+  bc.dkv_accum = parts > 1 ? dkv_parts.data_ptr<float>() : nullptr;
+  bc.dkv_accum_floats = parts > 1 ? dkv_parts.numel() : 0;
+  bc.key_mask = km;
+  bc.batch = static_cast<int>(B);
+  bc.seq = static_cast<int>(S);
+  bc.hq = static_cast<int>(hq);
+  bc.hkv = static_cast<int>(hkv);
+  bc.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)));
+  ok(stb::launch_attention_bwd(bc, g.status, st), "attention_bwd");
+  ok(stb::launch_rope(d_qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
+                      hkv, D, true, st), "rope inverse");
+  Tensor bias_partial = at::empty({64, W}, f32);
+  ok(stb::launch_colsum_bf16(d_qkv.data_ptr(), W, g_bias.data_ptr<float>(), M, W, false,
+                             bias_partial.data_ptr<float>(), 64, st), "bias colsum");
+  g.run(d_qkv, h1, g_qkv, true, true, nullptr, nullptr);                    // dW q|k|v
+  g.broadcast(d_qkv, w_qkv, true, push_b);                                  // dX q|k|v partial
+  sp.barrier();
+  Tensor d_h1 = at::empty({M, H}, f32);
+  ok(stb::launch_slot_sum_rmsnorm(recv_b.data_ptr<float>(), T, recv_b.stride(0), nullptr,
+                                  d_h1.data_ptr<float>(), nullptr, nullptr, nullptr, M, H, 0.f, st),
+     "slot sum");
+  Tensor dx = at::empty({M, H}, f32);
+  ok(stb::launch_rmsnorm_bwd(d_h1.data_ptr<float>(), x2.data_ptr<float>(), ln1.data_ptr<float>(),
+                             inv1.data_ptr<float>(), d_mid.data_ptr<float>(), dx.data_ptr<float>(),
+                             partial.data_ptr<float>(), kPartial, M, H, st), "rmsnorm_bwd");
+  ok(stb::launch_colsum_f32(partial.data_ptr<float>(), g_ln1.data_ptr<float>(), kPartial, H, false, st), "colsum");
+  return dx;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(stb, m) {
@@ -424,4 +596,6 @@ TORCH_LIBRARY_FRAGMENT(stb, m) {
   m.def("layer_backward", &layer_backward);
   m.def("layer_forward_sp", &layer_forward_sp);
   m.def("layer_backward_sp", &layer_backward_sp);
+  m.def("layer_forward_tp", &layer_forward_tp);
+  m.def("layer_backward_tp", &layer_backward_tp);
 }

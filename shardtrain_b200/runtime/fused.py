@@ -190,6 +190,7 @@ class FusedExecutor:
         else:
             self.tp_peer, self.reduce_peer = None, self.peer
         self._sp_buffers = {}
+        self._tp_buffers = {}
         self.exp_avg = self.exp_avg_sq = None
         self._shards_dirty = True
         self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
@@ -201,10 +202,6 @@ class FusedExecutor:
     # ------------------------------------------------------------------ allocation
     def allocate(self):
         rt = self.runtime
-        if rt.tp.degree > 1 and not rt.sp:
-            raise NotImplementedError(
-                "The sm_100a executor covers FSDP-only and FSDP x TP/SP meshes; tensor "
-                "parallelism without sequence parallelism runs with communication_backend=nccl")
         portable = rt.materializer
         mat = PeerMaterializer(portable.group, rt.comm, self.peer)
         total = rt.plan.padded_total()
@@ -382,6 +379,31 @@ class FusedExecutor:
             )
             self._sp_buffers[key] = buf
         return buf
+
+    def tp_buffers(self, batch, seq):
+        """Receive sets of the all-reduce used by tensor parallelism without SP: two alternating
+        sets of T fp32 [batch*seq, H] slots per rank, peer visible; `push_x[p]` is where this
+        rank's partial rows go in member p's set."""
+        key = (batch, seq)
+        buf = self._tp_buffers.get(key)
+        if buf is None:
+            T, H, tp = self.tp_degree, self.cfg.hidden_size, self.tp_peer
+            rows = batch * seq
+            slot_bytes = rows * H * 4
+            sets = [tp.alloc(T * slot_bytes) for _ in range(2)]
+            buf = dict(
+                recv=[b.tensor(self.ops, T * rows * H, torch.float32).view(T, rows, H) for b in sets],
+                push=[[p + self.tp_rank * slot_bytes for p in b.ptrs] for b in sets],
+                flags=list(tp.flags.ptrs),
+            )
+            self._tp_buffers[key] = buf
+        return buf
+
+    @property
+    def metric_peer(self):
+        """Group over which per-step sums run: with SP the TP ranks hold different sequence
+        slices (whole mesh); without SP they hold identical values (FSDP group only)."""
+        return self.reduce_peer if (self.runtime.sp or self.tp_degree == 1) else self.peer
 
     def launch_grad_check(self):
         self.ops.grad_check(self.grad, self._pad_ranges, self._flags)
@@ -610,6 +632,20 @@ class FusedLayerFn(torch.autograd.Function):
             w["w_qkv"], w["b_qkv"], w["w_o"], w["w_gu"], w["w_down"], w["ln1"], w["ln2"])
         unit.prefetch_after_input(unit.forward_prefetch_handle, "FWD")
         ctx.ex, ctx.unit, ctx.index, ctx.tables, ctx.mask = ex, unit, index, tables, mask
+        if ex.tp_degree > 1 and not ex.runtime.sp:
+            # tensor parallel, replicated activations: partial sums are all-reduced by push
+            tp = ex.tp_peer
+            buf = ex.tp_buffers(B, S)
+            epoch = tp.epochs["sp_ag"]
+            h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm = ops.layer_forward_tp(
+                x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
+                ex.status, B, S, hq, hkv, cfg.rms_norm_eps, buf["push"][0], buf["push"][1],
+                buf["recv"][0], buf["recv"][1], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
+                tp.max_spin)
+            tp.epochs["sp_ag"] = epoch + 2
+            ctx.dims = (B, S, H, inter)
+            ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm)
+            return out.view(B, S, H)
         if ex.tp_degree > 1:
             # sequence parallel: x is this rank's [B, S/T, H] slice of the residual stream
             T, tp = ex.tp_degree, ex.tp_peer
@@ -643,7 +679,7 @@ class FusedLayerFn(torch.autograd.Function):
         plan = ex.runtime.materializer.plans[unit.unit_id]
         unit.annotate("BWD")
         unit.weight(plan.names[0])  # state / generation check of the backward materialisation
-        if ex.tp_degree > 1:
+        if ex.tp_degree > 1 and ex.runtime.sp:
             return FusedLayerFn._backward_sp(ctx, dout, plan)
         x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm = ctx.saved_tensors
         B, S, H, inter = ctx.dims
@@ -658,6 +694,19 @@ class FusedLayerFn(torch.autograd.Function):
         unit.prefetch_after_input(unit.backward_prefetch_handle, "BWD")
 
         d_out = dout.reshape(M, H).contiguous()
+        if ex.tp_degree > 1:
+            tp = ex.tp_peer
+            buf = ex.tp_buffers(B, S)
+            epoch = tp.epochs["sp_ag"]
+            dx = ops.layer_backward_tp(
+                d_out, x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm, w_qkv, w_o, w_gu,
+                w_down, ln1, ln2, gv["down"], gv["gate_up"], gv["ln2"], gv["o"], gv["bias"],
+                gv["qkv"], gv["ln1"], cos, sin, positions, ctx.mask, ex.status, B, S, hq, hkv,
+                buf["push"][0], buf["push"][1], buf["recv"][0], buf["recv"][1], buf["flags"],
+                ex.tp_rank, epoch, SP_FLAG_SLOT, tp.max_spin)
+            tp.epochs["sp_ag"] = epoch + 2
+            return (dx.view(B, S, H), None, None, None, None, None,
+                    *([ex.token_grad] * len(plan.names)))
         # the 26 launches of the backward run from C++ (csrc/layer_executor.cpp)
         dx = ops.layer_backward(
             d_out, x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm, w_qkv, w_o, w_gu, w_down, ln1,

@@ -327,7 +327,10 @@ class PeerMaterializer:
 
         # TP axis of the reduction: the slot table lists the whole mesh; TP-replicated
         # parameters are summed over it (each TP rank saw its own sequence slice)
-        tp = (arenas.tp_degree, arenas.tp_rank, 1.0 / self.degree)
+        # with SP every TP rank saw its own sequence slice (sum); without SP all TP ranks hold the
+        # same gradient of a replicated parameter (average)
+        replicated_scale = 1.0 / self.degree if runtime.sp else 1.0 / (self.degree * arenas.tp_degree)
+        tp = (arenas.tp_degree, arenas.tp_rank, replicated_scale)
 
         def launch():
             arenas.reduce_peer.barrier("fsdp_rs")     # no-op for a single member

@@ -176,11 +176,6 @@ def _choose_executor(runtime):
     want = runtime.communication_backend
     if runtime.device.type != "cuda" or want == "nccl":
         return "portable"
-    if runtime.tp.degree > 1 and not runtime.sp:
-        if want == "peer":
-            raise NotImplementedError("The sm_100a executor covers FSDP-only and TP+SP meshes; "
-                                      "TP without SP runs with communication_backend=nccl")
-        return "portable"
     if not ops.available():
         raise RuntimeError("CUDA device requested but torch.cuda is unavailable")
     return "fused"
@@ -375,10 +370,9 @@ def sum_metric(runtime, value, kind):
     """SUM of a scalar over the SP group (when SP) and the FSDP group."""
     fused = getattr(runtime, "fused", None)
     if fused is not None and fused.reduce_peer.degree > 1:
-        # sm_100a executor: one kernel over peer memory covers the whole mesh (with SP the TP
-        # ranks hold different sequence slices, so the sum runs over F x T; without a TP axis the
-        # mesh is the FSDP group)
-        total = fused.reduce_peer.all_reduce_small(value.detach().to(torch.float64).reshape(1))
+        # sm_100a executor: one kernel over peer memory (with SP the TP ranks hold different
+        # sequence slices, so the sum runs over F x T; without SP over the FSDP group only)
+        total = fused.metric_peer.all_reduce_small(value.detach().to(torch.float64).reshape(1))
         if runtime.comm.diagnostics_enabled:
             runtime.comm.event("metric_allreduce", kind=kind, backend="peer_kernel")
         return total[0].to(value.dtype)

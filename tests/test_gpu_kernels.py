@@ -438,3 +438,19 @@ def test_gate_up_gemm_with_swiglu_epilogue(ops, M, inter, K):
     ref = x.float() @ w.float().t()
     assert rel(gu, ref) < 5e-3
     assert rel(h, torch.nn.functional.silu(ref[:, :inter]) * ref[:, inter:]) < 1e-2
+
+
+def test_gemm_broadcast_epilogue_writes_every_row_to_every_destination(ops):
+    """All-reduce push of tensor parallelism without SP: the fp32 result goes, row for row, into
+    each member's receive slot (local tensors stand in for the members)."""
+    from shardtrain_b200 import ops as module
+
+    M, N, K, T = 640, 512, 320, 3
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    want = a.float() @ w.float().t()
+    dest = [torch.full((M, N), float("nan"), device=DEV) for _ in range(T)]
+    module.load().gemm_broadcast(a, w, [d.data_ptr() for d in dest], False)
+    for d in dest:
+        torch.testing.assert_close(d, want, atol=2e-2, rtol=2e-2)
+        assert torch.equal(d, dest[0])
