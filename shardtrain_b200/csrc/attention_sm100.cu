@@ -88,10 +88,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
   uint64_t* q_full = bars;            // 1
   uint64_t* kv_full = bars + 1;       // 2
   uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // 1
-  uint64_t* p_full = bars + 6;        // 1 (128 arrivals)
-  uint64_t* o_done = bars + 7;        // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_full = bars + 5;        // 2: scores are double buffered in TMEM
+  uint64_t* p_full = bars + 7;        // 1 (128 arrivals)
+  uint64_t* o_done = bars + 8;        // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -105,7 +105,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_full, 128);
     mbar_init(o_done, 1);
     fence_barrier_init();
@@ -113,14 +114,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
     prefetch_tensormap(&map);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
+  // S(j) lives in columns (j & 1) * 128: Q K^T of key block j + 1 is issued before the softmax of
+  // block j has finished, so the tensor pipe works under the softmax instead of after it
+  const uint32_t tS0 = tmem, tO = tmem + 256;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -138,14 +141,25 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, p.status, kErrAttnWait);
+      if (ok) ok = mbar_wait(&kv_full[0], 0, p.status, kErrAttnWait);
+      if (ok) {
+        tc_fence_after_sync();
+        mma_128<false, false>(tS0, smem_u32(sQ), smem_u32(sKV), false);          // S(0) = Q K_0^T
+        tc_commit(&s_full[0]);
+      }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
         const uint32_t k_tile = smem_u32(sKV + s * 2 * kTile);
-        ok = mbar_wait(&kv_full[s], (j >> 1) & 1, p.status, kErrAttnWait);
-        if (!ok) break;
-        tc_fence_after_sync();
-        mma_128<false, false>(tS, smem_u32(sQ), k_tile, false);      // S = Q K^T
-        tc_commit(s_full);
+        if (j + 1 < n_kv) {
+          // S(j+1) into the other score buffer: its last reader, the softmax of block j-1,
+          // finished before p_full(j-1), which this thread has already waited for
+          const int s1 = (j + 1) & 1;
+          ok = mbar_wait(&kv_full[s1], ((j + 1) >> 1) & 1, p.status, kErrAttnWait);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_128<false, false>(tS0 + s1 * 128, smem_u32(sQ), smem_u32(sKV + s1 * 2 * kTile), false);
+          tc_commit(&s_full[s1]);
+        }
         ok = mbar_wait(p_full, j & 1, p.status, kErrAttnWait);       // P in smem, O rescaled
         if (!ok) break;
         tc_fence_after_sync();
@@ -154,7 +168,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
         tc_commit(o_done);
       }
       if (!ok) {  // let the softmax warps fall through their bounded waits quickly
-        tc_commit(s_full);
+        tc_commit(&s_full[0]);
+        tc_commit(&s_full[1]);
         tc_commit(o_done);
       }
     }
@@ -166,9 +181,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      ok = mbar_wait(s_full, j & 1, p.status, kErrAttnWait);
+      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, p.status, kErrAttnWait);
       if (!ok) break;
       tc_fence_after_sync();
+      const uint32_t tS = tS0 + (j & 1) * 128;
       const bool diag = (j == qb);
       // pass 1: row maximum
       float mx = -INFINITY;
@@ -268,7 +284,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, 512);
   }
 }
 

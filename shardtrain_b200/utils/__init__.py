@@ -1,1 +1,1 @@
-
+"""Small user-facing utilities: comparing benchmark records of two engines."""

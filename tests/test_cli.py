@@ -192,3 +192,23 @@ def test_native_fsdp2_baseline_two_ranks_matches_runtime(tmp_path):
         assert record["status"] == "completed"
         losses[module] = [row["loss"] for row in record["steps"]]
     assert losses["qwen2_native_baseline"] == pytest.approx(losses["qwen2_benchmark"], rel=1e-5)
+
+
+def test_compare_engines_reads_two_runs_and_refuses_different_workloads(tmp_path, capsys):
+    from shardtrain_b200.training import qwen2_native_baseline
+    from shardtrain_b200.utils import compare_engines
+
+    base = ["--training.steps", "2"]
+    qwen2_benchmark.run(load_config(CONFIGS / "qwen25_tiny.yaml", base + ["--debug.output_dir", str(tmp_path / "a")]))
+    qwen2_native_baseline.run(load_config(CONFIGS / "qwen25_tiny.yaml", base + ["--debug.output_dir", str(tmp_path / "b")]))
+    qwen2_benchmark.run(load_config(CONFIGS / "qwen25_tiny.yaml",
+                                    base + ["--training.local_batch_size", "4", "--debug.output_dir", str(tmp_path / "c")]))
+    result = compare_engines.compare(compare_engines.load_run(tmp_path / "a"), compare_engines.load_run(tmp_path / "b"))
+    assert result["a"]["engine"] == "shardtrain_b200" and result["b"]["engine"] == "native_fsdp2"
+    assert abs(result["first_loss_difference"]) < 1e-4 and result["throughput_ratio_a_over_b"] > 0
+    assert compare_engines.main([str(tmp_path / "a"), str(tmp_path / "b")]) == 0
+    assert "a / b throughput" in capsys.readouterr().out
+    with pytest.raises(ValueError, match="different workloads"):
+        compare_engines.compare(compare_engines.load_run(tmp_path / "a"), compare_engines.load_run(tmp_path / "c"))
+    with pytest.raises(FileNotFoundError):
+        compare_engines.load_run(tmp_path / "missing")
