@@ -186,67 +186,64 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
       tc_fence_after_sync();
       const uint32_t tS = tS0 + (j & 1) * 128;
       const bool diag = (j == qb);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + lane_base + c * 32, v);
-        tmem_ld_wait();
+      // the whole score row (128 fp32) is read from TMEM once and kept in registers: four loads in
+      // flight, one wait, no second pass over TMEM for the exponentials
+      uint32_t sv[128];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = j * kBlk + c * 32 + i;
-          bool keep = !diag || kv <= q_idx;
-          if (p.key_mask != nullptr && keep) keep = p.key_mask[b * p.seq + min(kv, p.seq - 1)] != 0;
-          if (keep) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale);
-        }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+      tmem_ld_wait();
+      const uint8_t* mask_row = p.key_mask != nullptr ? p.key_mask + b * p.seq : nullptr;
+      const bool plain = !diag && mask_row == nullptr;     // every key of the block is visible
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        const int kv = j * kBlk + i;
+        bool keep = plain || !diag || kv <= q_idx;
+        if (!plain && mask_row != nullptr && keep) keep = mask_row[min(kv, p.seq - 1)] != 0;
+        const float x = keep ? __uint_as_float(sv[i]) * p.scale : -INFINITY;
+        sv[i] = __float_as_uint(x);
+        mx = fmaxf(mx, x);
       }
       const float m_new = fmaxf(m, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m == -INFINITY) ? 0.f : __expf(m - m_use);
+      // probabilities, rounded to bf16 and packed (masked scores are -inf: exp gives 0); kept in
+      // registers until the previous P V has released the shared-memory P tile
+      float sum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 128; i += 2) {
+        const float x0 = __uint_as_float(sv[i]), x1 = __uint_as_float(sv[i + 1]);
+        float e0 = (x0 == -INFINITY) ? 0.f : __expf(x0 - m_use);
+        float e1 = (x1 == -INFINITY) ? 0.f : __expf(x1 - m_use);
+        // sum what the tensor core will see (bf16-rounded), as the normaliser
+        e0 = __bfloat162float(__float2bfloat16(e0));
+        e1 = __bfloat162float(__float2bfloat16(e1));
+        sum += e0 + e1;
+        pk[i >> 1] = pack_bf16x2(e0, e1);
+      }
       if (j > 0) {
-        // previous P V finished (o_done), so O may be rescaled in place
+        // previous P V finished (o_done), so O may be rescaled in place and P overwritten; the
+        // score registers are dead by now, so the whole O row (128 fp32) fits in registers
         ok = mbar_wait(o_done, (j - 1) & 1, p.status, kErrAttnWait);
         tc_fence_after_sync();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tO + lane_base + c * 32, v);
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          uint32_t ov[128];
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            tmem_ld_32x32(tO + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&ov[c * 32]));
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(tO + lane_base + c * 32, v);
-        }
-        tmem_st_wait();
-      }
-      // pass 2: probabilities -> bf16 P tile in shared memory
-      float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + lane_base + c * 32, v);
-        tmem_ld_wait();
-        float e[32];
+          for (int i = 0; i < 128; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = j * kBlk + c * 32 + i;
-          bool keep = !diag || kv <= q_idx;
-          if (p.key_mask != nullptr && keep) keep = p.key_mask[b * p.seq + min(kv, p.seq - 1)] != 0;
-          e[i] = keep ? __expf(__uint_as_float(v[i]) * p.scale - m_use) : 0.f;
-          // sum what the tensor core will see (bf16-rounded), as the normaliser
-          e[i] = __bfloat162float(__float2bfloat16(e[i]));
-          sum += e[i];
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 pk;
-          pk.x = pack_bf16x2(e[8 * g], e[8 * g + 1]);
-          pk.y = pack_bf16x2(e[8 * g + 2], e[8 * g + 3]);
-          pk.z = pack_bf16x2(e[8 * g + 4], e[8 * g + 5]);
-          pk.w = pack_bf16x2(e[8 * g + 6], e[8 * g + 7]);
-          store_row8(sP, r, c * 4 + g, pk);
+          for (int c = 0; c < 4; ++c)
+            tmem_st_32x32(tO + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&ov[c * 32]));
+          tmem_st_wait();
         }
       }
+#pragma unroll
+      for (int g = 0; g < 16; ++g)
+        store_row8(sP, r, g, make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]));
       l = l * alpha + sum;
       m = m_new;
       tc_fence_before_sync();
