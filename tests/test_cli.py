@@ -21,6 +21,10 @@ def test_every_preset_parses():
             "runtime_cpu.yaml", "smoke_gloo.yaml"} <= set(names)
     for name in names:
         load_config(CONFIGS / name)
+    for name, strategy in (("S-F", "F4T1"), ("S-H", "F2T2/SP"), ("N-F", "F4T1"), ("N-H", "F2T2/SP")):
+        preset = load_config(CONFIGS / "fsdp4_hybrid_2x2" / f"{name}.yaml")
+        assert preset.parallel.strategy == strategy
+        assert preset.training.local_batch_size * preset.parallel.fsdp_degree == 8
     headline = load_config(CONFIGS / "qwen25_1p5b_b200.yaml")
     assert headline.parallel.strategy == "F8T1"
     assert headline.training.local_batch_size * headline.parallel.fsdp_degree == 8
