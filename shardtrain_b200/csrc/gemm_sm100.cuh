@@ -108,7 +108,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   const int tile_cols = gated ? BN / 2 : BN;          // output columns (per half) covered by a tile
   const int n_span = gated ? ep.gated_inter : N;
   const int n_tiles = (n_span + tile_cols - 1) / tile_cols;
-  const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + kGemmBK - 1) / kGemmBK;
   constexpr int GROUP = 8;
   const int group_span = GROUP * n_tiles;
