@@ -228,7 +228,7 @@ def run_ours(args):
             "e2e": {"value": VALID_LABELS_PER_STEP * 1000.0 * args.steps / e2e_ms,
                     "unit": "labels/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": host_ids.numel() * host_ids.element_size() * fsdp,
-                    "d2h_bytes_per_step": 32 * args.gpus},
+                    "d2h_bytes_per_step": 40 * args.gpus},
             "gpu_launches": launches,
             "loss_first_last": [losses[0] if losses else None, losses[-1]],
             "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2**30,

@@ -100,10 +100,18 @@ class QwenTrainer:
         finite = self._finite_vote(reported)
         fused = self.runtime.fused
         padding = fused._flags[1] if fused is not None else torch.zeros((), device=finite.device)
+        # the kernels' status word (bounded waits that expired, rejected arguments) rides along in
+        # the same device-to-host read, so a silent peer fails this very step on the host
+        status = fused.status[0] if fused is not None else torch.zeros((), device=finite.device)
         row = torch.stack([finite.to(torch.float64), reported.detach().to(torch.float64),
-                           global_count.to(torch.float64), padding.to(torch.float64)]).cpu().tolist()
+                           global_count.to(torch.float64), padding.to(torch.float64),
+                           status.to(torch.float64)]).cpu().tolist()
         if fused is not None:
             fused._flags.zero_()
+            if row[4]:
+                from shardtrain_b200 import ops as ops_module
+
+                ops_module.check_status("in train_step")
         if row[3]:
             raise RuntimeError("Nonzero gradient padding in a shard")
         return bool(row[0]), float(row[1]), int(row[2])

@@ -90,3 +90,23 @@ def test_caller_supplied_position_ids_match_default_positions():
         pytest.approx(base, rel=1e-6)
     # a constant shift would not do: rotary attention depends on position differences only
     assert abs(trainer.train_step(ids, position_ids=row * 3).loss - base) > 1e-4
+
+
+def test_expired_device_wait_fails_the_step_on_the_host():
+    """A bounded device-side wait that gave up (here: a barrier whose peer flag nobody sets, with a
+    tiny spin limit) is seen by the trainer in the same read as the step metrics: the step
+    raises, the runtime goes FAILED, the CUDA context stays usable."""
+    from shardtrain_b200 import ops as module
+
+    dense, model, rt, tr = build(True)
+    ids = torch.randint(0, 2048, (4, 128), device="cuda")
+    tr.train_step(ids)
+    pads = [torch.zeros(64, device="cuda", dtype=torch.int32) for _ in range(2)]
+    module.load().peer_barrier([p.data_ptr() for p in pads], 0, 3, 1, 1000)   # "peer 1" is silent
+    with pytest.raises(RuntimeError, match="peer flag wait expired"):
+        tr.train_step(ids)
+    assert rt.failed
+    with pytest.raises(RuntimeError):
+        tr.train_step(ids)
+    assert module.load().status_read() == 0
+    assert torch.ones(8, device="cuda").sum().item() == 8
