@@ -18,7 +18,7 @@ OUT = ROOT / "_C.so"
 OBJ = ROOT / "csrc" / "build"
 
 CUDA_SOURCES = ["gemm_sm100.cu", "elementwise.cu", "peer.cu", "attention_sm100.cu", "noalloc.cu"]
-CPP_SOURCES = ["bindings.cpp", "layer_executor.cpp", "scheduler.cpp"]
+CPP_SOURCES = ["bindings.cpp", "layer_executor.cpp"]
 NVCC_FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",
