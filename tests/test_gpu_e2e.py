@@ -110,3 +110,23 @@ def test_expired_device_wait_fails_the_step_on_the_host():
         tr.train_step(ids)
     assert module.load().status_read() == 0
     assert torch.ones(8, device="cuda").sum().item() == 8
+
+
+def test_nonfinite_gradient_is_caught_by_the_reduction_kernels_check():
+    """An inf slipped into the gradient arena between the two micro-steps (host-side injection)
+    reaches the second reduce-scatter's accumulate, whose built-in check flags it; the step
+    raises and the runtime is FAILED."""
+    dense, model, rt, tr = build(True, accumulate=2, optimizer="adamw", lr=1e-3)
+    ids = torch.randint(0, 2048, (4, 128), device="cuda")
+    tr.train_step(ids)
+    end_step, state = rt.end_step, {"armed": True}
+
+    def poisoned_end_step():
+        end_step()
+        if state.pop("armed", False):
+            rt.grad_arena[3] = float("inf")
+
+    rt.end_step = poisoned_end_step
+    with pytest.raises(RuntimeError, match="Nonfinite"):
+        tr.train_step(ids)
+    assert rt.failed
