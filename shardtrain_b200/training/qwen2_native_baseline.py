@@ -11,8 +11,10 @@ forward / backward prefetch lists, autocast compute, AdamW(foreach=False), the s
 initialisation, the same synthetic batch and the same record layout (`benchmark.rank{r}.json`,
 `"engine": "native_fsdp2"`).
 
-Scope: FSDP meshes (T = 1).  The reference's DTensor tensor/sequence-parallel plan is not
-reproduced; a TP mesh is refused with a configuration error.
+Scope: FSDP meshes and FSDP x TP meshes without sequence parallelism (DTensor Colwise / Rowwise
+plan on the projections, `fully_shard` on the FSDP axis of a 2-D device mesh).  The reference's
+sequence-parallel plan with its shared gathered input is not reproduced; SP is refused with a
+configuration error.
 """
 
 from __future__ import annotations
@@ -59,6 +61,27 @@ def materialize_same_source(model, device) -> None:
     for name, buffer in list(model.named_buffers()):
         if buffer.device.type == "meta":
             raise RuntimeError(f"Buffer {name} cannot be materialised from a meta tensor")
+
+
+def parallelize_tensor_axis(model, tp_mesh) -> None:
+    """Megatron-style TP without SP through DTensor: q/k/v/gate/up column-wise, o/down row-wise
+    (all-reduce inside RowwiseParallel); activations, norms, embedding and head stay replicated."""
+    from torch.distributed.tensor.parallel import (ColwiseParallel, RowwiseParallel,
+                                                   parallelize_module)
+
+    degree = tp_mesh.size()
+    plan = {"self_attn.q_proj": ColwiseParallel(), "self_attn.k_proj": ColwiseParallel(),
+            "self_attn.v_proj": ColwiseParallel(), "self_attn.o_proj": RowwiseParallel(),
+            "mlp.gate_proj": ColwiseParallel(), "mlp.up_proj": ColwiseParallel(),
+            "mlp.down_proj": RowwiseParallel()}
+    for layer in model.model.layers:
+        attention = layer.self_attn
+        if attention.num_heads % degree or attention.num_key_value_heads % degree:
+            raise ConfigError("attention heads must be divisible by the TP degree")
+        parallelize_module(layer, tp_mesh, plan)
+        # the module reshapes its local projection outputs: it now owns 1/T of the heads
+        attention.num_heads //= degree
+        attention.num_key_value_heads //= degree
 
 
 def shard_with_fsdp2(model, mesh, *, reshard_after_forward, forward_prefetch, backward_prefetch):
@@ -167,8 +190,8 @@ def run(config: Config, *, warmup: int = 0, peak_tflops_per_gpu: float | None = 
     ranks reduced outside the timer, CUDA-event span)."""
     if config.model.model_type != "qwen2":
         raise ConfigError("The native baseline requires model.model_type=qwen2")
-    if config.parallel.tp_degree != 1 or config.parallel.sp_enabled:
-        raise ConfigError("The native baseline covers FSDP meshes only (tp_degree 1, no SP)")
+    if config.parallel.sp_enabled:
+        raise ConfigError("The native baseline covers FSDP and FSDP x TP meshes without SP")
     if type(warmup) is not int or warmup < 0:
         raise ConfigError("warmup must be a nonnegative integer")
     rank = WorkerEnvironment.read().rank
@@ -194,14 +217,20 @@ def run(config: Config, *, warmup: int = 0, peak_tflops_per_gpu: float | None = 
             model = build_qwen_model(config.model, tc.seed)
             parameters = sum(p.numel() for p in model.parameters())
             materialize_same_source(model, device)
+            group = None
             if session.worker.launched:
-                mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("fsdp",))
+                degrees = (config.parallel.fsdp_degree, config.parallel.tp_degree)
+                mesh = init_device_mesh(device.type, degrees, mesh_dim_names=("fsdp", "tp"))
+                if degrees[1] > 1:
+                    parallelize_tensor_axis(model, mesh["tp"])
                 payload["sharding"] = shard_with_fsdp2(
-                    model, mesh, reshard_after_forward=rc.reshard_after_forward,
+                    model, mesh["fsdp"], reshard_after_forward=rc.reshard_after_forward,
                     forward_prefetch=rc.forward_prefetch, backward_prefetch=rc.backward_prefetch)
+                payload["sharding"]["tensor_parallel_degree"] = degrees[1]
+                group = mesh["fsdp"].get_group()      # TP ranks of a replica see the same batch
             trainer = NativeQwenTrainer(model, tc.lr, dtype=tc.dtype, optimizer=tc.optimizer,
                                         accumulation_steps=tc.accumulation_steps, device=device,
-                                        group=dist.group.WORLD if session.worker.launched else None)
+                                        group=group)
             draw = torch.Generator().manual_seed(tc.seed + ctx.coordinate.fsdp)
             ids = torch.randint(model.config.vocab_size,
                                 (tc.local_batch_size * tc.accumulation_steps, config.model.seq_len),

@@ -177,9 +177,9 @@ def test_native_fsdp2_baseline_matches_the_sharded_runtime_single_rank(tmp_path)
         assert a["valid_tokens"] == b["valid_tokens"]
     assert native["performance"]["model_unique_parameters"] == \
         ours["performance"]["model_unique_parameters"]
-    with pytest.raises(ConfigError, match="FSDP meshes only"):
-        qwen2_native_baseline.run(load_config(CONFIGS / "qwen25_tiny.yaml",
-                                              ["--parallel.tp_degree", "2"]))
+    with pytest.raises(ConfigError, match="without SP"):
+        qwen2_native_baseline.run(load_config(
+            CONFIGS / "qwen25_tiny.yaml", ["--parallel.tp_degree", "2", "--parallel.sp_enabled", "true"]))
 
 
 @pytest.mark.distributed
@@ -216,3 +216,20 @@ def test_compare_engines_reads_two_runs_and_refuses_different_workloads(tmp_path
         compare_engines.compare(compare_engines.load_run(tmp_path / "a"), compare_engines.load_run(tmp_path / "c"))
     with pytest.raises(FileNotFoundError):
         compare_engines.load_run(tmp_path / "missing")
+
+
+@pytest.mark.distributed
+def test_native_baseline_fsdp_x_tp_mesh_matches_runtime(tmp_path):
+    """F2 x T2 without SP on 4 gloo ranks: DTensor Colwise / Rowwise plan + fully_shard against
+    this package's runtime on the same mesh."""
+    common = ["--config", CONFIGS / "qwen25_tiny.yaml", "--warmup", "0", "--parallel.fsdp_degree", "2",
+              "--parallel.tp_degree", "2", "--training.steps", "2"]
+    losses = {}
+    for module in ("qwen2_native_baseline", "qwen2_benchmark"):
+        out = tmp_path / module
+        code, log = run_workers(f"shardtrain_b200.training.{module}", 4, common + ["--debug.output_dir", out])
+        assert code == 0, log[-3000:]
+        records = [json.loads((out / f"benchmark.rank{r}.json").read_text()) for r in range(4)]
+        assert all(r["status"] == "completed" for r in records)
+        losses[module] = [row["loss"] for row in records[0]["steps"]]
+    assert losses["qwen2_native_baseline"] == pytest.approx(losses["qwen2_benchmark"], rel=1e-5)
