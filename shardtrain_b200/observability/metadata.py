@@ -27,7 +27,9 @@ def git_revision() -> str | None:
 
 
 def write_json(filename: Path, data: Any) -> None:
-    Path(filename).write_text(json.dumps(data, indent=2, ensure_ascii=False) + "\n", encoding="utf-8")
+    # values json does not know (dtypes, paths, devices) are written as their text form
+    text = json.dumps(data, indent=2, ensure_ascii=False, default=str)
+    Path(filename).write_text(text + "\n", encoding="utf-8")
 
 
 def _version(package: str) -> str | None:
