@@ -64,3 +64,37 @@ def test_profile_capture_modes_on_cpu(tmp_path):
     assert (tmp_path / "torch" / "profile.rank1.json").exists()
     record = json.loads((tmp_path / "torch" / "profiling.rank1.json").read_text())
     assert record["mode"] == "torch"
+
+
+def test_worker_session_logs_bootstrap_and_worker_failures(tmp_path, monkeypatch):
+    """A configuration that cannot run leaves "Worker bootstrap failed" in the rank log; an
+    exception inside the session is logged as "Worker failed"; a malformed launcher environment
+    still leaves a log behind."""
+    from shardtrain_b200.config import ConfigError
+    from shardtrain_b200.launch.bootstrap import WorkerSession
+
+    for key in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(key, raising=False)
+    bad = load_config(None, ["--parallel.fsdp_degree", "2", "--debug.output_dir", str(tmp_path / "bad")])
+    with pytest.raises(ConfigError):
+        with WorkerSession(bad, "runtime"):
+            pass
+    text = (tmp_path / "bad" / "rank0.jsonl").read_text()
+    assert "Worker bootstrap failed" in text
+
+    good = load_config(None, ["--debug.output_dir", str(tmp_path / "good")])
+    with pytest.raises(RuntimeError, match="injected"):
+        with WorkerSession(good, "train") as session:
+            assert session.context.device.type == "cpu"
+            raise RuntimeError("injected on the host")
+    rows = [json.loads(line) for line in (tmp_path / "good" / "rank0.jsonl").read_text().splitlines()]
+    assert any(r["message"] == "Worker failed" and "injected on the host" in r.get("exception", "")
+               for r in rows)
+
+    monkeypatch.setenv("RANK", "1")          # WORLD_SIZE missing: malformed launcher environment
+    with pytest.raises(ConfigError):
+        with WorkerSession(load_config(None, ["--debug.output_dir", str(tmp_path / "env")]), "train"):
+            pass
+    assert "Worker environment validation failed" in (tmp_path / "env" / "rank0.jsonl").read_text()
+    with pytest.raises(ConfigError, match="output_dir"):
+        WorkerSession(load_config(None, ["--debug.output_dir", " "]), "train")
