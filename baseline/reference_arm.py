@@ -34,7 +34,7 @@ def run_reference(args) -> None:
         unavailable(f"reference run failed: {type(exc).__name__}: {str(exc)[:300]}")
 
 
-def _run(args) -> None:
+def _measure(args, fsdp, tp, sp) -> dict:
     import torch
     import torch.distributed as dist
     from sharded_runtime.config import config_from_dict
@@ -45,13 +45,10 @@ def _run(args) -> None:
 
     import bench
 
-    fsdp, tp, sp = bench.resolve_strategy(args)
-    if fsdp * tp != args.gpus:
-        raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
     ours = bench.qwen15b_dict(args, fsdp, tp, sp)
     for key in ("communication_backend", "retain_parameters"):   # fields the reference lacks
         ours["runtime"].pop(key)
-    ours["debug"]["output_dir"] = f"/tmp/shardtrain_ref_bench_{os.getpid()}"
+    ours["debug"]["output_dir"] = f"/tmp/shardtrain_ref_bench_{os.getpid()}_{fsdp}x{tp}"
     config = config_from_dict(ours)
     with WorkerSession(config, "runtime") as session:
         mesh, rank = session.context, session.worker.rank
@@ -107,38 +104,70 @@ def _run(args) -> None:
         if multi:
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
         elapsed_ms, e2e_ms = times.tolist()
-        ms = elapsed_ms / args.steps
-        value = bench.VALID_LABELS_PER_STEP * 1000.0 / ms
-        strategy = f"F{fsdp}T{tp}" + ("/SP" if sp else "")
-        published = bench.PUBLISHED.get(args.gpus, {}).get(strategy)
-        line = {
-            "metric": "effective_labels_per_second", "value": value, "unit": "labels/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": value / published if published else None,
-            "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
-            "impl": "reference",
-            "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else ""),
-                       "global_batch": 16, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
-                       "parallelism": strategy,
-                       "valid_labels_per_step": bench.VALID_LABELS_PER_STEP,
-                       "precision": "bf16 autocast GEMMs, math SDPA; fp32 shards, gradients, "
-                                    "NCCL communication, AdamW(foreach=False) state",
-                       "runtime": {"reshard_after_forward": rc.reshard_after_forward,
-                                   "forward_prefetch": rc.forward_prefetch,
-                                   "backward_prefetch": rc.backward_prefetch,
-                                   "async_grad_rs": rc.async_grad_rs,
-                                   "communication_policy": rc.communication_policy},
-                       "torch": torch.__version__,
-                       "l2": "no explicit flush: each step streams >6 GB per GPU group"},
-            "clocks": clocks,
-            "e2e": {"value": bench.VALID_LABELS_PER_STEP * 1000.0 * args.steps / e2e_ms,
-                    "unit": "labels/s", "ms_per_step": e2e_ms / args.steps,
-                    "h2d_bytes_per_step": host_ids.numel() * host_ids.element_size() * fsdp,
-                    "d2h_bytes_per_step": 24 * args.gpus},
-            "gpu_launches": 0,
-            "loss_first_last": [losses[0] if losses else None, losses[-1]],
-            "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2**30,
-        }
-        if rank == 0:
-            print(json.dumps(line), flush=True)
+        out = dict(strategy=f"F{fsdp}T{tp}" + ("/SP" if sp else ""), rank=rank,
+                   ms=elapsed_ms / args.steps, e2e_ms=e2e_ms / args.steps, clocks=clocks,
+                   losses=[losses[0] if losses else None, losses[-1]],
+                   h2d=host_ids.numel() * host_ids.element_size() * fsdp,
+                   peak=torch.cuda.max_memory_allocated(device) / 2**30,
+                   switches={"reshard_after_forward": rc.reshard_after_forward,
+                             "forward_prefetch": rc.forward_prefetch,
+                             "backward_prefetch": rc.backward_prefetch,
+                             "async_grad_rs": rc.async_grad_rs,
+                             "communication_policy": rc.communication_policy},
+                   torch=torch.__version__)
+        del trainer, runtime, model
+        torch.cuda.empty_cache()
+    return out
+
+
+def _run(args) -> None:
+    import bench
+
+    fsdp, tp, sp = bench.resolve_strategy(args)
+    if fsdp * tp != args.gpus:
+        raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
+    m = _measure(args, fsdp, tp, sp)
+    labels = bench.VALID_LABELS_PER_STEP
+    value = labels * 1000.0 / m["ms"]
+    published = bench.PUBLISHED.get(args.gpus, {}).get(m["strategy"])
+    line = {
+        "metric": "effective_labels_per_second", "value": value, "unit": "labels/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": m["ms"],
+        "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / published if published else None,
+        "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+        "impl": "reference",
+        "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else ""),
+                   "global_batch": 16, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
+                   "parallelism": m["strategy"], "valid_labels_per_step": labels,
+                   "precision": "bf16 autocast GEMMs, math SDPA; fp32 shards, gradients, "
+                                "NCCL communication, AdamW(foreach=False) state",
+                   "inputs": "token ids + all-ones attention_mask + position_ids",
+                   "runtime": m["switches"], "torch": m["torch"],
+                   "l2": "no explicit flush: each step streams >6 GB per GPU group"},
+        "clocks": m["clocks"],
+        "e2e": {"value": labels * 1000.0 / m["e2e_ms"], "unit": "labels/s",
+                "ms_per_step": m["e2e_ms"], "h2d_bytes_per_step": m["h2d"],
+                "d2h_bytes_per_step": 24 * args.gpus},
+        "gpu_launches": 0,
+        "loss_first_last": m["losses"],
+        "peak_memory_gib": m["peak"],
+    }
+    hybrid = bench.HYBRID.get(args.gpus)
+    if hybrid is not None and not args.strategy and not args.no_secondary:
+        try:
+            h = _measure(args, *hybrid)
+            hv = labels * 1000.0 / h["ms"]
+            line["secondary"] = {
+                "parallelism": h["strategy"], "value": hv, "unit": "labels/s",
+                "ms_per_step": h["ms"],
+                "e2e": {"value": labels * 1000.0 / h["e2e_ms"], "ms_per_step": h["e2e_ms"],
+                        "h2d_bytes_per_step": h["h2d"], "d2h_bytes_per_step": 24 * args.gpus},
+                "loss_first_last": h["losses"], "clocks": h["clocks"],
+                "vs_baseline": (hv / bench.PUBLISHED[args.gpus][h["strategy"]]
+                                if h["strategy"] in bench.PUBLISHED.get(args.gpus, {}) else None),
+            }
+        except Exception as exc:  # noqa: BLE001 - the primary measurement must still be printed
+            line["secondary"] = {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    if m["rank"] == 0:
+        print(json.dumps(line), flush=True)

@@ -43,6 +43,10 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (not reportable)")
     ap.add_argument("--retain", type=int, default=0, help="runtime.retain_parameters")
     ap.add_argument("--backend", default="auto", choices=["auto", "peer", "nccl"])
+    ap.add_argument("--fp32-wire", action="store_true",
+                    help="gather parameters from the fp32 shards instead of their bf16 shadow")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the second (hybrid TP/SP) strategy that follows the F{N}T1 pass")
     return ap.parse_args()
 
 
@@ -127,7 +131,12 @@ def resolve_strategy(args):
     return int(f), int(t), sp
 
 
-def run_ours(args):
+HYBRID = {2: (1, 2, True), 4: (2, 2, True), 8: (4, 2, True)}   # N -> (F, T, SP) second strategy
+
+
+def measure_ours(args, fsdp, tp, sp):
+    """Warm up, then time exactly K steps of one strategy; returns the measurements of this rank
+    group (times already reduced to the maximum over ranks)."""
     import torch
     import torch.distributed as dist
 
@@ -137,9 +146,6 @@ def run_ours(args):
     from shardtrain_b200.runtime.engine import ShardedRuntime
     from shardtrain_b200.training.qwen2_trainer import QwenTrainer
 
-    fsdp, tp, sp = resolve_strategy(args)
-    if fsdp * tp != args.gpus:
-        raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
     config = qwen15b_config(args, fsdp, tp, sp)
     counter = ops.enable_launch_counting()
     with WorkerSession(config, "runtime") as session:
@@ -154,6 +160,8 @@ def run_ours(args):
             async_grad_rs=rc.async_grad_rs, communication_policy=rc.communication_policy,
             directory=None, diagnostics_enabled=False,
             communication_backend=rc.communication_backend, retain_parameters=rc.retain_parameters,
+            compute_dtype="bf16", device_wait_seconds=config.debug.distributed_timeout_seconds,
+            wire_dtype="fp32" if args.fp32_wire else "bf16",
         ).register(model, mesh if session.worker.launched else None, sp=sp)
         trainer = QwenTrainer(model, runtime, config.training.lr, dtype="bf16", optimizer="adamw",
                               accumulation_steps=config.training.accumulation_steps)
@@ -162,6 +170,10 @@ def run_ours(args):
         host_ids = torch.randint(model.config.vocab_size, (per_rank, config.model.seq_len),
                                  generator=gen).pin_memory()
         ids = host_ids.to(device)
+        # the reference's own benchmark passes an all-ones key mask and explicit positions
+        # (src/sharded_runtime/training/qwen2_benchmark.py:311-317): same inputs here
+        mask = torch.ones_like(ids)
+        positions = torch.arange(config.model.seq_len, device=device).unsqueeze(0)
         multi = session.worker.launched and session.worker.world_size > 1
 
         def fence():
@@ -169,21 +181,29 @@ def run_ours(args):
                 dist.barrier()
             torch.cuda.synchronize(device)
 
+        def step(tokens):
+            return trainer.train_step(tokens, tokens, attention_mask=mask, position_ids=positions)
+
         losses = []
         for _ in range(args.warmup):
-            losses.append(trainer.train_step(ids).loss)
+            losses.append(step(ids).loss)
         # ---- device-timed region: exactly K steps
         sampler = ClockSampler(device.index or 0)
         sampler.start()
         fence()
         launches_before = counter.launches
+        trainer.blocked_seconds = 0.0
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         begin.record()
         for _ in range(args.steps):
-            result = trainer.train_step(ids)
+            result = step(ids)
         end.record()
+        host_wall = time.perf_counter() - t0
         fence()
         elapsed_ms = begin.elapsed_time(end)
+        # host time not spent blocked in the per-step device-to-host read of the metrics
+        host_ms = (host_wall - trainer.blocked_seconds) * 1e3 / args.steps
         launches = counter.launches - launches_before
         clocks = sampler.stop()
         losses.append(result.loss)
@@ -192,49 +212,95 @@ def run_ours(args):
         t0 = time.perf_counter()
         for _ in range(args.steps):
             step_ids = host_ids.to(device, non_blocking=True)
-            result = trainer.train_step(step_ids)
+            result = step(step_ids)
         fence()
         e2e_ms = (time.perf_counter() - t0) * 1e3
         ops.check_status("bench")
-        times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+        times = torch.tensor([elapsed_ms, e2e_ms, host_ms], device=device, dtype=torch.float64)
         if multi:
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = times.tolist()
-        ms = elapsed_ms / args.steps
-        value = VALID_LABELS_PER_STEP * 1000.0 / ms
-        strategy = config.parallel.strategy
-        published = PUBLISHED.get(args.gpus, {}).get(strategy)
-        line = {
-            "metric": "effective_labels_per_second", "value": value, "unit": "labels/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": value / published if published else None,
-            "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
-            "impl": "ours",
-            "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else ""),
-                       "global_batch": 16, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
-                       "parallelism": strategy, "valid_labels_per_step": VALID_LABELS_PER_STEP,
-                       "precision": "bf16 GEMMs; fp32 shards, gradients, communication, AdamW state",
-                       "runtime": {"reshard_after_forward": rc.reshard_after_forward,
-                                   "forward_prefetch": rc.forward_prefetch,
-                                   "backward_prefetch": rc.backward_prefetch,
-                                   "async_grad_rs": rc.async_grad_rs,
-                                   "communication_policy": rc.communication_policy,
-                                   "executor": runtime.executor.name,
-                                   "retain_parameters": rc.retain_parameters},
-                       "l2": "no explicit flush: each step streams >6 GB of parameters, "
-                             "gradients and optimizer state per GPU group, far above the 126 MB L2"},
-            "clocks": clocks,
-            "e2e": {"value": VALID_LABELS_PER_STEP * 1000.0 * args.steps / e2e_ms,
-                    "unit": "labels/s", "ms_per_step": e2e_ms / args.steps,
-                    "h2d_bytes_per_step": host_ids.numel() * host_ids.element_size() * fsdp,
-                    "d2h_bytes_per_step": 40 * args.gpus},
-            "gpu_launches": launches,
-            "loss_first_last": [losses[0] if losses else None, losses[-1]],
-            "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2**30,
-        }
-        if rank == 0:
-            print(json.dumps(line), flush=True)
+        elapsed_ms, e2e_ms, host_ms = times.tolist()
+        out = dict(
+            strategy=config.parallel.strategy, rank=rank, ms=elapsed_ms / args.steps,
+            e2e_ms=e2e_ms / args.steps, host_ms=host_ms, launches=launches, clocks=clocks,
+            losses=[losses[0] if losses else None, losses[-1]],
+            h2d=host_ids.numel() * host_ids.element_size() * fsdp,
+            peak=torch.cuda.max_memory_allocated(device) / 2**30,
+            executor=runtime.executor.name,
+            switches={"reshard_after_forward": rc.reshard_after_forward,
+                      "forward_prefetch": rc.forward_prefetch,
+                      "backward_prefetch": rc.backward_prefetch,
+                      "async_grad_rs": rc.async_grad_rs,
+                      "communication_policy": rc.communication_policy,
+                      "retain_parameters": rc.retain_parameters},
+        )
+        del trainer, model
+        runtime.close()
+        del runtime
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args):
+    fsdp, tp, sp = resolve_strategy(args)
+    if fsdp * tp != args.gpus:
+        raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
+    m = measure_ours(args, fsdp, tp, sp)
+    value = VALID_LABELS_PER_STEP * 1000.0 / m["ms"]
+    published = PUBLISHED.get(args.gpus, {}).get(m["strategy"])
+    wire = ("fp32 parameter shards" if args.fp32_wire else
+            "bf16 shadow of the fp32 shards for matrices, fp32 for vectors")
+    line = {
+        "metric": "effective_labels_per_second", "value": value, "unit": "labels/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": m["ms"],
+        "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / published if published else None,
+        "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else ""),
+                   "global_batch": 16, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
+                   "parallelism": m["strategy"], "valid_labels_per_step": VALID_LABELS_PER_STEP,
+                   "precision": "bf16 GEMM operands, fp32 accumulation; fp32 master shards, "
+                                "gradients and AdamW state; on the wire: " + wire +
+                                ", fp32 gradients, bf16 sequence-parallel activations with fp32 "
+                                "partial sums",
+                   "inputs": "token ids + all-ones attention_mask + position_ids, as the "
+                             "reference benchmark passes them",
+                   "runtime": {**m["switches"], "executor": m["executor"]},
+                   "l2": "no explicit flush: each step streams >6 GB of parameters, "
+                         "gradients and optimizer state per GPU group, far above the 126 MB L2"},
+        "clocks": m["clocks"],
+        "e2e": {"value": VALID_LABELS_PER_STEP * 1000.0 / m["e2e_ms"],
+                "unit": "labels/s", "ms_per_step": m["e2e_ms"],
+                "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": 40 * args.gpus},
+        "gpu_launches": m["launches"],
+        "launches_per_step": m["launches"] / args.steps,
+        "host_enqueue_ms_per_step": m["host_ms"],
+        "loss_first_last": m["losses"],
+        "peak_memory_gib": m["peak"],
+    }
+    # the second strategy the headline metric names for this GPU count (F4T2/SP on 8, F2T2/SP on
+    # 4, F1T2/SP on 2), same steps and warm-up; skipped when a strategy was asked for explicitly
+    hybrid = HYBRID.get(args.gpus)
+    if hybrid is not None and not args.strategy and not args.no_secondary:
+        try:
+            h = measure_ours(args, *hybrid)
+            hv = VALID_LABELS_PER_STEP * 1000.0 / h["ms"]
+            line["secondary"] = {
+                "parallelism": h["strategy"], "value": hv, "unit": "labels/s",
+                "ms_per_step": h["ms"],
+                "e2e": {"value": VALID_LABELS_PER_STEP * 1000.0 / h["e2e_ms"],
+                        "ms_per_step": h["e2e_ms"], "h2d_bytes_per_step": h["h2d"],
+                        "d2h_bytes_per_step": 40 * args.gpus},
+                "loss_first_last": h["losses"], "clocks": h["clocks"],
+                "gpu_launches": h["launches"], "host_enqueue_ms_per_step": h["host_ms"],
+                "vs_baseline": (hv / PUBLISHED[args.gpus][h["strategy"]]
+                                if h["strategy"] in PUBLISHED.get(args.gpus, {}) else None),
+            }
+        except Exception as exc:  # noqa: BLE001 - the primary measurement must still be printed
+            line["secondary"] = {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    if m["rank"] == 0:
+        print(json.dumps(line), flush=True)
 
 
 def main():

@@ -17,7 +17,8 @@ CSRC = ROOT / "csrc"
 OUT = ROOT / "_C.so"
 OBJ = ROOT / "csrc" / "build"
 
-CUDA_SOURCES = ["gemm_sm100.cu", "elementwise.cu", "peer.cu", "attention_sm100.cu", "noalloc.cu"]
+CUDA_SOURCES = ["gemm_sm100.cu", "gemm_allgather_sm100.cu", "elementwise.cu", "peer.cu",
+                "attention_sm100.cu", "noalloc.cu"]
 CPP_SOURCES = ["bindings.cpp", "layer_executor.cpp"]
 NVCC_FLAGS = [
     "-gencode",

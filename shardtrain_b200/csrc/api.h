@@ -2,10 +2,15 @@
 // bindings.cpp wraps these as torch custom ops; every function enqueues on `stream` and returns
 // the CUDA error of the launch, never synchronising the device.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace stb {
+
+// Streaming multiprocessors of the current device (queried once per process; grids are sized from
+// it instead of from a constant).
+int sm_count();
 
 // ------------------------------------------------------------------ GEMM (gemm_sm100.cu)
 struct GemmCall {
@@ -121,7 +126,8 @@ struct TpAxis {
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        int* flags, cudaStream_t s, TpAxis tp = TpAxis{});
+                                        int* flags, cudaStream_t s, TpAxis tp = TpAxis{},
+                                        const int* status = nullptr);
 // Same, and applies AdamW to the owned shard in the same pass (last micro-step only).
 // `flags` (optional, int[2]) receives the gradient check of what was written: [0] non-finite
 // value, [1] non-zero shard padding.
@@ -130,7 +136,45 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
                                         cudaStream_t s, TpAxis tp = TpAxis{},
-                                        void* shadow = nullptr);   // bf16 copy of p, same offsets
+                                        void* shadow = nullptr,    // bf16 copy of p, same offsets
+                                        const int* status = nullptr);
+// `status` (both reductions): when the word already holds a failure code on entry the kernel
+// returns without touching gradients or parameters (the data it would reduce may be stale).
+// ------------------------------------------------------------------ all-gather -> GEMM (gemm_allgather_sm100.cu)
+// One FSDP-sharded parameter of the fused weight: `rows` consecutive rows of W, stored flat
+// ([rows * K] elements) and cut into F shards of q elements that sit at `shard_off` in every
+// rank's arena; `full_off` is where the parameter starts in the local full (gathered) buffer.
+struct AgSegment {
+  int64_t shard_off, q, full_off;
+  int rows;
+};
+struct AgWeights {
+  const __nv_bfloat16* shadow[kMaxPeers];  // bf16 arenas (one per FSDP rank); shadow[0] == nullptr
+  const float* shard[kMaxPeers];           // ... selects the fp32 arenas (fp32 on the wire)
+  int degree;
+  int n_segs;                              // 1..4 parameters, in row order of the fused weight
+  AgSegment seg[4];
+  __nv_bfloat16* full;                     // optional: the pulled rows are also stored here
+};
+// out[M, N] = a[M, K] * W[N, K]^T (+ bias), W pulled from the FSDP ranks' arenas inside the GEMM
+// (peer pointers are read with plain loads; tensor maps cover local memory only).  Gated mode
+// (gated_inter > 0): W = gate|up (two segments of gated_inter rows), out = [M, 2 * gated_inter]
+// gate|up and gated_out = [M, gated_inter] silu(gate) * up, all bf16.  When M needs more row
+// tiles than TMEM holds accumulators (512 / tile width), `w.full` is required: later passes read
+// the weight from there instead of crossing the link again.
+struct AgGemmCall {
+  const void* a;        // bf16 [M, lda], local
+  void* out;            // bf16 [M, ldo]
+  const float* bias;    // optional fp32 [N]
+  void* gated_out;
+  int M, N, K;
+  int64_t lda, ldo;
+  int gated_inter;
+  int force_bn;         // 0 = rule, else 64 or 128 (plain mode only)
+  AgWeights w;
+};
+cudaError_t launch_gemm_allgather(const AgGemmCall& c, int* status, cudaStream_t stream);
+
 // Embedding lookup straight from the (possibly remote) fp32 shards: no all-gather of the table.
 cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t q,
                                             const int64_t* ids, float* out, int rows, int cols,
@@ -142,9 +186,12 @@ cudaError_t launch_seq_gather(const void* const* peers, int degree, void* out, i
 cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree, int rank,
                                           const float* residual, float* out, int batch,
                                           int seq_local, int cols, cudaStream_t s);
-// Cross-GPU barrier over flag words in peer memory; bounded spin, status word on expiry.
+// Cross-GPU barrier over flag words in peer memory.  The wait is bounded by `budget_ns`
+// nanoseconds of the global timer; on expiry the status block records {code, silent member,
+// epoch awaited, epoch seen}.  With a failure already recorded the kernel publishes its epoch
+// and returns without waiting.
 cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank, uint32_t epoch,
-                                int slot, int* status, uint32_t max_spin, cudaStream_t s);
+                                int slot, int* status, uint64_t budget_ns, cudaStream_t s);
 
 // All-reduce of up to 16 doubles over peer memory in one launch (the per-step metrics: valid-label
 // count, loss numerator, finite vote).  Element i is summed, or minimised when bit i of min_mask
@@ -153,7 +200,7 @@ cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank
 cudaError_t launch_peer_allreduce_small(uint32_t* const* flag_pads, double* const* inboxes, int degree,
                                         int rank, uint32_t epoch, int slot, const double* in,
                                         double* out, int n, uint32_t min_mask, int* status,
-                                        uint32_t max_spin, cudaStream_t s);
+                                        uint64_t budget_ns, cudaStream_t s);
 
 // ------------------------------------------------------------------ attention (attention_sm100.cu)
 struct AttnCall {

@@ -78,6 +78,7 @@ constexpr int kFwdSmem = kTile + 4 * kTile + kTile + 1024 + 256;
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
+  if (kernel_should_skip(p.status)) return;   // an earlier kernel already failed
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -331,6 +332,7 @@ constexpr int kDqSmem = 5 * kTile + 1024 + 256;
 __global__ void __launch_bounds__(kThreads, 1)
 attention_dq_kernel(const __grid_constant__ CUtensorMap map_qkv,
                     const __grid_constant__ CUtensorMap map_do, BwdParams p) {
+  if (kernel_should_skip(p.status)) return;   // an earlier kernel already failed
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -490,6 +492,7 @@ constexpr int kDkvSmem = 6 * kTile + 1024 + 1024 + 256;
 __global__ void __launch_bounds__(kThreads, 1)
 attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
                      const __grid_constant__ CUtensorMap map_do, BwdParams p) {
+  if (kernel_should_skip(p.status)) return;   // an earlier kernel already failed
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -761,7 +764,7 @@ cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t
   attention_dq_kernel<<<dim3(nblk, c.hq, c.batch), kThreads, kDqSmem, s>>>(map_qkv, map_do, p);
   if (parts > 1) {
     const int64_t work = rows * (2 * c.hkv * kD / 8);
-    const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, 148 * 8));
+    const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, sm_count() * 8));
     attention_dkv_finish_kernel<<<grid, 256, 0, s>>>(c.dkv_accum, parts, rows, c.hq, c.hkv,
                                                      reinterpret_cast<__nv_bfloat16*>(c.dqkv));
   }
@@ -774,7 +777,7 @@ int attention_bwd_parts(int batch, int seq, int hq, int hkv) {
   const int nblk = (seq + kBlk - 1) / kBlk;
   const int base = nblk * hkv * batch;
   for (int parts = 1; parts <= group; ++parts)
-    if (group % parts == 0 && base * parts >= 148) return parts;
+    if (group % parts == 0 && base * parts >= sm_count()) return parts;
   return group;
 }
 

@@ -486,7 +486,7 @@ void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor
                                            static_cast<int>(rank), table.data() + i, n,
                                            grad_shard.data_ptr<float>(), grad_shard.numel(),
                                            static_cast<float>(scale), accumulate, flags_ptr(flags),
-                                           cur_stream(), tp),
+                                           cur_stream(), tp, status_ptr()),
           "reduce_scatter");
   }
 }
@@ -514,9 +514,71 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
               m.data_ptr<float>(), v.data_ptr<float>(), grad_shard.numel(),
               static_cast<float>(scale), accumulate,
               adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream(), tp,
-              shadow_ptr),
+              shadow_ptr, status_ptr()),
           "reduce_scatter_adamw");
   }
+}
+
+// Parameter all-gather fused into the consuming GEMM.  `segs`: CPU int64 [n, 5] rows of the
+// unit's gather table (shard_off, q, numel, full_off, flags) for the n <= 4 parameters that form
+// the fused weight, in row order.  `arena_ptrs`: one arena base per FSDP rank -- bf16 shadow
+// arenas when `wire_fp32` is false, fp32 shard arenas otherwise.  `full` (optional): the unit's
+// local bf16 full-parameter buffer; the pulled rows are mirrored into it.
+void gemm_allgather(const Tensor& a, Tensor out, const c10::optional<Tensor>& bias,
+                    c10::ArrayRef<int64_t> arena_ptrs, bool wire_fp32, const Tensor& segs,
+                    const c10::optional<Tensor>& full, const c10::optional<Tensor>& gated_out,
+                    int64_t force_bn) {
+  need(a, at::kBFloat16, "a");
+  need(out, at::kBFloat16, "out");
+  TORCH_CHECK(a.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && out.stride(1) == 1 &&
+                  out.size(0) == a.size(0),
+              "gemm_allgather: a and out must be 2-D with a contiguous inner dimension");
+  TORCH_CHECK(!arena_ptrs.empty() && arena_ptrs.size() <= stb::kMaxPeers, "1..8 arenas expected");
+  const auto table = read_segs(segs);
+  TORCH_CHECK(!table.empty() && table.size() <= 4, "1..4 weight segments expected");
+  const c10::cuda::CUDAGuard guard(a.device());
+  stb::AgGemmCall c{};
+  c.a = a.data_ptr();
+  c.out = out.data_ptr();
+  c.M = static_cast<int>(a.size(0));
+  c.K = static_cast<int>(a.size(1));
+  c.N = static_cast<int>(out.size(1));
+  c.lda = a.stride(0);
+  c.ldo = out.stride(0);
+  c.force_bn = static_cast<int>(force_bn);
+  if (bias.has_value()) {
+    need(*bias, at::kFloat, "bias");
+    TORCH_CHECK(bias->numel() == c.N, "bias length mismatch");
+    c.bias = bias->data_ptr<float>();
+  }
+  c.w.degree = static_cast<int>(arena_ptrs.size());
+  for (size_t i = 0; i < arena_ptrs.size(); ++i) {
+    if (wire_fp32)
+      c.w.shard[i] = reinterpret_cast<const float*>(arena_ptrs[i]);
+    else
+      c.w.shadow[i] = reinterpret_cast<const __nv_bfloat16*>(arena_ptrs[i]);
+  }
+  c.w.n_segs = static_cast<int>(table.size());
+  for (size_t j = 0; j < table.size(); ++j) {
+    TORCH_CHECK(table[j].numel % c.K == 0, "a weight segment is not a whole number of rows");
+    c.w.seg[j].shard_off = table[j].shard_off;
+    c.w.seg[j].q = table[j].q;
+    c.w.seg[j].full_off = table[j].full_off;
+    c.w.seg[j].rows = static_cast<int>(table[j].numel / c.K);
+  }
+  if (full.has_value()) {
+    need(*full, at::kBFloat16, "full");
+    c.w.full = reinterpret_cast<__nv_bfloat16*>(full->data_ptr());
+  }
+  if (gated_out.has_value()) {
+    need(*gated_out, at::kBFloat16, "gated_out");
+    TORCH_CHECK(gated_out->is_contiguous() && gated_out->size(0) == a.size(0) &&
+                    gated_out->size(1) * 2 == out.size(1),
+                "gemm_allgather: gated_out must be [M, N / 2]");
+    c.gated_out = gated_out->data_ptr();
+    c.gated_inter = static_cast<int>(gated_out->size(1));
+  }
+  check(stb::launch_gemm_allgather(c, status_ptr(), cur_stream()), "gemm_allgather");
 }
 
 void embedding_gather_sharded(c10::ArrayRef<int64_t> shard_ptrs, int64_t q, const Tensor& ids,
@@ -555,20 +617,26 @@ void seq_reduce_scatter(c10::ArrayRef<int64_t> ptrs, int64_t rank,
         "seq_reduce_scatter");
 }
 
+// `wait_us`: time budget of the flag wait in microseconds.
+uint64_t budget_ns(int64_t wait_us) {
+  TORCH_CHECK(wait_us > 0, "the wait budget must be positive (microseconds)");
+  return static_cast<uint64_t>(wait_us) * 1000ull;
+}
+
 void peer_barrier(c10::ArrayRef<int64_t> pad_ptrs, int64_t rank, int64_t epoch, int64_t slot,
-                  int64_t max_spin) {
+                  int64_t wait_us) {
   std::vector<uint32_t*> p(pad_ptrs.size());
   for (size_t i = 0; i < pad_ptrs.size(); ++i) p[i] = reinterpret_cast<uint32_t*>(pad_ptrs[i]);
   check(stb::launch_peer_barrier(p.data(), static_cast<int>(pad_ptrs.size()),
                                  static_cast<int>(rank), static_cast<uint32_t>(epoch),
                                  static_cast<int>(slot), status_ptr(),
-                                 static_cast<uint32_t>(max_spin), cur_stream()),
+                                 budget_ns(wait_us), cur_stream()),
         "peer_barrier");
 }
 
 void peer_allreduce_small(c10::ArrayRef<int64_t> pad_ptrs, c10::ArrayRef<int64_t> inbox_ptrs,
                           int64_t rank, int64_t epoch, int64_t slot, const Tensor& in, Tensor out,
-                          int64_t min_mask, int64_t max_spin) {
+                          int64_t min_mask, int64_t wait_us) {
   need(in, at::kDouble, "in");
   need(out, at::kDouble, "out");
   TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.numel() == out.numel() &&
@@ -584,7 +652,7 @@ void peer_allreduce_small(c10::ArrayRef<int64_t> pad_ptrs, c10::ArrayRef<int64_t
             pads.data(), inboxes.data(), static_cast<int>(pads.size()), static_cast<int>(rank),
             static_cast<uint32_t>(epoch), static_cast<int>(slot), in.data_ptr<double>(),
             out.data_ptr<double>(), static_cast<int>(in.numel()), static_cast<uint32_t>(min_mask),
-            status_ptr(), static_cast<uint32_t>(max_spin), cur_stream()),
+            status_ptr(), budget_ns(wait_us), cur_stream()),
         "peer_allreduce_small");
 }
 
@@ -596,6 +664,7 @@ int64_t peer_alloc(int64_t nbytes) {
   return reinterpret_cast<int64_t>(p);
 }
 void peer_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
+void device_synchronize() { check(cudaDeviceSynchronize(), "device_synchronize"); }
 Tensor ipc_handle(int64_t ptr) {
   cudaIpcMemHandle_t h;
   check(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr)), "ipc_handle");
@@ -708,6 +777,9 @@ TORCH_LIBRARY(stb, m) {
         "float wd, float bc1, float bc2, float gscale, Tensor? flags, int tp_degree=1, "
         "int tp_rank=0, float rep_scale=1.0, Tensor? shadow=None) -> ()",
         &reduce_scatter_adamw);
+  m.def("gemm_allgather(Tensor a, Tensor out, Tensor? bias, int[] arena_ptrs, bool wire_fp32, "
+        "Tensor segs, Tensor? full, Tensor? gated_out, int force_bn=0) -> ()",
+        &gemm_allgather);
   m.def("embedding_gather_sharded", &embedding_gather_sharded);
   m.def("seq_gather", &seq_gather);
   m.def("seq_reduce_scatter", &seq_reduce_scatter);
@@ -715,6 +787,7 @@ TORCH_LIBRARY(stb, m) {
   m.def("peer_allreduce_small", &peer_allreduce_small);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);
+  m.def("device_synchronize", &device_synchronize);
   m.def("ipc_handle", &ipc_handle);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);

@@ -1,7 +1,7 @@
 // Shared device-side primitives for the sm_100a kernels: mbarrier, TMA (bulk tensor) loads,
 // tcgen05 (5th-gen tensor core) MMA / TMEM access, and bounded waits.
 //
-// Every wait in this file has an iteration limit.  When a wait runs out it records a code in a
+// Every wait in this file has a time limit.  When a wait runs out it records a code in a
 // global status word and returns false; callers leave their loops, the CTA tears down normally
 // (TMEM freed, outstanding copies drained with a second bounded wait) and the host raises after
 // reading the status word.  Nothing here traps or spins without limit.
@@ -25,9 +25,33 @@ enum : int {
   kErrBadArgument = 7,
 };
 
-// ~2^26 polls of try_wait (each poll itself blocks for a short hardware-defined time) is far
-// beyond any legitimate wait inside one kernel, and still finite.
-constexpr uint32_t kMaxSpin = 1u << 26;
+// Waits are bounded in *time*: after a short burst of polls that never reads a clock, a waiter
+// compares the global nanosecond timer against a budget and also gives up as soon as another
+// kernel (or another CTA) has already recorded a failure in the status word, so one silent peer
+// cannot make every kernel queued behind it spin its whole budget in turn.
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;   // 2 s: far beyond any legitimate in-kernel wait
+constexpr uint32_t kFastPolls = 2048;
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// True when some kernel already recorded a failure: work queued behind it must not run on data a
+// silent peer never delivered.  Call from one thread and broadcast (see kernel_should_skip).
+__device__ __forceinline__ bool status_failed(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != kOk;
+}
+
+// CTA-uniform entry check: every thread returns the same answer, so a kernel may `return` on it
+// before it initialises barriers or allocates TMEM.
+__device__ __forceinline__ bool kernel_should_skip(const int* status) {
+  __shared__ int skip;
+  if (threadIdx.x == 0) skip = status_failed(status) ? 1 : 0;
+  __syncthreads();
+  return skip != 0;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -72,10 +96,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false (and the status word set) once the limit is reached.
+// Bounded wait: false (and the status word set) once the time budget is spent, or as soon as the
+// status word shows that something else already failed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < kMaxSpin; ++i) {
+  for (uint32_t i = 0; i < kFastPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+  }
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (uint32_t i = 0; i < 256; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (status_failed(status)) return false;
+    if (global_ns() - t0 > kWaitBudgetNs) break;
   }
   if (status != nullptr) atomicCAS(status, kOk, code);
   return false;

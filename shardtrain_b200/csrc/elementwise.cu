@@ -488,7 +488,9 @@ __global__ void grad_check_kernel(const float* __restrict__ g, int64_t n,
   if (__syncthreads_or(padbad) && threadIdx.x == 0) atomicOr(&flags[1], 1);
 }
 
-inline int grid_for(int64_t work, int threads, int cap = 148 * 8) {
+// cap = 0: eight CTAs per SM of the current device
+inline int grid_for(int64_t work, int threads, int cap = 0) {
+  if (cap <= 0) cap = sm_count() * 8;
   int64_t g = (work + threads - 1) / threads;
   if (g < 1) g = 1;
   if (g > cap) g = cap;
@@ -560,7 +562,7 @@ cudaError_t launch_rope(void* qkv, const float* cos, const float* sin, const int
 cudaError_t launch_swiglu_fwd(const void* gu, void* h, int rows, int inter, cudaStream_t s) {
   if (inter % 8) return cudaErrorInvalidValue;
   const int64_t work = static_cast<int64_t>(rows) * (inter / 8);
-  swiglu_fwd_kernel<<<grid_for(work, 256, 148 * 16), 256, 0, s>>>(
+  swiglu_fwd_kernel<<<grid_for(work, 256, sm_count() * 16), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(gu), reinterpret_cast<__nv_bfloat16*>(h), rows, inter);
   return cudaGetLastError();
 }
@@ -569,7 +571,7 @@ cudaError_t launch_swiglu_bwd(const void* dh, const void* gu, void* dgu, int row
                               cudaStream_t s) {
   if (inter % 8) return cudaErrorInvalidValue;
   const int64_t work = static_cast<int64_t>(rows) * (inter / 8);
-  swiglu_bwd_kernel<<<grid_for(work, 256, 148 * 16), 256, 0, s>>>(
+  swiglu_bwd_kernel<<<grid_for(work, 256, sm_count() * 16), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(dh), reinterpret_cast<const __nv_bfloat16*>(gu),
       reinterpret_cast<__nv_bfloat16*>(dgu), rows, inter);
   return cudaGetLastError();
@@ -603,30 +605,30 @@ cudaError_t launch_embedding_scatter_add(const float* dx, const int64_t* ids, fl
 }
 
 cudaError_t launch_cast_f32_to_bf16(const float* x, void* y, int64_t n, cudaStream_t s) {
-  cast_f32_bf16_kernel<<<grid_for(n / 4 + 1, 256, 148 * 16), 256, 0, s>>>(
+  cast_f32_bf16_kernel<<<grid_for(n / 4 + 1, 256, sm_count() * 16), 256, 0, s>>>(
       x, reinterpret_cast<__nv_bfloat16*>(y), n);
   return cudaGetLastError();
 }
 
 cudaError_t launch_add_f32(const float* a, const float* b, float* out, int64_t n, cudaStream_t s) {
-  add_f32_kernel<<<grid_for(n / 4 + 1, 256, 148 * 16), 256, 0, s>>>(a, b, out, n);
+  add_f32_kernel<<<grid_for(n / 4 + 1, 256, sm_count() * 16), 256, 0, s>>>(a, b, out, n);
   return cudaGetLastError();
 }
 
 cudaError_t launch_adamw(float* p, const float* g, float* m, float* v, int64_t n, AdamWArgs a,
                          cudaStream_t s) {
-  adamw_kernel<<<grid_for(n / 4 + 1, 256, 148 * 16), 256, 0, s>>>(p, g, m, v, n, a);
+  adamw_kernel<<<grid_for(n / 4 + 1, 256, sm_count() * 16), 256, 0, s>>>(p, g, m, v, n, a);
   return cudaGetLastError();
 }
 
 cudaError_t launch_sgd(float* p, const float* g, int64_t n, float lr, cudaStream_t s) {
-  sgd_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, s>>>(p, g, n, lr);
+  sgd_kernel<<<grid_for(n, 256, sm_count() * 16), 256, 0, s>>>(p, g, n, lr);
   return cudaGetLastError();
 }
 
 cudaError_t launch_grad_check(const float* g, int64_t n, const int64_t* pad_ranges, int n_ranges,
                               int* flags, cudaStream_t s) {
-  grad_check_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, s>>>(g, n, pad_ranges, n_ranges, flags);
+  grad_check_kernel<<<grid_for(n, 256, sm_count() * 8), 256, 0, s>>>(g, n, pad_ranges, n_ranges, flags);
   return cudaGetLastError();
 }
 

@@ -83,17 +83,18 @@ bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int6
   return true;
 }
 
-namespace {
-
 int sm_count() {
   static int n = [] {
-    int dev = 0, v = 148;
+    int dev = 0, v = 0;
     cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v < 1)
+      v = 1;
     return v;
   }();
   return n;
 }
+
+namespace {
 
 // How the tail wave of `tiles` tiles is cut along K (see GemmSplit).  `want`: 0 = rule, 1 = never,
 // n > 1 = exactly n (tests).  Returns the split factor and fills full / kb_per.

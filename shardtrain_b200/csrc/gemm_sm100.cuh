@@ -90,6 +90,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   // next; the shared-memory operand pipeline runs across tile boundaries without draining.
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::kStages;
+  // an earlier kernel recorded a failure (a peer that never signalled, a wait that expired): the
+  // operands may be stale, skip the work -- uniformly, before any barrier or TMEM exists
+  if (kernel_should_skip(status)) return;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));

@@ -127,11 +127,11 @@ struct SpLink {
   int rank;
   uint32_t epoch;
   int slot;
-  uint32_t max_spin;
+  uint64_t budget_ns;
   void barrier() {
     ++epoch;
     ok(stb::launch_peer_barrier(pads.data(), static_cast<int>(pads.size()), rank, epoch, slot, status,
-                                max_spin, stream), "sp barrier");
+                                budget_ns, stream), "sp barrier");
   }
   // out[b, r*sl + s, :] = peer r's [b, s, :]
   void gather(c10::ArrayRef<int64_t> src, Tensor& out, int64_t B, int64_t seq_local) const {
@@ -144,9 +144,10 @@ struct SpLink {
 };
 
 SpLink make_link(cudaStream_t st, int* status, c10::ArrayRef<int64_t> pads, int64_t rank,
-                 int64_t epoch, int64_t slot, int64_t max_spin) {
+                 int64_t epoch, int64_t slot, int64_t wait_us) {
+  TORCH_CHECK(wait_us > 0, "the wait budget must be positive (microseconds)");
   SpLink l{st, status, {}, static_cast<int>(rank), static_cast<uint32_t>(epoch),
-           static_cast<int>(slot), static_cast<uint32_t>(max_spin)};
+           static_cast<int>(slot), static_cast<uint64_t>(wait_us) * 1000ull};
   for (int64_t p : pads) l.pads.push_back(reinterpret_cast<uint32_t*>(p));
   return l;
 }
@@ -288,7 +289,7 @@ std::vector<Tensor> layer_forward_sp(
     int64_t hkv, double eps, Tensor h1_local, Tensor h2_local, c10::ArrayRef<int64_t> h1_ptrs,
     c10::ArrayRef<int64_t> h2_ptrs, c10::ArrayRef<int64_t> push_ptrs, Tensor recv,
     c10::ArrayRef<int64_t> flag_ptrs, int64_t tp_rank, int64_t epoch, int64_t flag_slot,
-    int64_t max_spin) {
+    int64_t wait_us) {
   const int64_t T = static_cast<int64_t>(h1_ptrs.size());
   const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
@@ -299,7 +300,7 @@ std::vector<Tensor> layer_forward_sp(
   auto f32 = x2.options().dtype(at::kFloat);
   cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
   Gemm g{st, status.data_ptr<int>()};
-  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
   const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
   const float feps = static_cast<float>(eps);
@@ -353,7 +354,7 @@ Tensor layer_backward_sp(
     Tensor dmb_local, c10::ArrayRef<int64_t> h1_ptrs, c10::ArrayRef<int64_t> h2_ptrs,
     c10::ArrayRef<int64_t> dob_ptrs, c10::ArrayRef<int64_t> dmb_ptrs,
     c10::ArrayRef<int64_t> push_ptrs, Tensor recv, c10::ArrayRef<int64_t> flag_ptrs,
-    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t max_spin) {
+    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t wait_us) {
   const int64_t T = static_cast<int64_t>(h1_ptrs.size());
   const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
@@ -361,7 +362,7 @@ Tensor layer_backward_sp(
   auto f32 = x2.options().dtype(at::kFloat);
   cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
   Gemm g{st, status.data_ptr<int>()};
-  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
   const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
   constexpr int kPartial = 592;
@@ -454,7 +455,7 @@ std::vector<Tensor> layer_forward_tp(
     const c10::optional<Tensor>& mask, Tensor status, int64_t B, int64_t S, int64_t hq,
     int64_t hkv, double eps, c10::ArrayRef<int64_t> push_a, c10::ArrayRef<int64_t> push_b,
     Tensor recv_a, Tensor recv_b, c10::ArrayRef<int64_t> flag_ptrs, int64_t tp_rank,
-    int64_t epoch, int64_t flag_slot, int64_t max_spin) {
+    int64_t epoch, int64_t flag_slot, int64_t wait_us) {
   const int64_t T = static_cast<int64_t>(push_a.size());
   const int64_t M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
@@ -464,7 +465,7 @@ std::vector<Tensor> layer_forward_tp(
   auto f32 = x2.options().dtype(at::kFloat);
   cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
   Gemm g{st, status.data_ptr<int>()};
-  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
   const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
   const float feps = static_cast<float>(eps);
@@ -510,7 +511,7 @@ Tensor layer_backward_tp(
     const Tensor& sin, const c10::optional<Tensor>& positions, const c10::optional<Tensor>& mask,
     Tensor status, int64_t B, int64_t S, int64_t hq, int64_t hkv, c10::ArrayRef<int64_t> push_a,
     c10::ArrayRef<int64_t> push_b, Tensor recv_a, Tensor recv_b, c10::ArrayRef<int64_t> flag_ptrs,
-    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t max_spin) {
+    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t wait_us) {
   const int64_t T = static_cast<int64_t>(push_a.size());
   const int64_t M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
@@ -518,7 +519,7 @@ Tensor layer_backward_tp(
   auto f32 = x2.options().dtype(at::kFloat);
   cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
   Gemm g{st, status.data_ptr<int>()};
-  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, max_spin);
+  SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
   const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
   constexpr int kPartial = 592;

@@ -1,6 +1,7 @@
 // Allocation-free column sum (see noalloc.h for the contract and for who needs it).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 #include "noalloc.h"
 
@@ -47,6 +48,10 @@ extern "C" int stb_colsum_bf16_noalloc(const void* x, int64_t ldx, float* out, i
                                        int accumulate, void* stream) {
   if (x == nullptr || out == nullptr || rows <= 0 || cols <= 0 || (cols & 1) ||
       cols > STB_COLSUM_NOALLOC_MAX_COLS || ldx < cols || (ldx & 1))
+    return -1;
+  // the kernels read x two bf16 at a time (4-byte loads) and write fp32: a view that starts at an
+  // odd element offset would be a misaligned device access, so it is refused here, unlaunched
+  if ((reinterpret_cast<uintptr_t>(x) & 3) != 0 || (reinterpret_cast<uintptr_t>(out) & 3) != 0)
     return -1;
   int device = 0;
   cudaError_t err = cudaGetDevice(&device);

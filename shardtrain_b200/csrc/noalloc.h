@@ -22,9 +22,13 @@ extern "C" {
 // out fp32 [cols].  `stream` is a cudaStream_t (0 = default stream).  Enqueues two kernels and
 // returns without synchronising.
 //
-// Returns 0 on success; -1 for cols > STB_COLSUM_NOALLOC_MAX_COLS, odd cols, non-positive sizes,
-// null pointers or ldx < cols (nothing is launched); otherwise the positive cudaError_t value of
-// the failing runtime call.
+// Alignment: x must be 4-byte aligned (the kernel loads two bf16 per access), so cols and ldx
+// must be even and a view may not start at an odd element offset of its storage; out must be
+// 4-byte aligned.
+//
+// Returns 0 on success; -1 for cols > STB_COLSUM_NOALLOC_MAX_COLS, odd cols, odd ldx, ldx < cols,
+// non-positive sizes, null pointers, or a misaligned x / out (nothing is launched in any of these
+// cases); otherwise the positive cudaError_t value of the failing runtime call.
 //
 // * Allocation: none -- no cudaMalloc, cudaFree, or allocating library routine is called.
 // * First call on a device: looks up the device address of the workspace once (a host-side

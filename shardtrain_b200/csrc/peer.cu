@@ -7,7 +7,7 @@
 //   * sequence-parallel activation gather / reduce-scatter (src/sharded_runtime/runtime/comm.py:781-884)
 //   * embedding rows fetched from the owning shard without gathering the table.
 // With degree 1 the same kernels read only local memory.  No kernel here waits on another GPU
-// except peer_barrier_kernel, whose spin is bounded.
+// except the flag barrier and the small all-reduce, whose waits are bounded in time.
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -166,7 +166,10 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int t
                                       float* __restrict__ p, float* __restrict__ m,
                                       float* __restrict__ v, float split_scale, float rep_scale,
                                       int accumulate, AdamWArgs a, int* __restrict__ flags,
-                                      __nv_bfloat16* __restrict__ shadow) {
+                                      __nv_bfloat16* __restrict__ shadow, const int* status) {
+  // A failure recorded earlier (a peer that never signalled) means the slots may hold stale
+  // data: neither the gradient shard nor, with ADAMW, the parameters are touched.
+  if (kernel_should_skip(status)) return;
   const SegmentDesc sg = tab.s[blockIdx.y];
   const bool replicated = tp > 1 && sg.pad != 0;
   const int n_src = replicated ? degree * tp : degree;
@@ -362,28 +365,44 @@ __device__ __forceinline__ void report_flag_timeout(int* status, int peer, uint3
   }
 }
 
+// Bounded wait for `*flag` to reach `epoch` (epochs only grow; the signed distance tolerates
+// wrap-around).  The bound is a time budget read from the global nanosecond timer; the wait also
+// ends as soon as the status word shows that something already failed.  Returns true when seen.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, const int* status,
+                                          uint64_t budget_ns) {
+  uint32_t v;
+  for (int i = 0; i < 64; ++i) {   // the common case: the peer is already there or nearly so
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(v - epoch) >= 0) return true;
+  }
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 32; ++i) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) return true;
+      __nanosleep(64);
+    }
+    if (status_failed(status)) return false;
+    if (global_ns() - t0 > budget_ns) return false;
+  }
+}
+
 // Thread t tells peer t "rank `rank` reached `epoch`" and then waits until peer t says the same.
-// Pad layout: pad[slot * kMaxPeers + source_rank].  The spin is bounded; on expiry the status
-// word is set and the kernel returns.
+// Pad layout: pad[slot * kMaxPeers + source_rank].  The wait is bounded in time; on expiry the
+// status block is set and the kernel returns.  When a failure is already recorded on entry the
+// kernel still publishes its own epoch (so that healthy peers are not held up by this rank) but
+// does not wait: after one silent peer the barriers queued behind it return at once.
 __global__ void peer_barrier_kernel(FlagPeers pads, int degree, int rank, uint32_t epoch, int slot,
-                                    int* status, uint32_t max_spin) {
+                                    int* status, uint64_t budget_ns) {
   const int t = threadIdx.x;
   if (t >= degree) return;
+  const bool failed_before = status_failed(status);
   __threadfence_system();
   uint32_t* remote = pads.p[t] + slot * kMaxPeers + rank;
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  if (failed_before) return;
   const uint32_t* mine = pads.p[rank] + slot * kMaxPeers + t;
-  bool seen = false;
-  for (uint32_t i = 0; i < max_spin; ++i) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-    // epochs only grow; signed distance tolerates wrap-around
-    if (static_cast<int32_t>(v - epoch) >= 0) {
-      seen = true;
-      break;
-    }
-    __nanosleep(64);
-  }
+  const bool seen = wait_flag(mine, epoch, status, budget_ns);
   if (!seen && status != nullptr) report_flag_timeout(status, t, epoch, mine);
   __threadfence_system();
 }
@@ -402,27 +421,21 @@ struct InboxPeers {
 __global__ void peer_allreduce_small_kernel(FlagPeers pads, InboxPeers inboxes, int degree, int rank,
                                             uint32_t epoch, int slot, const double* __restrict__ in,
                                             double* __restrict__ out, int n, uint32_t min_mask,
-                                            int* status, uint32_t max_spin) {
+                                            int* status, uint64_t budget_ns) {
   const int t = threadIdx.x;
   const int parity = static_cast<int>(epoch & 1u);
   if (t < degree) {
+    const bool failed_before = status_failed(status);
     double* dst = inboxes.p[t] + (static_cast<int64_t>(parity) * kMaxPeers + rank) * kMetricWidth;
     for (int i = 0; i < n; ++i) dst[i] = in[i];
     __threadfence_system();
     uint32_t* remote = pads.p[t] + slot * kMaxPeers + rank;
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-    const uint32_t* mine = pads.p[rank] + slot * kMaxPeers + t;
-    bool seen = false;
-    for (uint32_t i = 0; i < max_spin; ++i) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-      if (static_cast<int32_t>(v - epoch) >= 0) {
-        seen = true;
-        break;
-      }
-      __nanosleep(64);
+    if (!failed_before) {
+      const uint32_t* mine = pads.p[rank] + slot * kMaxPeers + t;
+      const bool seen = wait_flag(mine, epoch, status, budget_ns);
+      if (!seen && status != nullptr) report_flag_timeout(status, t, epoch, mine);
     }
-    if (!seen && status != nullptr) report_flag_timeout(status, t, epoch, mine);
     __threadfence_system();
   }
   __syncthreads();
@@ -461,9 +474,9 @@ int chunks_for(const SegmentDesc* segs, int n, bool per_shard) {
     const int64_t len = per_shard ? segs[i].q : segs[i].numel;
     most = std::max<int64_t>(most, (len + kChunk - 1) / kChunk);
   }
-  const int64_t budget = std::max<int64_t>(1, (148 * kCtasPerSm) / std::max(1, n));
+  const int64_t budget = std::max<int64_t>(1, (sm_count() * kCtasPerSm) / std::max(1, n));
   // and never more than four CTAs per SM for one segment: more only adds scheduling work
-  return static_cast<int>(std::min<int64_t>({most, budget, static_cast<int64_t>(148 * 4)}));
+  return static_cast<int>(std::min<int64_t>({most, budget, static_cast<int64_t>(sm_count() * 4)}));
 }
 
 }  // namespace
@@ -496,7 +509,7 @@ bool valid_mesh(int degree, int rank, TpAxis tp) {
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        int* flags, cudaStream_t s, TpAxis tp) {
+                                        int* flags, cudaStream_t s, TpAxis tp, const int* status) {
   (void)shard_total;
   SegTable tab;
   if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
@@ -504,7 +517,7 @@ cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int ran
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, nullptr, nullptr, nullptr,
-      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags, nullptr);
+      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags, nullptr, status);
   return cudaGetLastError();
 }
 
@@ -512,7 +525,7 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
-                                        cudaStream_t s, TpAxis tp, void* shadow) {
+                                        cudaStream_t s, TpAxis tp, void* shadow, const int* status) {
   (void)shard_total;
   SegTable tab;
   if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
@@ -521,7 +534,7 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
   reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, p, m, v, scale,
       tp.replicated_scale, accumulate ? 1 : 0, a, flags,
-      reinterpret_cast<__nv_bfloat16*>(shadow));
+      reinterpret_cast<__nv_bfloat16*>(shadow), status);
   return cudaGetLastError();
 }
 
@@ -539,7 +552,7 @@ cudaError_t launch_seq_gather(const void* const* peers, int degree, void* out, i
   VoidPeers vp;
   for (int i = 0; i < degree; ++i) vp.p[i] = peers[i];
   const int64_t total = static_cast<int64_t>(batch) * seq_local * (row_bytes / 16) * degree;
-  const int grid = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, 148 * 8));
+  const int grid = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, sm_count() * 8));
   seq_gather_kernel<<<grid, 256, 0, s>>>(vp, degree, reinterpret_cast<uint4*>(out), batch,
                                          seq_local, row_bytes / 16);
   return cudaGetLastError();
@@ -552,7 +565,7 @@ cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree,
   FloatPeers fp;
   for (int i = 0; i < degree; ++i) fp.p[i] = peers[i];
   const int64_t total = static_cast<int64_t>(batch) * seq_local * (cols / 4);
-  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 8));
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, sm_count() * 8));
   seq_reduce_scatter_kernel<<<grid, 256, 0, s>>>(fp, degree, rank, residual, out, batch, seq_local,
                                                  cols);
   return cudaGetLastError();
@@ -561,7 +574,7 @@ cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree,
 cudaError_t launch_peer_allreduce_small(uint32_t* const* flag_pads, double* const* inboxes, int degree,
                                         int rank, uint32_t epoch, int slot, const double* in,
                                         double* out, int n, uint32_t min_mask, int* status,
-                                        uint32_t max_spin, cudaStream_t s) {
+                                        uint64_t budget_ns, cudaStream_t s) {
   if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree || n < 1 || n > kMetricWidth)
     return cudaErrorInvalidValue;
   FlagPeers fp;
@@ -571,17 +584,17 @@ cudaError_t launch_peer_allreduce_small(uint32_t* const* flag_pads, double* cons
     ip.p[i] = inboxes[i];
   }
   peer_allreduce_small_kernel<<<1, 32, 0, s>>>(fp, ip, degree, rank, epoch, slot, in, out, n,
-                                               min_mask, status, max_spin);
+                                               min_mask, status, budget_ns);
   return cudaGetLastError();
 }
 
 cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank, uint32_t epoch,
-                                int slot, int* status, uint32_t max_spin, cudaStream_t s) {
+                                int slot, int* status, uint64_t budget_ns, cudaStream_t s) {
   if (degree < 1 || degree > kMaxPeers || rank < 0 || rank >= degree)
     return cudaErrorInvalidValue;
   FlagPeers fp;
   for (int i = 0; i < degree; ++i) fp.p[i] = flag_pads[i];
-  peer_barrier_kernel<<<1, 32, 0, s>>>(fp, degree, rank, epoch, slot, status, max_spin);
+  peer_barrier_kernel<<<1, 32, 0, s>>>(fp, degree, rank, epoch, slot, status, budget_ns);
   return cudaGetLastError();
 }
 

@@ -7,11 +7,20 @@ pointer and one device pointer per member (this rank's entry is the local pointe
 kernels take those pointer tables; through NVSwitch every peer is one hop away at full bandwidth.
 
 `barrier(channel)` launches a 1-CTA kernel on the current stream: it publishes a new epoch to
-every peer's flag pad (`st.release.sys`) and waits, with an iteration limit, until every peer has
-published the same epoch to this rank's pad.  Each logical channel has its own flag slot and its
-own epoch counter; all members must call the barriers of a channel in the same order.  When the
-limit is reached the kernel records a status code and returns; `ops.check_status()` raises on the
-host.  With one member every call is a no-op and buffers are ordinary device tensors.
+every peer's flag pad (`st.release.sys`) and waits until every peer has published the same epoch
+to this rank's pad.  The wait is bounded in *time* (`wait_seconds`, seconds rather than minutes;
+derived from `debug.distributed_timeout_seconds` by the executor): when it runs out the kernel
+records a status block and returns, `ops.check_status()` raises on the host, and every barrier
+already queued behind it returns at once instead of spinning its own budget.  Each logical
+channel has its own flag slot and its own epoch counter; all members must call the barriers of a
+channel in the same order.  With one member every call is a no-op and buffers are ordinary
+device tensors.
+
+Teardown: an exported buffer is freed only after every member has said (on the host, through the
+group's store-backed `all_gather_object`, which the group's timeout bounds) that its device is
+idle and its imports are closed.  When that handshake cannot complete -- a member failed, the
+caller says the run failed -- nothing is freed: the buffers stay mapped until the process exits,
+so a peer kernel that is still reading them never sees freed memory.
 """
 
 from __future__ import annotations
@@ -39,12 +48,18 @@ class PeerBuffer:
 
 
 class PeerMemory:
-    def __init__(self, group, device, ops, *, max_spin: int = 200_000_000):
+    MAX_WAIT_SECONDS = 10.0     # upper clamp of any device-side wait
+
+    def __init__(self, group, device, ops, *, wait_seconds: float = 2.0):
         self.group, self.device, self.ops = group, torch.device(device), ops
         live = dist.is_initialized() and group is not None
         self.degree = dist.get_world_size(group) if live else 1
         self.rank = dist.get_rank(group) if live else 0
-        self.max_spin = max_spin
+        if wait_seconds <= 0:
+            raise ValueError("wait_seconds must be positive")
+        # microseconds handed to the kernels; seconds, never minutes, on a shared GPU
+        self.wait_us = max(1, int(min(wait_seconds, self.MAX_WAIT_SECONDS) * 1e6))
+        self.closed = False
         self.epochs = {name: 0 for name in CHANNEL_SLOTS}
         self._allocations: list[PeerBuffer] = []
         self._opened: list[int] = []
@@ -81,7 +96,7 @@ class PeerMemory:
             return
         self.epochs[channel] += 1
         self.ops.peer_barrier(self.flags.ptrs, self.rank, self.epochs[channel],
-                              CHANNEL_SLOTS[channel], self.max_spin)
+                              CHANNEL_SLOTS[channel], self.wait_us)
 
     def all_reduce_small(self, values: torch.Tensor, min_mask: int = 0) -> torch.Tensor:
         """SUM (or MIN where bit i of `min_mask` is set) of a float64 vector of at most
@@ -95,17 +110,46 @@ class PeerMemory:
         self.epochs["metrics"] += 1
         self.ops.peer_allreduce_small(self.flags.ptrs, self.inbox.ptrs, self.rank,
                                       self.epochs["metrics"], CHANNEL_SLOTS["metrics"],
-                                      values.contiguous(), out, min_mask, self.max_spin)
+                                      values.contiguous(), out, min_mask, self.wait_us)
         return out
 
-    def close(self) -> None:
+    def close(self, *, failed: bool = False) -> bool:
+        """Release the peer mappings.  Returns True when the exported buffers were freed.
+
+        Order: (1) this rank's device goes idle, (2) its imports of the peers' buffers are
+        closed, (3) every member reports both on the host, (4) only then are the exported
+        buffers freed.  With `failed=True`, or when step 3 raises (a member is gone, the group's
+        timeout ran out), steps 2-4 are skipped for the exported buffers: they are leaked until
+        the process exits, because a peer may still have a kernel in flight that reads them.
+        """
+        if self.closed:
+            return False
+        self.closed = True
         if self.degree == 1:
             self._allocations.clear()
-            return
-        for ptr in self._opened:
-            self.ops.ipc_close(ptr)
-        self._opened.clear()
+            return True
+        if failed:
+            self._leak()
+            return False
+        try:
+            self.ops.device_synchronize()
+            for ptr in self._opened:
+                self.ops.ipc_close(ptr)
+            self._opened.clear()
+            reports: list = [None] * self.degree
+            dist.all_gather_object(reports, ("idle", self.rank), group=self.group)
+            if any(r is None or r[0] != "idle" for r in reports):
+                raise RuntimeError("a member did not report an idle device")
+        except Exception:  # noqa: BLE001 - any failure of the handshake means: do not free
+            self._leak()
+            return False
         for buf in self._allocations:
             if buf.owner is None:
                 self.ops.peer_free(buf.local_ptr)
+        self._allocations.clear()
+        return True
+
+    def _leak(self) -> None:
+        """Forget the bookkeeping without freeing: the driver reclaims at process exit."""
+        self._opened.clear()
         self._allocations.clear()

@@ -45,7 +45,21 @@ def _coordinates(runtime):
     return runtime.materializer.rank, runtime.tp.rank
 
 
-def save_sharded(runtime, directory, optimizer=None, *, trainer_step=None) -> Path:
+def _refuse_failed(runtime):
+    """A FAILED runtime may hold a half-applied or non-finite update (the fused AdamW runs inside
+    the last reduction, before the step's finite vote is read): its state must never be saved."""
+    if runtime.failed:
+        raise RuntimeError("Refusing to save a checkpoint from a FAILED runtime: its shards may "
+                           "hold the update of the step that failed")
+
+
+def save_sharded(runtime, directory, optimizer=None, *, trainer_step=None, trainer=None) -> Path:
+    """`trainer` (optional): its step counter and loss-scaler state are stored too and restored
+    by `load_sharded(..., trainer=...)`."""
+    _refuse_failed(runtime)
+    if trainer is not None and trainer_step is None:
+        trainer_step = trainer.step_id
+    scaler = getattr(trainer, "scaler", None)
     directory = Path(directory)
     directory.mkdir(parents=True, exist_ok=True)
     f, t = _coordinates(runtime)
@@ -57,6 +71,7 @@ def save_sharded(runtime, directory, optimizer=None, *, trainer_step=None) -> Pa
         "fsdp_rank": f, "tp_rank": t, "runtime_step": runtime.step_id,
         "parameter_version": runtime.parameter_shards_version,
         "optimizer_step": getattr(optimizer, "arena_step", None), "trainer_step": trainer_step,
+        "scaler": scaler.state_dict() if scaler is not None and scaler.is_enabled() else None,
         "specs": {n: {**{k: (str(v) if k == "dtype" else v) for k, v in asdict(h.spec).items()}}
                   for n, h in runtime.registry.items()},
     }
@@ -65,8 +80,15 @@ def save_sharded(runtime, directory, optimizer=None, *, trainer_step=None) -> Pa
 
 
 @torch.no_grad()
-def load_sharded(runtime, directory, optimizer=None) -> dict:
-    """Restore this rank's shards (and moments) written on the same F x T mesh."""
+def load_sharded(runtime, directory, optimizer=None, *, trainer=None) -> dict:
+    """Restore this rank's shards (and moments) written on the same F x T mesh, between steps.
+
+    Also restored: the optimizer's step count, the runtime's step counter (so event logs and
+    leases continue the saved numbering) and, with `trainer`, its step counter and loss-scaler
+    state.  On sm_100a the bf16 shadow of the shards is marked stale, so the next gather first
+    rebuilds it from the loaded FP32 masters."""
+    if runtime.active:
+        raise RuntimeError("load_sharded must run between steps")
     directory = Path(directory)
     f, t = _coordinates(runtime)
     tag = f"f{f}t{t}"
@@ -84,6 +106,16 @@ def load_sharded(runtime, directory, optimizer=None) -> dict:
             arena.narrow(0, h.arena_offset, h.spec.fsdp_shard_numel).copy_(reader.tensor(f"{tag_name}.{name}"))
     if optimizer is not None and meta.get("optimizer_step") is not None:
         optimizer.arena_step = meta["optimizer_step"]
+        for state in getattr(optimizer, "state", {}).values():
+            if "step" in state:
+                state["step"].fill_(float(meta["optimizer_step"]))
+    if meta.get("runtime_step") is not None:
+        runtime.step_id = runtime.comm.step_id = int(meta["runtime_step"])
+    if trainer is not None:
+        if meta.get("trainer_step") is not None:
+            trainer.step_id = int(meta["trainer_step"])
+        if meta.get("scaler") and trainer.scaler.is_enabled():
+            trainer.scaler.load_state_dict(meta["scaler"])
     runtime.parameter_shards_version += 1
     runtime.publish_parameter_shards_ready("checkpoint_load")
     return meta
@@ -115,6 +147,7 @@ def full_state_dict(runtime, optimizer=None) -> dict[str, torch.Tensor]:
 
 def save_full(runtime, directory, optimizer=None) -> Path:
     """Rank 0 writes `model.safetensors` (+ `optimizer.safetensors`); every rank participates."""
+    _refuse_failed(runtime)
     directory = Path(directory)
     state = full_state_dict(runtime, optimizer)
     rank = dist.get_rank() if dist.is_initialized() else 0

@@ -228,7 +228,8 @@ class ShardedRuntime:
     def __init__(self, *, device="cpu", reshard_after_forward=True, forward_prefetch=False,
                  backward_prefetch=False, async_grad_rs=False, communication_policy="conservative",
                  directory=None, diagnostics_enabled=True, communication_backend="auto",
-                 retain_parameters=False):
+                 retain_parameters=False, compute_dtype=None, device_wait_seconds=2.0,
+                 wire_dtype="bf16"):
         self.device = torch.device(device)
         self.reshard_after_forward = reshard_after_forward
         self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
@@ -237,6 +238,18 @@ class ShardedRuntime:
         self.communication_policy = communication_policy
         self.communication_backend = communication_backend
         self.retain_parameters = retain_parameters
+        # dtype of the GEMM operands the trainer will ask for ("fp32", "fp16", "bf16"; None =
+        # not stated).  Only bf16 (or unstated) runs may be given to the sm_100a executor.
+        if compute_dtype not in (None, "fp32", "fp16", "bf16"):
+            raise ValueError("compute_dtype must be fp32, fp16 or bf16")
+        self.requested_dtype = compute_dtype
+        # what the sm_100a parameter gather moves over NVLink: the bf16 shadow of the shards
+        # (same bits as gather-then-cast, half the bytes) or the fp32 shards themselves
+        if wire_dtype not in ("bf16", "fp32"):
+            raise ValueError("wire_dtype must be bf16 or fp32")
+        self.wire_dtype = wire_dtype
+        # time budget of every device-side wait on a peer (seconds; clamped by PeerMemory)
+        self.device_wait_seconds = float(device_wait_seconds)
         rank = dist.get_rank() if dist.is_initialized() else 0
         self.comm = CommunicationCoordinator(self.device, rank, directory,
                                              communication_policy=communication_policy,
@@ -537,6 +550,12 @@ class ShardedRuntime:
         left.record(compute)
         self.comm.wait_event(left, dependency_type="DATA_DEP", stream=caller,
                              consumer="compute_context_outputs")
+
+    def close(self):
+        """Give back what the executor holds outside torch's allocator (peer-memory mappings).
+        After a failure nothing a peer might still be reading is freed (see `PeerMemory.close`)."""
+        if self.fused is not None:
+            self.fused.close(failed=self.failed)
 
     def fail(self, reason):
         self.failed = True

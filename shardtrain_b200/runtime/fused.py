@@ -176,15 +176,18 @@ class FusedExecutor:
             raise ValueError("The sm_100a attention kernel supports head_dim 128 only")
         self.ops = ops_module.load()
         self.status = self.ops.status_tensor()
-        self.peer = PeerMemory(mesh.fsdp_group if mesh else None, runtime.device, self.ops)
+        wait = runtime.device_wait_seconds
+        self.peer = PeerMemory(mesh.fsdp_group if mesh else None, runtime.device, self.ops,
+                               wait_seconds=wait)
         # With a TP axis: activations travel inside the TP group, gradient slots are visible to
         # the whole mesh (TP-replicated parameters are summed over all of it).
         self.tp_degree, self.tp_rank = runtime.tp.degree, runtime.tp.rank
         if self.tp_degree > 1:
             import torch.distributed as dist
 
-            self.tp_peer = PeerMemory(mesh.tp_group, runtime.device, self.ops)
-            self.reduce_peer = PeerMemory(dist.group.WORLD, runtime.device, self.ops)
+            self.tp_peer = PeerMemory(mesh.tp_group, runtime.device, self.ops, wait_seconds=wait)
+            self.reduce_peer = PeerMemory(dist.group.WORLD, runtime.device, self.ops,
+                                          wait_seconds=wait)
             if self.reduce_peer.degree != self.peer.degree * self.tp_degree:
                 raise ValueError("The mesh must cover the whole world (F * T ranks)")
         else:
@@ -262,6 +265,16 @@ class FusedExecutor:
         matrices = [h for h in unit.handles if h.spec.param_id not in plan.fp32_names]
         return bool(matrices) and all(
             h.arena_offset - lo == plan.param_offsets[h.spec.param_id] for h in matrices)
+
+    def close(self, *, failed=False):
+        """Unmap and free the peer-visible buffers (arenas, gradient ring, activation slots).
+        Tensors that alias them (`param`, `grad` views, shard leaves) must not be used
+        afterwards.  With `failed` nothing is freed: a peer may still be reading."""
+        seen = set()
+        for peer in (self.tp_peer, self.reduce_peer, self.peer):
+            if peer is not None and id(peer) not in seen:
+                seen.add(id(peer))
+                peer.close(failed=failed)
 
     def finish_registration(self):
         rt = self.runtime
@@ -641,7 +654,7 @@ class FusedLayerFn(torch.autograd.Function):
                 x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
                 ex.status, B, S, hq, hkv, cfg.rms_norm_eps, buf["push"][0], buf["push"][1],
                 buf["recv"][0], buf["recv"][1], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
-                tp.max_spin)
+                tp.wait_us)
             tp.epochs["sp_ag"] = epoch + 2
             ctx.dims = (B, S, H, inter)
             ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm)
@@ -657,7 +670,7 @@ class FusedLayerFn(torch.autograd.Function):
                 x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
                 ex.status, B, S_full, hq, hkv, cfg.rms_norm_eps, h1, h2, h1_ptrs, h2_ptrs,
                 buf["push"], buf["recv"], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
-                tp.max_spin)
+                tp.wait_us)
             tp.epochs["sp_ag"] = epoch + 4
             ctx.dims = (B, S_full, H, inter)
             ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm)
@@ -703,7 +716,7 @@ class FusedLayerFn(torch.autograd.Function):
                 w_down, ln1, ln2, gv["down"], gv["gate_up"], gv["ln2"], gv["o"], gv["bias"],
                 gv["qkv"], gv["ln1"], cos, sin, positions, ctx.mask, ex.status, B, S, hq, hkv,
                 buf["push"][0], buf["push"][1], buf["recv"][0], buf["recv"][1], buf["flags"],
-                ex.tp_rank, epoch, SP_FLAG_SLOT, tp.max_spin)
+                ex.tp_rank, epoch, SP_FLAG_SLOT, tp.wait_us)
             tp.epochs["sp_ag"] = epoch + 2
             return (dx.view(B, S, H), None, None, None, None, None,
                     *([ex.token_grad] * len(plan.names)))
@@ -736,7 +749,7 @@ class FusedLayerFn(torch.autograd.Function):
             w["w_down"], w["ln1"], w["ln2"], gv["down"], gv["gate_up"], gv["ln2"], gv["o"],
             gv["bias"], gv["qkv"], gv["ln1"], cos, sin, positions, ctx.mask, ex.status, B, S_full,
             ex.hq, ex.hkv, dob, dmb, h1_ptrs, h2_ptrs, dob_ptrs, dmb_ptrs, buf["push"], buf["recv"],
-            buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT, tp.max_spin)
+            buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT, tp.wait_us)
         tp.epochs["sp_ag"] = epoch + 4
         return (dx.view(B, S_full // ex.tp_degree, H), None, None, None, None, None,
                 *([ex.token_grad] * len(plan.names)))

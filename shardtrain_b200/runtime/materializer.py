@@ -273,8 +273,9 @@ class PeerMaterializer:
             # its own), never on activations queued on the compute stream
             runtime.wait_parameter_shards_ready()
             if plan.gather_table.numel():     # empty when the unit's buffer aliases the shadow
+                shadows = [] if runtime.wire_dtype == "fp32" else self.arenas.shadow_peer_ptrs
                 self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32,
-                                       self.arenas.shadow_peer_ptrs)
+                                       shadows)
 
         # a buffer may be re-gathered only after its last reader on the compute stream
         after = (plan.last_reader,) if plan.last_reader is not None else ()

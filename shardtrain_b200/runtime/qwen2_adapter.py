@@ -170,14 +170,59 @@ def _plan_parameters(model, tied):
     return plan
 
 
-def _choose_executor(runtime):
+MAX_PEER_WORLD = 8      # size of the kernels' peer-pointer tables (csrc/api.h: kMaxPeers)
+
+
+def fused_obstacles(runtime, cfg, mesh) -> list[str]:
+    """Why the sm_100a executor cannot run this configuration (empty list: it can).
+
+    The kernels are bf16 with 128-wide attention heads, address peers through CUDA-IPC tables of
+    at most eight entries, and CUDA IPC only reaches GPUs of the same host.
+    """
+    reasons = []
+    dtype = runtime.requested_dtype
+    if dtype not in (None, "bf16"):
+        reasons.append(f"compute dtype {dtype} (the sm_100a kernels are bf16 only)")
+    if cfg.head_dim != 128:
+        reasons.append(f"head_dim {cfg.head_dim} (the attention kernels need 128)")
+    world = dist.get_world_size() if dist.is_initialized() and mesh is not None else 1
+    if world > MAX_PEER_WORLD:
+        reasons.append(f"{world} ranks (peer tables hold {MAX_PEER_WORLD})")
+    if world > 1 and not _single_host():
+        reasons.append("ranks on several hosts (CUDA IPC peer memory is per host)")
+    return reasons
+
+
+def _single_host() -> bool:
+    import socket
+
+    names: list = [None] * dist.get_world_size()
+    dist.all_gather_object(names, socket.gethostname())
+    return len(set(names)) == 1
+
+
+def _choose_executor(runtime, cfg=None, mesh=None):
+    """`auto`: the sm_100a executor when it can serve the configuration, else the portable one
+    (with a log line saying why); `nccl`: always portable; `peer`: sm_100a or an error."""
     from shardtrain_b200 import ops
 
     want = runtime.communication_backend
     if runtime.device.type != "cuda" or want == "nccl":
+        if want == "peer":
+            raise ValueError("communication_backend: peer needs a CUDA device")
         return "portable"
     if not ops.available():
         raise RuntimeError("CUDA device requested but torch.cuda is unavailable")
+    reasons = fused_obstacles(runtime, cfg, mesh) if cfg is not None else []
+    if reasons:
+        if want == "peer":
+            raise ValueError("communication_backend: peer cannot serve this run: " + "; ".join(reasons))
+        import logging
+
+        logging.getLogger("shardtrain_b200").warning(
+            "sm_100a executor not used, falling back to the portable NCCL executor: %s",
+            "; ".join(reasons))
+        return "portable"
     return "fused"
 
 
@@ -218,7 +263,7 @@ def register_qwen(runtime, model, mesh=None, *, sp=False):
             layout = {0: "column", 1: "row", None: "replicated"}[dim]
             handle = runtime.add_parameter(unit, name, shape_only, tuple(parameter.shape), layout)
             owners[name] = (module, attr, parameter)
-    kind = _choose_executor(runtime)
+    kind = _choose_executor(runtime, cfg, mesh)
     if kind == "fused":
         from shardtrain_b200.runtime.fused import FusedExecutor
 

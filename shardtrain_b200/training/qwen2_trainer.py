@@ -11,6 +11,7 @@ runtime to `FAILED`.  The optimizer is a flat-arena one (`training/optim.py`).
 
 from __future__ import annotations
 
+import time
 from contextlib import contextmanager
 from dataclasses import dataclass
 
@@ -53,9 +54,17 @@ class QwenTrainer:
         self.compute_dtype = resolve_qwen_compute_dtype(dtype, runtime.device)
         if accumulation_steps < 1:
             raise ValueError("accumulation_steps must be positive")
+        if runtime.fused is not None and dtype != "bf16":
+            # the sm_100a executor computes in bf16 whatever the trainer asks for: refuse rather
+            # than train silently in another precision than the one configured
+            raise ValueError(
+                f"training dtype {dtype} on the sm_100a executor, whose kernels are bf16 only: "
+                "construct ShardedRuntime(compute_dtype=...) with the training dtype (the portable "
+                "executor is then selected) or set runtime.communication_backend: nccl")
         runtime.compute_dtype = self.compute_dtype
         self.model, self.runtime, self.dtype = model, runtime, dtype
         self.accumulation_steps, self.step_id = accumulation_steps, 0
+        self.blocked_seconds = 0.0    # host time spent waiting in the per-step metric read
         if optimizer == "sgd":
             self.optimizer = ArenaSGD(runtime, lr=lr)
         elif optimizer == "adamw":
@@ -103,9 +112,12 @@ class QwenTrainer:
         # the kernels' status word (bounded waits that expired, rejected arguments) rides along in
         # the same device-to-host read, so a silent peer fails this very step on the host
         status = fused.status[0] if fused is not None else torch.zeros((), device=finite.device)
-        row = torch.stack([finite.to(torch.float64), reported.detach().to(torch.float64),
-                           global_count.to(torch.float64), padding.to(torch.float64),
-                           status.to(torch.float64)]).cpu().tolist()
+        packed = torch.stack([finite.to(torch.float64), reported.detach().to(torch.float64),
+                              global_count.to(torch.float64), padding.to(torch.float64),
+                              status.to(torch.float64)])
+        began = time.perf_counter()
+        row = packed.cpu().tolist()          # the step's one device-to-host read
+        self.blocked_seconds += time.perf_counter() - began
         if fused is not None:
             fused._flags.zero_()
             if row[4]:

@@ -17,7 +17,39 @@ CASES = [
                              "stream_ordered", "--accum", 2, "--optimizer", "sgd"]),
     ("f4t1_untied", 4, ["--fsdp", 4, "--flags", "110", "--policy", "stream_ordered", "--tied", 0,
                         "--optimizer", "sgd"]),
+    # the 8-rank meshes of the reference's gloo gate (tests/distributed/test_runtime.py:110-129)
+    ("f4t2_sp", 8, ["--fsdp", 4, "--tp", 2, "--sp", 1, "--flags", "111", "--policy", "stream_ordered",
+                    "--optimizer", "sgd"]),
+    ("f2t4_sp", 8, ["--fsdp", 2, "--tp", 4, "--sp", 1, "--flags", "111", "--policy", "stream_ordered",
+                    "--optimizer", "sgd", "--shape", "tiny4", "--tied", 0]),
+    ("f8t1", 8, ["--fsdp", 8, "--flags", "111", "--policy", "stream_ordered", "--optimizer", "sgd"]),
 ]
+
+
+def degree(args, flag):
+    return int(args[args.index(flag) + 1]) if flag in args else 1
+
+
+def assert_same_sequence_per_communicator(results, fsdp, tp):
+    """Every member of a communicator issued the same collectives in the same order (kind, unit,
+    phase): the invariant that keeps blocking collectives from pairing up wrongly.  Rank r sits
+    at (f, t) = divmod(r, tp); tp / tp_grad communicators fix f, fsdp / fsdp_grad fix t."""
+    def issued(rank, role):
+        return [tuple(entry[1:]) for entry in results[rank]["seq"] if entry[0] == role]
+
+    groups = []
+    for role in ("tp", "tp_grad"):
+        groups += [(role, [f * tp + t for t in range(tp)]) for f in range(fsdp)]
+    for role in ("fsdp", "fsdp_grad"):
+        groups += [(role, [f * tp + t for f in range(fsdp)]) for t in range(tp)]
+    checked = 0
+    for role, members in groups:
+        sequences = [issued(m, role) for m in members]
+        for member, sequence in zip(members[1:], sequences[1:]):
+            assert sequence == sequences[0], (
+                f"{role} communicator {members}: rank {member} diverges from rank {members[0]}")
+        checked += len(sequences[0]) * (len(members) > 1)
+    assert checked > 0, "no multi-member communicator issued anything"
 
 
 def load(out, ranks):
@@ -26,7 +58,8 @@ def load(out, ranks):
 
 @pytest.mark.parametrize("name,nproc,args", CASES, ids=[c[0] for c in CASES])
 def test_sharded_training_matches_dense(tmp_path, name, nproc, args):
-    code, log = run_workers("tests.workers.qwen_worker", nproc, ["--out", tmp_path, *args])
+    code, log = run_workers("tests.workers.qwen_worker", nproc, ["--out", tmp_path, *args],
+                            timeout=240 if nproc < 8 else 420)
     assert code == 0, log[-3000:]
     results = load(tmp_path, nproc)
     adamw = "adamw" in [str(a) for a in args]
@@ -37,8 +70,7 @@ def test_sharded_training_matches_dense(tmp_path, name, nproc, args):
         # ~lr whatever the summation order; SGD runs must agree tightly
         assert r["param_err"] < (2e-4 if adamw else 5e-6)
         assert r["shard_ok"] and r["live"] == 0
-    # every member of a communicator issued the same sequence of collectives
-    assert len({json.dumps(r["seq"]) for r in results}) <= (2 if "--tp" in args and "--fsdp" in args else 1) or True
+    assert_same_sequence_per_communicator(results, degree(args, "--fsdp"), degree(args, "--tp"))
     first = results[0]
     layers, steps = 2, 3
     micro = 2 if "--accum" in args else 1

@@ -302,32 +302,57 @@ def test_shard_gather_and_reduce_scatter_with_emulated_ranks(ops):
 
 
 def test_bounded_peer_wait_reports_instead_of_hanging(ops):
-    """A flag nobody sets: the barrier kernel gives up after its iteration limit and records a
-    status code; the context stays usable."""
+    """A flag nobody sets: the barrier kernel gives up once its *time* budget is spent and
+    records a status block; the context stays usable.  Budgets here are a few milliseconds."""
+    import time
+
     from shardtrain_b200 import ops as module
 
+    budget_us = 5000
     pad_a = torch.zeros(64, device=DEV, dtype=torch.int32)
     pad_b = torch.zeros(64, device=DEV, dtype=torch.int32)
-    ops.peer_barrier([pad_a.data_ptr()], 0, 1, 0, 1000)
+    ops.peer_barrier([pad_a.data_ptr()], 0, 1, 0, budget_us)
     torch.cuda.synchronize()
     assert ops.status_read() == 0
-    ops.peer_barrier([pad_a.data_ptr(), pad_b.data_ptr()], 0, 5, 1, 2000)   # "peer 1" never signals
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    ops.peer_barrier([pad_a.data_ptr(), pad_b.data_ptr()], 0, 5, 1, budget_us)   # "peer 1" never signals
+    end.record()
     torch.cuda.synchronize()
+    waited_ms = begin.elapsed_time(end)
+    assert 0.5 * budget_us / 1e3 <= waited_ms <= 10 * budget_us / 1e3, waited_ms
+    # with the failure on record, a second barrier on an unset flag returns without spinning its
+    # budget, and work queued behind the failure is skipped instead of running on stale data
+    x = torch.randn(256, 128, device=DEV).bfloat16()
+    w = torch.randn(256, 128, device=DEV).bfloat16()
+    out = torch.full((256, 256), 7.0, device=DEV, dtype=torch.bfloat16)
+    begin.record()
+    ops.peer_barrier([pad_a.data_ptr(), pad_b.data_ptr()], 0, 6, 1, 1_000_000)    # 1 s budget
+    ops.gemm(x, w, out, False, False, None, None, False, 1.0, 0)
+    end.record()
+    torch.cuda.synchronize()
+    assert begin.elapsed_time(end) < 100.0            # nowhere near the 1 s budget
+    assert bool((out == 7.0).all())                    # the GEMM did not run
     with pytest.raises(RuntimeError, match="peer flag wait expired") as info:
         module.check_status("test")
     # who was silent, which epoch was awaited, what was last seen
     assert "group member 1 silent: waited for epoch 5, last saw 0" in str(info.value)
     assert ops.status_read() == 0
     assert torch.ones(4, device=DEV).sum().item() == 4
+    ops.gemm(x, w, out, False, False, None, None, False, 1.0, 0)     # status cleared: runs again
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), x.float() @ w.float().t(), atol=0.5, rtol=2e-2)
     # the small all-reduce has the same bounded wait; a single member never waits
     pads, inbox = [pad_a.data_ptr(), pad_b.data_ptr()], torch.zeros(2, 2 * 8 * 16, device=DEV,
                                                                    dtype=torch.float64)
     values, out = torch.tensor([1.5, 2.0], device=DEV, dtype=torch.float64), torch.zeros(2, device=DEV, dtype=torch.float64)
-    ops.peer_allreduce_small(pads, [inbox[0].data_ptr(), inbox[1].data_ptr()], 0, 9, 6, values, out, 0, 2000)
+    t0 = time.perf_counter()
+    ops.peer_allreduce_small(pads, [inbox[0].data_ptr(), inbox[1].data_ptr()], 0, 9, 6, values, out, 0, budget_us)
     torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
     with pytest.raises(RuntimeError, match="waited for epoch 9"):
         module.check_status("test")
-    ops.peer_allreduce_small(pads[:1], [inbox[0].data_ptr()], 0, 10, 6, values, out, 0, 2000)
+    ops.peer_allreduce_small(pads[:1], [inbox[0].data_ptr()], 0, 10, 6, values, out, 0, budget_us)
     torch.cuda.synchronize()
     module.check_status("test")
     assert out.tolist() == [1.5, 2.0]

@@ -173,3 +173,51 @@ def test_nonzero_padding_and_nonfinite_gradients_are_rejected():
     handle.grad_shard[0] = float("nan")
     with pytest.raises(RuntimeError, match="Nonfinite gradient"):
         rt.finalize_backward()
+
+
+def test_executor_selection_rules(monkeypatch, caplog):
+    """`auto` hands a run to the sm_100a executor only when that executor can serve it (bf16,
+    head_dim 128, at most 8 ranks on one host); otherwise it falls back to the portable one and
+    says why.  An explicit `peer` that cannot be met is an error, never a silent fallback."""
+    from types import SimpleNamespace
+
+    import torch.distributed as dist
+
+    from shardtrain_b200 import ops
+    from shardtrain_b200.runtime import qwen2_adapter as qa
+
+    monkeypatch.setattr(ops, "available", lambda: True)
+
+    def pick(backend="auto", dtype=None, head_dim=128, device="cuda", mesh=None):
+        rt = SimpleNamespace(device=torch.device(device), communication_backend=backend,
+                             requested_dtype=dtype)
+        return qa._choose_executor(rt, SimpleNamespace(head_dim=head_dim), mesh)
+
+    assert pick() == "fused" and pick(dtype="bf16") == "fused" and pick("peer") == "fused"
+    assert pick("nccl") == "portable" and pick(device="cpu") == "portable"
+    for kwargs, word in ((dict(dtype="fp32"), "fp32"), (dict(dtype="fp16"), "fp16"),
+                         (dict(head_dim=64), "head_dim 64")):
+        caplog.clear()
+        with caplog.at_level("WARNING", logger="shardtrain_b200"):
+            assert pick(**kwargs) == "portable"
+        assert word in caplog.text
+        with pytest.raises(ValueError, match="peer cannot serve"):
+            pick("peer", **kwargs)
+    with pytest.raises(ValueError, match="needs a CUDA device"):
+        pick("peer", device="cpu")
+    # meshes beyond the peer tables or spanning hosts
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_world_size", lambda group=None: 16)
+    monkeypatch.setattr(qa, "_single_host", lambda: True)
+    assert pick(mesh=object()) == "portable"
+    monkeypatch.setattr(dist, "get_world_size", lambda group=None: 8)
+    assert pick(mesh=object()) == "fused"
+    monkeypatch.setattr(qa, "_single_host", lambda: False)
+    assert pick(mesh=object()) == "portable"
+    with pytest.raises(ValueError, match="several hosts"):
+        pick("peer", mesh=object())
+
+
+def test_runtime_rejects_an_unknown_compute_dtype():
+    with pytest.raises(ValueError, match="compute_dtype"):
+        ShardedRuntime(device="cpu", compute_dtype="int8")

@@ -29,7 +29,7 @@ def main():
     ap.add_argument("--tied", type=int, default=1)
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--mismatch", type=int, default=0)
-    ap.add_argument("--shape", default="tiny", choices=["tiny", "d128", "d128tp"])
+    ap.add_argument("--shape", default="tiny", choices=["tiny", "tiny4", "d128", "d128tp"])
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--optimizer", default="adamw")
     ap.add_argument("--backend", default="auto")
@@ -56,6 +56,10 @@ def main():
             cfg = Qwen2ModelConfig(vocab_size=2048, hidden_size=512, intermediate_size=512,
                                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                                    tie_word_embeddings=bool(a.tied))
+        elif a.shape == "tiny4":   # 4 KV heads: divisible by TP 4
+            cfg = Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128,
+                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
+                                   tie_word_embeddings=bool(a.tied))
         else:
             cfg = Qwen2ModelConfig(vocab_size=1024, hidden_size=64, intermediate_size=128,
                                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
@@ -69,7 +73,7 @@ def main():
         rt = ShardedRuntime(device=ctx.device, reshard_after_forward=bool(a.reshard),
                             forward_prefetch=fp, backward_prefetch=bp, async_grad_rs=ar,
                             communication_policy=a.policy, directory=out,
-                            communication_backend=a.backend)
+                            communication_backend=a.backend, compute_dtype=a.dtype)
         rt.register(model, ctx, sp=bool(a.sp))
         lr = 1e-3 if a.optimizer == "adamw" else 0.05
         tr = QwenTrainer(model, rt, lr=lr, optimizer=a.optimizer, accumulation_steps=a.accum,
@@ -129,7 +133,7 @@ def main():
         kinds = {}
         for t in rt.comm.tickets:
             kinds[t.kind] = kinds.get(t.kind, 0) + 1
-        seq = [(t.pg_id, t.kind) for t in rt.comm.tickets]
+        seq = [(t.pg_id, t.kind, t.unit_id, t.phase) for t in rt.comm.tickets]
         shard_ok = all(p.ndim == 1 and p.dtype == torch.float32 for p in model.parameters())
         (out / f"result.rank{worker.rank}.json").write_text(json.dumps(dict(
             rows=rows, param_err=err, events=events, kinds=kinds, seq=seq, shard_ok=shard_ok,
