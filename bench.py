@@ -41,10 +41,17 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--strategy", default="", help="F{dp}T{tp}[/SP]; default F{gpus}T1")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (not reportable)")
+    ap.add_argument("--global-batch", type=int, default=16,
+                    help="debug only: another global batch, e.g. 4 on 2 GPUs gives every rank the "
+                         "per-rank shapes of the 8-GPU run (not reportable)")
     ap.add_argument("--retain", type=int, default=0, help="runtime.retain_parameters")
     ap.add_argument("--backend", default="auto", choices=["auto", "peer", "nccl"])
     ap.add_argument("--fp32-wire", action="store_true",
                     help="gather parameters from the fp32 shards instead of their bf16 shadow")
+    ap.add_argument("--fused-allgather", default="auto", choices=["auto", "on", "off"],
+                    help="pull q|k|v and gate|up inside the forward GEMMs (FSDP degree > 1)")
+    ap.add_argument("--no-seq-pull", action="store_true",
+                    help="sequence parallel: gather kernel + GEMM instead of the pulling GEMM")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the second (hybrid TP/SP) strategy that follows the F{N}T1 pass")
     return ap.parse_args()
@@ -107,9 +114,13 @@ def qwen15b_dict(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
         "runtime": dict(param_grouping="block", reshard_after_forward=True, forward_prefetch=True,
                         backward_prefetch=True, async_grad_rs=True,
                         communication_policy="stream_ordered",
-                        communication_backend=args.backend, retain_parameters=bool(args.retain)),
+                        communication_backend=args.backend, retain_parameters=bool(args.retain),
+                        fused_allgather=args.fused_allgather,
+                        wire_dtype="fp32" if args.fp32_wire else "bf16",
+                        fused_seq_gather=not args.no_seq_pull),
         "training": dict(dtype="bf16", optimizer="adamw", lr=1e-5, steps=args.steps,
-                         local_batch_size=16 // fsdp // 2, accumulation_steps=2, seed=1234),
+                         local_batch_size=args.global_batch // fsdp // 2, accumulation_steps=2,
+                         seed=1234),
         "debug": dict(output_dir=f"/tmp/shardtrain_b200_bench_{os.getpid()}",
                       distributed_timeout_seconds=300),
     })
@@ -161,7 +172,8 @@ def measure_ours(args, fsdp, tp, sp):
             directory=None, diagnostics_enabled=False,
             communication_backend=rc.communication_backend, retain_parameters=rc.retain_parameters,
             compute_dtype="bf16", device_wait_seconds=config.debug.distributed_timeout_seconds,
-            wire_dtype="fp32" if args.fp32_wire else "bf16",
+            wire_dtype=rc.wire_dtype, fused_allgather=rc.fused_allgather,
+            fused_seq_gather=rc.fused_seq_gather,
         ).register(model, mesh if session.worker.launched else None, sp=sp)
         trainer = QwenTrainer(model, runtime, config.training.lr, dtype="bf16", optimizer="adamw",
                               accumulation_steps=config.training.accumulation_steps)
@@ -257,8 +269,9 @@ def run_ours(args):
         "vs_baseline": value / published if published else None,
         "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else ""),
-                   "global_batch": 16, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
+        "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else "")
+                            + (" (debug batch: labels/s not comparable)" if args.global_batch != 16 else ""),
+                   "global_batch": args.global_batch, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
                    "parallelism": m["strategy"], "valid_labels_per_step": VALID_LABELS_PER_STEP,
                    "precision": "bf16 GEMM operands, fp32 accumulation; fp32 master shards, "
                                 "gradients and AdamW state; on the wire: " + wire +
@@ -266,7 +279,8 @@ def run_ours(args):
                                 "partial sums",
                    "inputs": "token ids + all-ones attention_mask + position_ids, as the "
                              "reference benchmark passes them",
-                   "runtime": {**m["switches"], "executor": m["executor"]},
+                   "runtime": {**m["switches"], "executor": m["executor"],
+                               "fused_allgather": args.fused_allgather},
                    "l2": "no explicit flush: each step streams >6 GB of parameters, "
                          "gradients and optimizer state per GPU group, far above the 126 MB L2"},
         "clocks": m["clocks"],

@@ -2,10 +2,14 @@
 
 The schema (section names, field names, defaults, override syntax `--section.field value`) is the
 one of the reference's `src/sharded_runtime/config.py:17-268`, so its YAML presets load unchanged.
-The validation rules are stated as a table of checks instead of a chain of `if`s.  Two optional
+The validation rules are stated as a table of checks instead of a chain of `if`s.  Five optional
 runtime fields are new and default to the reference behaviour: `communication_backend`
-("auto" | "peer" | "nccl") selects the NVLink peer-memory kernels or the NCCL baseline path, and
-`retain_parameters` keeps the gathered compute-dtype parameters for the whole optimizer step.
+("auto" | "peer" | "nccl") selects the NVLink peer-memory kernels or the NCCL baseline path,
+`retain_parameters` keeps the gathered compute-dtype parameters for the whole optimizer step,
+`fused_allgather` ("auto" | "on" | "off") lets a decoder layer's forward GEMMs pull q|k|v and
+gate|up from the owning ranks' shards instead of gathering them first, `wire_dtype`
+("bf16" | "fp32") picks what the parameter gather moves over NVLink, and `fused_seq_gather`
+lets the GEMM that consumes a sequence all-gather pull the peers' slices itself.
 
 This module never imports torch.
 """
@@ -72,6 +76,9 @@ class RuntimeConfig:
     communication_policy: str = "conservative"
     communication_backend: str = "auto"
     retain_parameters: bool = False
+    fused_allgather: str = "auto"
+    wire_dtype: str = "bf16"
+    fused_seq_gather: bool = True
 
 
 @dataclass(frozen=True)
@@ -262,6 +269,14 @@ class Config:
             (
                 lambda: r.communication_backend != "peer" or p.device == "cuda",
                 "communication_backend=peer needs CUDA peer memory",
+            ),
+            (
+                lambda: r.fused_allgather in {"auto", "on", "off"},
+                "runtime.fused_allgather must be auto, on or off",
+            ),
+            (
+                lambda: r.wire_dtype in {"bf16", "fp32"},
+                "runtime.wire_dtype must be bf16 or fp32",
             ),
         ]
 

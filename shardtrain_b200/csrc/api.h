@@ -39,6 +39,17 @@ struct GemmCall {
   int scatter_seq;
   int scatter_seq_local;
   int scatter_broadcast;  // 1: store every row into all scatter_out buffers (all-reduce push)
+  // Optional sequence all-gather of the A operand inside the GEMM (pull_degree > 1, a K-major):
+  // `a` is then the local [M, lda] buffer the kernel *fills* -- row b * (degree * seq_local) +
+  // r * seq_local + s comes from row b * seq_local + s of pull_peers[r] (row pitch pull_src_ld
+  // elements; peer pointers allowed, read with plain loads) -- and consumes tile by tile as the
+  // rows land.  M must equal pull_batch * pull_degree * pull_seq_local.  The gathered rows stay
+  // in `a` for later GEMMs.  One such GEMM at a time per device.
+  const void* pull_peers[8];
+  int pull_degree;
+  int pull_batch;
+  int pull_seq_local;
+  int64_t pull_src_ld;
 };
 cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream);
 

@@ -86,6 +86,47 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, bool a_mn, bool b_mn,
   check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm");
 }
 
+// out = A @ B^T (or A @ B with b_mn) where A is gathered along the sequence inside the GEMM:
+// `a_dst` is the local [batch * T * seq_local, K] buffer the kernel fills from the T peers'
+// [batch * seq_local, K] slices (`peer_ptrs`, contiguous rows) and then reads tile by tile.
+void gemm_seq_pull(Tensor a_dst, const Tensor& b, Tensor out, bool b_mn,
+                   const c10::optional<Tensor>& bias, c10::ArrayRef<int64_t> peer_ptrs,
+                   int64_t batch, int64_t seq_local, int64_t force_bn) {
+  need(a_dst, at::kBFloat16, "a_dst");
+  need(b, at::kBFloat16, "b");
+  TORCH_CHECK(a_dst.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a_dst.stride(1) == 1 &&
+                  b.stride(1) == 1 && out.stride(1) == 1, "gemm_seq_pull: 2-D operands expected");
+  TORCH_CHECK(peer_ptrs.size() >= 2 && peer_ptrs.size() <= 8, "2..8 sequence owners expected");
+  const c10::cuda::CUDAGuard guard(a_dst.device());
+  stb::GemmCall c{};
+  c.M = static_cast<int>(a_dst.size(0));
+  c.K = static_cast<int>(a_dst.size(1));
+  c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == c.K, "gemm reduction sizes differ");
+  TORCH_CHECK(out.size(0) == c.M && out.size(1) == c.N, "gemm output shape mismatch");
+  c.a = a_dst.data_ptr();
+  c.b = b.data_ptr();
+  c.out = out.data_ptr();
+  c.lda = a_dst.stride(0);
+  c.ldb = b.stride(0);
+  c.ldo = out.stride(0);
+  c.b_mn = b_mn;
+  c.out_fp32 = out.scalar_type() == at::kFloat;
+  c.alpha = 1.f;
+  c.force_bn = static_cast<int>(force_bn);
+  if (bias.has_value()) {
+    need(*bias, at::kFloat, "bias");
+    c.bias = bias->data_ptr<float>();
+  }
+  c.pull_degree = static_cast<int>(peer_ptrs.size());
+  c.pull_batch = static_cast<int>(batch);
+  c.pull_seq_local = static_cast<int>(seq_local);
+  c.pull_src_ld = c.K;
+  for (size_t i = 0; i < peer_ptrs.size(); ++i)
+    c.pull_peers[i] = reinterpret_cast<const void*>(peer_ptrs[i]);
+  check(stb::launch_gemm_bf16(c, status_ptr(), cur_stream()), "gemm_seq_pull");
+}
+
 void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor inv, double eps) {
   need(x, at::kFloat, "x");
   need(w, at::kFloat, "w");
@@ -665,6 +706,16 @@ int64_t peer_alloc(int64_t nbytes) {
 }
 void peer_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
 void device_synchronize() { check(cudaDeviceSynchronize(), "device_synchronize"); }
+// Let kernels on the current device dereference pointers into `peer_device`'s memory (one
+// process driving two GPUs; across processes the CUDA-IPC mappings above do the same).
+void enable_peer_access(int64_t peer_device) {
+  const cudaError_t e = cudaDeviceEnablePeerAccess(static_cast<int>(peer_device), 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();   // clear the sticky-free error state
+    return;
+  }
+  check(e, "enable_peer_access");
+}
 Tensor ipc_handle(int64_t ptr) {
   cudaIpcMemHandle_t h;
   check(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr)), "ipc_handle");
@@ -747,6 +798,7 @@ TORCH_LIBRARY(stb, m) {
         "bool accumulate, float alpha, int force_bn, int split_k=0) -> ()",
         &gemm);
   m.def("gemm_scatter", &gemm_scatter);
+  m.def("gemm_seq_pull", &gemm_seq_pull);
   m.def("gemm_swiglu", &gemm_swiglu);
   m.def("gemm_broadcast", &gemm_broadcast);
   m.def("slot_sum_rmsnorm", &slot_sum_rmsnorm);
@@ -788,6 +840,7 @@ TORCH_LIBRARY(stb, m) {
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);
   m.def("device_synchronize", &device_synchronize);
+  m.def("enable_peer_access", &enable_peer_access);
   m.def("ipc_handle", &ipc_handle);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);

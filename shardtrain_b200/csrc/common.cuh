@@ -23,6 +23,7 @@ enum : int {
   kErrPeerFlagWait = 5,
   kErrAttnWait = 6,
   kErrBadArgument = 7,
+  kErrPullWait = 8,
 };
 
 // Waits are bounded in *time*: after a short burst of polls that never reads a clock, a waiter
@@ -42,6 +43,28 @@ __device__ __forceinline__ uint64_t global_ns() {
 // silent peer never delivered.  Call from one thread and broadcast (see kernel_should_skip).
 __device__ __forceinline__ bool status_failed(const int* status) {
   return status != nullptr && *reinterpret_cast<const volatile int*>(status) != kOk;
+}
+
+// Bounded wait for a 32-bit flag in this GPU's memory to become `value` (written with
+// st.release.gpu by another CTA of the same grid).  False when the time budget is spent or a
+// failure is already on record.
+__device__ __forceinline__ bool wait_flag_equal(const uint32_t* flag, uint32_t value,
+                                                const int* status) {
+  uint32_t v;
+  for (uint32_t i = 0; i < kFastPolls; ++i) {
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v == value) return true;
+  }
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (uint32_t i = 0; i < 64; ++i) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v == value) return true;
+      __nanosleep(32);
+    }
+    if (status_failed(status)) return false;
+    if (global_ns() - t0 > kWaitBudgetNs) return false;
+  }
 }
 
 // CTA-uniform entry check: every thread returns the same answer, so a kernel may `return` on it

@@ -40,14 +40,14 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kThreads = 192;
 constexpr int kProducers = 128;
-constexpr int kAStages = 4;
+constexpr int kAStages = 8;          // two k-blocks of four row tiles: hides the L2 latency of A
 constexpr int kLag = 3;              // weight stages a producer keeps in flight before it waits
 constexpr int kATile = kBM * kBK * 2;
 
 template <int BN>
 struct AgSmem {
   static constexpr int kBTile = BN * kBK * 2;
-  static constexpr int kBStages = BN == 128 ? 6 : 8;
+  static constexpr int kBStages = BN == 128 ? 5 : 8;
   static constexpr int kBarrierBytes = 512;
   static constexpr int kTotal = kBStages * kBTile + kAStages * kATile + 1024 + kBarrierBytes;
 };
@@ -90,7 +90,7 @@ struct SegShared {
 // Where one row of a weight tile comes from: parameter `seg`, flat element index of (row, k = 0)
 // inside that parameter; seg < 0 marks a row beyond the weight (zero filled).
 struct RowSource {
-  int64_t flat0;
+  uint32_t flat0;     // < 2^31: the host rejects larger parameters
   int seg;
 };
 
@@ -100,13 +100,19 @@ __device__ __forceinline__ RowSource locate_row(const SegShared* segs, int n_seg
   if (fused_row < 0 || fused_row >= n_rows) return r;
   for (int j = 0; j < n_segs; ++j) {
     if (fused_row < segs[j].first_row + segs[j].rows) {
-      r.flat0 = static_cast<int64_t>(fused_row - segs[j].first_row) * K;
+      r.flat0 = static_cast<uint32_t>(fused_row - segs[j].first_row) * static_cast<uint32_t>(K);
       r.seg = j;
       return r;
     }
   }
   return r;
 }
+
+// Every CTA reads the whole of A, one k-block after the other.  If all CTAs walked K in the same
+// order they would ask the L2 for the same few lines at the same moment; each tile therefore
+// starts at its own k-block and wraps around (the sum over K does not depend on the order up to
+// fp32 rounding).
+__device__ __forceinline__ int k_rotation(int tile, int num_kb) { return (tile * 7) % num_kb; }
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -184,10 +190,12 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int rot = k_rotation(tile, num_kb);
         for (int pass = 0; pass < passes && ok; ++pass) {
           const int m_first = pass * p.mt;
           const int m_count = min(p.mt, m_tiles - m_first);
-          for (int kb = 0; kb < num_kb && ok; ++kb) {
+          for (int step = 0; step < num_kb && ok; ++step) {
+            const int kb = (step + rot) % num_kb;
             for (int m = 0; m < m_count; ++m, ++it) {
               const int s = it % kAStages;
               if (!mbar_wait(&a_empty[s], ((it / kAStages) & 1) ^ 1, p.status,
@@ -243,7 +251,7 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
               for (int k = 0; k < kBK / 16; ++k) {
                 const uint64_t da = make_smem_desc_sw128(a_base + k * 32, 16, 1024);
                 const uint64_t db = make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-                tc_mma_f16(tmem_base + m * BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                tc_mma_f16(tmem_base + m * BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);   // kb: step
               }
               tc_commit(&a_empty[sa]);
             }
@@ -264,6 +272,7 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       const int n0 = tile * tile_cols;
+      const int rot = k_rotation(tile, num_kb);
       RowSource src[ROWS_PER_THREAD];
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) {
@@ -308,7 +317,8 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
         };
         // ---- produce the weight stages of this pass
         int waiting = 0;                      // stages issued whose copies were not yet awaited
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++itb) {
+        for (int step = 0; step < num_kb && ok; ++step, ++itb) {
+          const int kb = (step + rot) % num_kb;
           const int sb = itb % NB;
           if (!mbar_wait(&b_empty[sb], ((itb / NB) & 1) ^ 1, p.status, kErrProducerEmptyWait)) {
             *abort_flag = 1;
@@ -326,7 +336,8 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
               continue;
             }
             const SegShared& sg = segs[src[i].seg];
-            const int64_t flat = src[i].flat0 + k0;
+            const uint32_t flat = src[i].flat0 + static_cast<uint32_t>(k0);
+            const uint32_t q32 = static_cast<uint32_t>(sg.q);
             const bool whole = sg.vec && k0 + 8 <= p.K;     // one aligned 16-byte piece
             if (!from_peers) {
               // later passes: the first pass left the rows in the local full buffer
@@ -342,16 +353,16 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
               continue;
             }
             if (whole && p.w.shadow[0] != nullptr) {
-              const int owner = static_cast<int>(flat / sg.q);
-              cp_async_16(smem_u32(dst), p.w.shadow[owner] + sg.shard_off + (flat - owner * sg.q));
+              const uint32_t owner = flat / q32;
+              cp_async_16(smem_u32(dst), p.w.shadow[owner] + sg.shard_off + (flat - owner * q32));
               continue;
             }
             // general path: fp32 on the wire, or shard boundaries that are not 8-element aligned
             __nv_bfloat16 v[8];
             if (whole) {
-              const int owner = static_cast<int>(flat / sg.q);
+              const uint32_t owner = flat / q32;
               const float4* g = reinterpret_cast<const float4*>(p.w.shard[owner] + sg.shard_off +
-                                                                (flat - owner * sg.q));
+                                                                (flat - owner * q32));
               const float4 lo = g[0], hi = g[1];
               v[0] = __float2bfloat16(lo.x); v[1] = __float2bfloat16(lo.y);
               v[2] = __float2bfloat16(lo.z); v[3] = __float2bfloat16(lo.w);
@@ -362,9 +373,9 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
               for (int e = 0; e < 8; ++e) {
                 v[e] = __float2bfloat16(0.f);
                 if (k0 + e < p.K) {
-                  const int64_t f = flat + e;
-                  const int owner = static_cast<int>(f / sg.q);
-                  const int64_t off = sg.shard_off + (f - owner * sg.q);
+                  const uint32_t f = flat + e;
+                  const uint32_t owner = f / q32;
+                  const int64_t off = sg.shard_off + (f - owner * q32);
                   v[e] = p.w.shadow[0] != nullptr ? p.w.shadow[owner][off]
                                                   : __float2bfloat16(p.w.shard[owner][off]);
                 }
@@ -376,14 +387,15 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
           ++waiting;
           if (waiting > kLag) {
             cp_async_wait<kLag>();               // the oldest outstanding stage is complete
-            publish(itb - kLag, kb - kLag);
+            publish(itb - kLag, (step - kLag + rot) % num_kb);
             --waiting;
           }
         }
         // ---- tail: the stages still in flight
         cp_async_wait<0>();
         if (ok) {
-          for (int back = waiting; back >= 1; --back) publish(itb - back, num_kb - back);
+          for (int back = waiting; back >= 1; --back)
+            publish(itb - back, (num_kb - back + rot) % num_kb);
         }
         if (mirror && passes > 1) {
           // the next pass of this CTA reads back what these 128 threads just wrote to `full`
@@ -526,7 +538,8 @@ cudaError_t launch_gemm_allgather(const AgGemmCall& c, int* status, cudaStream_t
   for (int j = 0; j < w.n_segs; ++j) {
     const AgSegment& s = w.seg[j];
     if (s.rows <= 0 || s.q <= 0 || s.shard_off < 0 || s.full_off < 0 ||
-        s.q * w.degree < static_cast<int64_t>(s.rows) * c.K)
+        s.q * w.degree < static_cast<int64_t>(s.rows) * c.K ||
+        static_cast<int64_t>(s.rows) * c.K >= (int64_t{1} << 31))   // 32-bit flat indices
       return cudaErrorInvalidValue;
     rows += s.rows;
   }

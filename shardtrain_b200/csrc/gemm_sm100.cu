@@ -104,9 +104,19 @@ int plan_split(int tiles, int num_kb, int want, int* full, int* kb_per) {
   const int rem = tiles - *full;
   *kb_per = num_kb;
   if (rem == 0 || want == 1) return 1;
-  // parking and re-reading a partial tile costs about as much as 10 k-blocks: only splits that
-  // keep at least 32 k-blocks each pay off
-  int split = want > 1 ? want : std::min({sms / rem, 8, num_kb / 32});
+  // parking and re-reading a partial tile costs about as much as 10 k-blocks: in the tail of a
+  // multi-wave GEMM only splits that keep at least 32 k-blocks each pay off.  A GEMM of less
+  // than half a wave is different: its run time is one tile's k-loop on a few SMs while the
+  // others idle, so its tiles are cut down to 6 k-blocks each to spread the loop over the
+  // machine.
+  int split;
+  if (want > 1) {
+    split = want;
+  } else if (*full == 0 && 2 * rem <= sms) {
+    split = std::min({sms / rem, 8, num_kb / 6});
+  } else {
+    split = std::min({sms / rem, 8, num_kb / 32});
+  }
   split = std::min(split, sms / rem);
   if (split < 2) return 1;
   *kb_per = (num_kb + split - 1) / split;
@@ -144,6 +154,32 @@ cudaError_t split_buffers(cudaStream_t stream, SplitBuffers* out) {
   return cudaSuccess;
 }
 
+// Arrival flags of the PULL variant, one buffer per (device, stream), and the epoch counter that
+// makes every launch's flag value unique (flags are never cleared).
+constexpr int kPullFlagCount = 65536;       // 8-row groups: up to 524288 rows of A
+std::unordered_map<uint64_t, uint32_t*> g_pull_flags;
+uint32_t g_pull_epoch = 0;
+
+cudaError_t pull_flags(cudaStream_t stream, uint32_t** flags, uint32_t* epoch) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint64_t key = (static_cast<uint64_t>(dev) << 56) ^ reinterpret_cast<uint64_t>(stream);
+  std::lock_guard<std::mutex> lock(g_split_mutex);
+  auto it = g_pull_flags.find(key);
+  if (it == g_pull_flags.end()) {
+    uint32_t* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, kPullFlagCount * sizeof(uint32_t));
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(p, 0, kPullFlagCount * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    it = g_pull_flags.emplace(key, p).first;
+  }
+  *flags = it->second;
+  if (++g_pull_epoch == 0) ++g_pull_epoch;   // 0 is the cleared state
+  *epoch = g_pull_epoch;
+  return cudaSuccess;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
@@ -175,14 +211,7 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   ep.scatter_broadcast = c.scatter_broadcast ? 1 : 0;
   for (int i = 0; i < 8; ++i) ep.scatter_out[i] = i < ep.scatter_degree ? c.scatter_out[i] : nullptr;
 
-  auto kernel = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
   constexpr int smem = GemmSmem<BN>::kTotal;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  });
-  if (attr_err != cudaSuccess) return attr_err;
   const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
   const int n_tiles = c.gated_inter > 0 ? (c.gated_inter + BN / 2 - 1) / (BN / 2) : (c.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
@@ -201,6 +230,37 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   }
   sp.total_units = sp.full_tiles + (tiles - sp.full_tiles) * sp.split;
   const int grid = std::min(sp.total_units, sm_count());   // persistent: one CTA per SM
+  if constexpr (!A_MN) {
+    if (c.pull_degree > 1) {
+      GemmPull pull{};
+      for (int i = 0; i < c.pull_degree; ++i) pull.peers[i] = c.pull_peers[i];
+      pull.degree = c.pull_degree;
+      pull.batch = c.pull_batch;
+      pull.seq_local = c.pull_seq_local;
+      pull.src_ld = c.pull_src_ld;
+      pull.dst = const_cast<void*>(c.a);
+      pull.dst_ld = c.lda;
+      const cudaError_t e = pull_flags(stream, &pull.flags, &pull.epoch);
+      if (e != cudaSuccess) return e;
+      auto kernel = gemm_pull_bf16_tcgen05_kernel<BN, B_MN>;
+      static std::once_flag once;
+      static cudaError_t attr_err = cudaSuccess;
+      std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      });
+      if (attr_err != cudaSuccess) return attr_err;
+      kernel<<<grid, kGemmThreads + kPullThreads, smem, stream>>>(ta, tb, ep, sp, pull, c.M, c.N,
+                                                                 c.K, status);
+      return cudaGetLastError();
+    }
+  }
+  auto kernel = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
   kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, ep, sp, c.M, c.N, c.K, status);
   return cudaGetLastError();
 }
@@ -235,6 +295,16 @@ cudaError_t launch_gemm_bf16(const GemmCall& c, int* status, cudaStream_t stream
       return cudaErrorInvalidValue;
     for (int i = 0; i < c.scatter_degree; ++i)
       if (c.scatter_out[i] == nullptr || !aligned16(c.scatter_out[i])) return cudaErrorInvalidValue;
+  }
+  if (c.pull_degree > 1) {
+    // A is gathered inside the GEMM: K-major A only, whole 16-byte pieces per row, aligned peers
+    if (c.a_mn || c.pull_degree > 8 || c.pull_batch <= 0 || c.pull_seq_local <= 0 || (c.K % 8) ||
+        (c.pull_src_ld % 8) ||
+        static_cast<int64_t>(c.pull_batch) * c.pull_degree * c.pull_seq_local != c.M ||
+        (c.M + kPullRows - 1) / kPullRows > kPullFlagCount)
+      return cudaErrorInvalidValue;
+    for (int i = 0; i < c.pull_degree; ++i)
+      if (c.pull_peers[i] == nullptr || !aligned16(c.pull_peers[i])) return cudaErrorInvalidValue;
   }
   if (c.gated_inter > 0) {
     // SwiGLU epilogue: 256-wide tiles (128 gate + 128 up columns), forward operand order, bf16

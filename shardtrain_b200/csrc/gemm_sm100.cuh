@@ -60,6 +60,35 @@ struct GemmSplit {
   int* counters;      // [rem_tiles], zero between launches
 };
 
+// Sequence all-gather fused into the GEMM that consumes the gathered activation (PULL variant).
+// The A operand is the concatenation along the sequence of T ranks' [batch, seq_local, K] slices:
+// row b * (T * seq_local) + r * seq_local + s of A is row b * seq_local + s of rank r's slice.
+// Four extra warps of every CTA copy 8-row groups of A from the owners' buffers (plain 16-byte
+// peer loads, twelve in flight per thread) into the local buffer `dst` that the A tensor map
+// covers, and publish one flag per group; the TMA producer waits (bounded) for the flags of the
+// rows a tile needs before it loads them.  Tiles whose rows have landed run while later groups
+// are still crossing the link, so the transfer overlaps the MMAs tile by tile and the gathered
+// activation stays in the local buffer for the GEMMs that reuse it.
+//
+// Flags hold the `epoch` of the launch that wrote them, so they never need clearing; every
+// launch on a flag buffer must use a new epoch.  All CTAs of the grid must be able to become
+// resident (the launcher keeps the grid at one CTA per SM) and two PULL GEMMs must not run
+// concurrently on one device: a CTA waits for groups that other CTAs of its own grid pull.
+struct GemmPull {
+  const void* peers[8];   // rank r's [batch * seq_local, K] bf16 slice (row pitch `src_ld` elements)
+  int degree;
+  int batch;
+  int seq_local;
+  int64_t src_ld;         // elements
+  void* dst;              // local [M, lda] bf16 buffer = the A operand
+  int64_t dst_ld;
+  uint32_t* flags;        // one per kPullRows-row group of A
+  uint32_t epoch;
+};
+constexpr int kPullRows = 8;       // small groups: every CTA of the grid gets some to pull
+constexpr int kPullThreads = 128;
+constexpr int kPullBatch = 12;     // independent 16-byte loads per thread before the first store
+
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;
 constexpr int kGemmThreads = 192;
@@ -80,11 +109,12 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStageBytes + 1024 + kBarrierBytes + kScatterStageBytes;
 };
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
-                         const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep, GemmSplit sp,
-                         int M, int N, int K, int* __restrict__ status) {
+template <int BN, bool A_MN, bool B_MN, bool PULL>
+__device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
+                                                       const CUtensorMap& tma_b,
+                                                       const GemmEpilogue& ep, const GemmSplit& sp,
+                                                       const GemmPull& pull, int M, int N, int K,
+                                                       int* __restrict__ status) {
   // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
   // double buffered in TMEM (2 x BN columns) so the epilogue of one tile overlaps the MMAs of the
   // next; the shared-memory operand pipeline runs across tile boundaries without draining.
@@ -168,6 +198,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         int tile, kb0, kb1, part, m0, n0;
         unit_work(unit, tile, kb0, kb1, part);
         tile_origin(tile, m0, n0);
+        if constexpr (PULL) {
+          // the rows m0 .. m0 + 127 of A must have landed in the local buffer
+          const int g_first = m0 / kPullRows;
+          const int g_last = (min(M, m0 + kGemmBM) - 1) / kPullRows;
+          for (int g = g_first; g <= g_last && ok; ++g) {
+            if (!wait_flag_equal(pull.flags + g, pull.epoch, status)) {
+              if (status != nullptr) atomicCAS(status, kOk, kErrPullWait);
+              *abort_flag = 1;
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          // generic-proxy stores of the pulling warps -> visible to the TMA (async proxy) reads
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -249,6 +294,48 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         tc_commit(&acc_full[ab]);
       }
+    }
+  } else if (PULL && warp >= 6) {
+    // Pull warps: copy groups of rows of A from their owners into the local buffer, lowest groups
+    // first (the order in which the tiles of the first wave need them), then publish the flag.
+    const int t = threadIdx.x - kGemmThreads;              // 0..127
+    const int seq = pull.degree * pull.seq_local;
+    const int chunks_per_row = (K * 2) / 16;               // 16-byte pieces of a row (K % 8 == 0)
+    const int groups = (M + kPullRows - 1) / kPullRows;
+    for (int g = blockIdx.x; g < groups; g += gridDim.x) {
+      const int row0 = g * kPullRows;
+      const int rows = min(kPullRows, M - row0);
+      const int total = rows * chunks_per_row;
+      for (int i0 = t; i0 < total; i0 += kPullThreads * kPullBatch) {
+        uint4 v[kPullBatch];
+#pragma unroll
+        for (int u = 0; u < kPullBatch; ++u) {
+          const int i = i0 + u * kPullThreads;
+          if (i < total) {
+            const int r = row0 + i / chunks_per_row, c = i % chunks_per_row;
+            const int b = r / seq, pos = r - b * seq;
+            const int owner = pos / pull.seq_local;
+            const int64_t src_row = static_cast<int64_t>(b) * pull.seq_local + (pos - owner * pull.seq_local);
+            v[u] = *(reinterpret_cast<const uint4*>(
+                         reinterpret_cast<const __nv_bfloat16*>(pull.peers[owner]) +
+                         src_row * pull.src_ld) + c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kPullBatch; ++u) {
+          const int i = i0 + u * kPullThreads;
+          if (i < total) {
+            const int r = row0 + i / chunks_per_row, c = i % chunks_per_row;
+            *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(pull.dst) +
+                                       static_cast<int64_t>(r) * pull.dst_ld) + c) = v[u];
+          }
+        }
+      }
+      __threadfence();                                      // the group's rows before its flag
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (t == 0)
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(pull.flags + g), "r"(pull.epoch)
+                     : "memory");
     }
   } else {
     // Epilogue: 4 warps x 32 lanes = the 128 accumulator rows.
@@ -502,6 +589,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, S::kTmemCols);
   }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+                         const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep, GemmSplit sp,
+                         int M, int N, int K, int* __restrict__ status) {
+  gemm_bf16_tcgen05_body<BN, A_MN, B_MN, false>(tma_a, tma_b, ep, sp, GemmPull{}, M, N, K, status);
+}
+
+// The same GEMM with four more warps that pull the A operand from its owners (see GemmPull).
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads + kPullThreads, 1)
+gemm_pull_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+                              const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep,
+                              GemmSplit sp, GemmPull pull, int M, int N, int K,
+                              int* __restrict__ status) {
+  gemm_bf16_tcgen05_body<BN, false, B_MN, true>(tma_a, tma_b, ep, sp, pull, M, N, K, status);
 }
 
 }  // namespace stb

@@ -7,6 +7,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/library.h>
 
+#include <cuda_bf16.h>
+
 #include <cmath>
 #include <vector>
 
@@ -20,12 +22,96 @@ void ok(cudaError_t e, const char* what) {
   TORCH_CHECK(e == cudaSuccess, "shardtrain_b200 layer executor: ", what, ": ", cudaGetErrorString(e));
 }
 
+// Optional "pull the weights inside the GEMM" plan of a layer forward: the FSDP ranks' arenas
+// and, for q|k|v and gate|up, the rows of the unit's gather table that describe those parameters.
+// Empty `arenas`: the weights were gathered beforehand and the plain GEMMs run.
+struct AgPlan {
+  std::vector<int64_t> arenas;
+  bool wire_fp32 = false;
+  const at::Tensor* segs_qkv = nullptr;   // CPU int64 [3, 5]
+  const at::Tensor* segs_gu = nullptr;    // CPU int64 [2, 5]
+  at::Tensor full;                        // the unit's local bf16 full-parameter buffer
+  bool on() const { return !arenas.empty(); }
+};
+
+AgPlan make_ag_plan(c10::ArrayRef<int64_t> arenas, bool wire_fp32,
+                    const c10::optional<at::Tensor>& segs_qkv,
+                    const c10::optional<at::Tensor>& segs_gu,
+                    const c10::optional<at::Tensor>& full) {
+  AgPlan plan;
+  if (arenas.empty()) return plan;
+  TORCH_CHECK(segs_qkv.has_value() && segs_gu.has_value() && full.has_value(),
+              "fused all-gather: segment tables and the full buffer are required");
+  plan.arenas.assign(arenas.begin(), arenas.end());
+  plan.wire_fp32 = wire_fp32;
+  plan.segs_qkv = &*segs_qkv;
+  plan.segs_gu = &*segs_gu;
+  plan.full = *full;
+  return plan;
+}
+
+// Sequence all-gather of a GEMM's A operand inside the GEMM: the peers' [B * Sl, K] slices.
+struct SeqPull {
+  c10::ArrayRef<int64_t> peers;
+  int64_t batch = 0, seq_local = 0;
+  bool on() const { return peers.size() > 1; }
+};
+
 struct Gemm {
   cudaStream_t stream;
   int* status;
+  static void set_pull(stb::GemmCall& c, const SeqPull& pull, int64_t src_ld) {
+    if (!pull.on()) return;
+    c.pull_degree = static_cast<int>(pull.peers.size());
+    c.pull_batch = static_cast<int>(pull.batch);
+    c.pull_seq_local = static_cast<int>(pull.seq_local);
+    c.pull_src_ld = src_ld;
+    for (size_t i = 0; i < pull.peers.size(); ++i)
+      c.pull_peers[i] = reinterpret_cast<const void*>(pull.peers[i]);
+  }
+  // out = a @ W^T (+ bias) [+ SwiGLU into hm] with W pulled from the FSDP ranks inside the GEMM
+  void allgather(const Tensor& a, Tensor& out, const float* bias, Tensor* hm, const AgPlan& plan,
+                 const at::Tensor& segs) const {
+    TORCH_CHECK(!segs.is_cuda() && segs.scalar_type() == at::kLong && segs.dim() == 2 &&
+                    segs.size(1) == 5 && segs.size(0) >= 1 && segs.size(0) <= 4 &&
+                    segs.is_contiguous(), "fused all-gather: bad segment table");
+    stb::AgGemmCall c{};
+    c.a = a.data_ptr();
+    c.out = out.data_ptr();
+    c.bias = bias;
+    c.M = static_cast<int>(a.size(0));
+    c.K = static_cast<int>(a.size(1));
+    c.N = static_cast<int>(out.size(1));
+    c.lda = a.stride(0);
+    c.ldo = out.stride(0);
+    if (hm != nullptr) {
+      c.gated_out = hm->data_ptr();
+      c.gated_inter = static_cast<int>(hm->size(1));
+    }
+    c.w.degree = static_cast<int>(plan.arenas.size());
+    for (size_t i = 0; i < plan.arenas.size(); ++i) {
+      if (plan.wire_fp32)
+        c.w.shard[i] = reinterpret_cast<const float*>(plan.arenas[i]);
+      else
+        c.w.shadow[i] = reinterpret_cast<const __nv_bfloat16*>(plan.arenas[i]);
+    }
+    const int64_t* t = segs.data_ptr<int64_t>();
+    c.w.n_segs = static_cast<int>(segs.size(0));
+    for (int j = 0; j < c.w.n_segs; ++j) {
+      c.w.seg[j].shard_off = t[5 * j];
+      c.w.seg[j].q = t[5 * j + 1];
+      TORCH_CHECK(t[5 * j + 2] % c.K == 0, "fused all-gather: a parameter is not whole rows");
+      c.w.seg[j].rows = static_cast<int>(t[5 * j + 2] / c.K);
+      c.w.seg[j].full_off = t[5 * j + 3];
+    }
+    c.w.full = reinterpret_cast<__nv_bfloat16*>(plan.full.data_ptr());
+    ok(stb::launch_gemm_allgather(c, status, stream), "gemm all-gather");
+  }
+  // `pull`: `a` is the local buffer that the GEMM first fills from the peers' sequence slices
   void run(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, const float* bias,
-           const Tensor* residual) const {
+           const Tensor* residual, const SeqPull& pull = SeqPull{}) const {
     stb::GemmCall c{};
+    set_pull(c, pull, a.stride(0));
     c.M = static_cast<int>(a_mn ? a.size(1) : a.size(0));
     c.K = static_cast<int>(a_mn ? a.size(0) : a.size(1));
     c.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
@@ -46,8 +132,10 @@ struct Gemm {
     ok(stb::launch_gemm_bf16(c, status, stream), "gemm");
   }
   // gate|up projection with the SwiGLU epilogue: gu = a @ w_gu^T, hm = silu(gate) * up
-  void swiglu(const Tensor& a, const Tensor& w_gu, Tensor& gu, Tensor& hm) const {
+  void swiglu(const Tensor& a, const Tensor& w_gu, Tensor& gu, Tensor& hm,
+              const SeqPull& pull = SeqPull{}) const {
     stb::GemmCall c{};
+    set_pull(c, pull, a.stride(0));
     c.M = static_cast<int>(a.size(0));
     c.K = static_cast<int>(a.size(1));
     c.N = static_cast<int>(w_gu.size(0));
@@ -61,6 +149,14 @@ struct Gemm {
     c.gated_out = hm.data_ptr();
     c.gated_inter = static_cast<int>(hm.size(1));
     ok(stb::launch_gemm_bf16(c, status, stream), "gemm swiglu");
+  }
+  // q|k|v projection (+ bias), pulling the weights inside the GEMM when a plan is given
+  void qkv_proj(const Tensor& a, const Tensor& w_qkv, Tensor& qkv, const float* bias,
+                const AgPlan& plan, const SeqPull& pull = SeqPull{}) const {
+    if (plan.on())
+      allgather(a, qkv, bias, nullptr, plan, *plan.segs_qkv);
+    else
+      run(a, w_qkv, qkv, false, false, bias, nullptr, pull);
   }
   // fp32 partial rows pushed into every TP rank's receive slot (all-reduce without SP)
   void broadcast(const Tensor& a, const Tensor& b, bool b_mn, c10::ArrayRef<int64_t> dest) const {
@@ -86,12 +182,17 @@ struct Gemm {
   // epilogue the tile's output grows by half and the epilogue becomes the bottleneck of this
   // short-K GEMM at 2048+ rows (240 us against 190 + 39 us at 4096 rows); at 1024 rows and below
   // the fused kernel wins (31 us against 28 + 8 us at 512 rows).  Results are bit-identical.
-  void gate_up(const Tensor& a, const Tensor& w_gu, Tensor& gu, Tensor& hm, cudaStream_t st) const {
-    if (a.size(0) <= 1024) {
-      swiglu(a, w_gu, gu, hm);
+  void gate_up(const Tensor& a, const Tensor& w_gu, Tensor& gu, Tensor& hm, cudaStream_t st,
+               const AgPlan& plan = AgPlan{}, const SeqPull& pull = SeqPull{}) const {
+    if (plan.on()) {
+      allgather(a, gu, nullptr, &hm, plan, *plan.segs_gu);
       return;
     }
-    run(a, w_gu, gu, false, false, nullptr, nullptr);
+    if (a.size(0) <= 1024) {
+      swiglu(a, w_gu, gu, hm, pull);
+      return;
+    }
+    run(a, w_gu, gu, false, false, nullptr, nullptr, pull);
     ok(stb::launch_swiglu_fwd(gu.data_ptr(), hm.data_ptr(), static_cast<int>(a.size(0)),
                               static_cast<int>(hm.size(1)), st), "swiglu");
   }
@@ -159,7 +260,10 @@ std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const T
                                   const Tensor& ln1, const Tensor& ln2, const Tensor& cos,
                                   const Tensor& sin, const c10::optional<Tensor>& positions,
                                   const c10::optional<Tensor>& mask, Tensor status, int64_t B,
-                                  int64_t S, int64_t hq, int64_t hkv, double eps) {
+                                  int64_t S, int64_t hq, int64_t hkv, double eps, c10::ArrayRef<int64_t> ag_arenas,
+    bool ag_wire_fp32, const c10::optional<Tensor>& ag_segs_qkv,
+    const c10::optional<Tensor>& ag_segs_gu, const c10::optional<Tensor>& ag_full) {
+  const AgPlan ag = make_ag_plan(ag_arenas, ag_wire_fp32, ag_segs_qkv, ag_segs_gu, ag_full);
   const int64_t M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
   auto bf = x2.options().dtype(at::kBFloat16);
@@ -173,7 +277,7 @@ std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const T
   ok(stb::launch_rmsnorm_fwd(x2.data_ptr<float>(), ln1.data_ptr<float>(), h1.data_ptr(),
                              inv1.data_ptr<float>(), M, H, static_cast<float>(eps), false, st), "rmsnorm");
   Tensor qkv = at::empty({M, W}, bf);
-  g.run(h1, w_qkv, qkv, false, false, b_qkv.data_ptr<float>(), nullptr);
+  g.qkv_proj(h1, w_qkv, qkv, b_qkv.data_ptr<float>(), ag);
   ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
                       hkv, D, false, st), "rope");
   Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
@@ -187,7 +291,7 @@ std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const T
   ok(stb::launch_rmsnorm_fwd(x_mid.data_ptr<float>(), ln2.data_ptr<float>(), h2.data_ptr(),
                              inv2.data_ptr<float>(), M, H, static_cast<float>(eps), false, st), "rmsnorm");
   Tensor gu = at::empty({M, 2 * inter}, bf), hm = at::empty({M, inter}, bf);
-  g.gate_up(h2, w_gu, gu, hm, st);
+  g.gate_up(h2, w_gu, gu, hm, st, ag);
   Tensor out = at::empty({M, H}, f32);
   g.run(hm, w_down, out, false, false, nullptr, &x_mid);
   return {h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm};
@@ -289,9 +393,14 @@ std::vector<Tensor> layer_forward_sp(
     int64_t hkv, double eps, Tensor h1_local, Tensor h2_local, c10::ArrayRef<int64_t> h1_ptrs,
     c10::ArrayRef<int64_t> h2_ptrs, c10::ArrayRef<int64_t> push_ptrs, Tensor recv,
     c10::ArrayRef<int64_t> flag_ptrs, int64_t tp_rank, int64_t epoch, int64_t flag_slot,
-    int64_t wait_us) {
+    int64_t wait_us, bool seq_pull, c10::ArrayRef<int64_t> ag_arenas,
+    bool ag_wire_fp32, const c10::optional<Tensor>& ag_segs_qkv,
+    const c10::optional<Tensor>& ag_segs_gu, const c10::optional<Tensor>& ag_full) {
+  const AgPlan ag = make_ag_plan(ag_arenas, ag_wire_fp32, ag_segs_qkv, ag_segs_gu, ag_full);
   const int64_t T = static_cast<int64_t>(h1_ptrs.size());
   const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
+  // the sequence gather runs inside the consuming GEMM unless that GEMM already pulls its weights
+  const bool pull_a = seq_pull && !ag.on();
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
   TORCH_CHECK(S % T == 0 && x2.size(0) == Ml && recv.dim() == 3 && recv.size(0) == T &&
                   recv.size(1) == Ml && recv.size(2) == H && recv.is_contiguous(),
@@ -310,9 +419,10 @@ std::vector<Tensor> layer_forward_sp(
                              inv1.data_ptr<float>(), Ml, H, feps, false, st), "rmsnorm");
   sp.barrier();                                   // every rank's h1 slice is written
   Tensor h_full = at::empty({M, H}, bf);
-  sp.gather(h1_ptrs, h_full, B, Sl);
+  if (!pull_a) sp.gather(h1_ptrs, h_full, B, Sl);
   Tensor qkv = at::empty({M, W}, bf);
-  g.run(h_full, w_qkv, qkv, false, false, b_qkv.data_ptr<float>(), nullptr);
+  g.qkv_proj(h_full, w_qkv, qkv, b_qkv.data_ptr<float>(), ag,
+             pull_a ? SeqPull{h1_ptrs, B, Sl} : SeqPull{});
   ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
                       hkv, D, false, st), "rope");
   Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
@@ -328,9 +438,9 @@ std::vector<Tensor> layer_forward_sp(
                                   h2_local.data_ptr(), inv2.data_ptr<float>(), Ml, H, feps, st),
      "slot sum + rmsnorm");
   sp.barrier();                                   // h2 slices written, receive slots consumed
-  sp.gather(h2_ptrs, h_full, B, Sl);
+  if (!pull_a) sp.gather(h2_ptrs, h_full, B, Sl);
   Tensor gu = at::empty({M, 2 * inter}, bf), hm = at::empty({M, inter}, bf);
-  g.gate_up(h_full, w_gu, gu, hm, st);
+  g.gate_up(h_full, w_gu, gu, hm, st, ag, pull_a ? SeqPull{h2_ptrs, B, Sl} : SeqPull{});
   g.scatter(hm, w_down, false, push_ptrs, static_cast<int>(S));
   sp.barrier();
   Tensor out = at::empty({Ml, H}, f32);
@@ -354,7 +464,7 @@ Tensor layer_backward_sp(
     Tensor dmb_local, c10::ArrayRef<int64_t> h1_ptrs, c10::ArrayRef<int64_t> h2_ptrs,
     c10::ArrayRef<int64_t> dob_ptrs, c10::ArrayRef<int64_t> dmb_ptrs,
     c10::ArrayRef<int64_t> push_ptrs, Tensor recv, c10::ArrayRef<int64_t> flag_ptrs,
-    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t wait_us) {
+    int64_t tp_rank, int64_t epoch, int64_t flag_slot, int64_t wait_us, bool seq_pull) {
   const int64_t T = static_cast<int64_t>(h1_ptrs.size());
   const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
@@ -370,10 +480,16 @@ Tensor layer_backward_sp(
   ok(stb::launch_cast_f32_to_bf16(d_out.data_ptr<float>(), dob_local.data_ptr(), Ml * H, st), "cast");
   sp.barrier();
   Tensor d_full = at::empty({M, H}, bf), h_full = at::empty({M, H}, bf);
-  sp.gather(dob_ptrs, d_full, B, Sl);
-  g.run(d_full, hm, g_down, true, true, nullptr, nullptr);                  // dW down
   Tensor d_hm = at::empty({M, inter}, bf);
-  g.run(d_full, w_down, d_hm, false, true, nullptr, nullptr);               // dX down (local cols)
+  if (seq_pull) {
+    // dX down gathers the peers' output-gradient slices while it runs; dW down reads them locally
+    g.run(d_full, w_down, d_hm, false, true, nullptr, nullptr, SeqPull{dob_ptrs, B, Sl});
+    g.run(d_full, hm, g_down, true, true, nullptr, nullptr);                // dW down
+  } else {
+    sp.gather(dob_ptrs, d_full, B, Sl);
+    g.run(d_full, hm, g_down, true, true, nullptr, nullptr);                // dW down
+    g.run(d_full, w_down, d_hm, false, true, nullptr, nullptr);             // dX down (local cols)
+  }
   Tensor d_gu = at::empty({M, 2 * inter}, bf);
   ok(stb::launch_swiglu_bwd(d_hm.data_ptr(), gu.data_ptr(), d_gu.data_ptr(), M, inter, st), "swiglu_bwd");
   sp.gather(h2_ptrs, h_full, B, Sl);                                        // re-gather h2
@@ -392,10 +508,15 @@ Tensor layer_backward_sp(
 
   ok(stb::launch_cast_f32_to_bf16(d_mid.data_ptr<float>(), dmb_local.data_ptr(), Ml * H, st), "cast");
   sp.barrier();
-  sp.gather(dmb_ptrs, d_full, B, Sl);
-  g.run(d_full, attn, g_o, true, true, nullptr, nullptr);                   // dW o
   Tensor d_attn = at::empty({M, hq * D}, bf);
-  g.run(d_full, w_o, d_attn, false, true, nullptr, nullptr);                // dX o (local heads)
+  if (seq_pull) {
+    g.run(d_full, w_o, d_attn, false, true, nullptr, nullptr, SeqPull{dmb_ptrs, B, Sl});  // dX o
+    g.run(d_full, attn, g_o, true, true, nullptr, nullptr);                 // dW o
+  } else {
+    sp.gather(dmb_ptrs, d_full, B, Sl);
+    g.run(d_full, attn, g_o, true, true, nullptr, nullptr);                 // dW o
+    g.run(d_full, w_o, d_attn, false, true, nullptr, nullptr);              // dX o (local heads)
+  }
   Tensor d_qkv = at::empty({M, W}, bf), delta = at::empty({B, hq, S}, f32);
   stb::AttnBwdCall bc{};
   bc.qkv = qkv.data_ptr();
@@ -455,7 +576,10 @@ std::vector<Tensor> layer_forward_tp(
     const c10::optional<Tensor>& mask, Tensor status, int64_t B, int64_t S, int64_t hq,
     int64_t hkv, double eps, c10::ArrayRef<int64_t> push_a, c10::ArrayRef<int64_t> push_b,
     Tensor recv_a, Tensor recv_b, c10::ArrayRef<int64_t> flag_ptrs, int64_t tp_rank,
-    int64_t epoch, int64_t flag_slot, int64_t wait_us) {
+    int64_t epoch, int64_t flag_slot, int64_t wait_us, c10::ArrayRef<int64_t> ag_arenas,
+    bool ag_wire_fp32, const c10::optional<Tensor>& ag_segs_qkv,
+    const c10::optional<Tensor>& ag_segs_gu, const c10::optional<Tensor>& ag_full) {
+  const AgPlan ag = make_ag_plan(ag_arenas, ag_wire_fp32, ag_segs_qkv, ag_segs_gu, ag_full);
   const int64_t T = static_cast<int64_t>(push_a.size());
   const int64_t M = B * S, H = x2.size(1), D = 128;
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
@@ -474,7 +598,7 @@ std::vector<Tensor> layer_forward_tp(
   ok(stb::launch_rmsnorm_fwd(x2.data_ptr<float>(), ln1.data_ptr<float>(), h1.data_ptr(),
                              inv1.data_ptr<float>(), M, H, feps, false, st), "rmsnorm");
   Tensor qkv = at::empty({M, W}, bf);
-  g.run(h1, w_qkv, qkv, false, false, b_qkv.data_ptr<float>(), nullptr);
+  g.qkv_proj(h1, w_qkv, qkv, b_qkv.data_ptr<float>(), ag);
   ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
                       hkv, D, false, st), "rope");
   Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
@@ -490,7 +614,7 @@ std::vector<Tensor> layer_forward_tp(
                                   ln2.data_ptr<float>(), h2.data_ptr(), inv2.data_ptr<float>(), M, H,
                                   feps, st), "slot sum + rmsnorm");
   Tensor gu = at::empty({M, 2 * inter}, bf), hm = at::empty({M, inter}, bf);
-  g.gate_up(h2, w_gu, gu, hm, st);
+  g.gate_up(h2, w_gu, gu, hm, st, ag);
   g.broadcast(hm, w_down, false, push_b);
   sp.barrier();
   Tensor out = at::empty({M, H}, f32);

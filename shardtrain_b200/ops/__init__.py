@@ -29,7 +29,7 @@ _KERNELS_PER_CALL = {"colsum_bf16": 2, "attention_bwd": 3, "status_read": 0, "st
                      "layer_forward": 10, "layer_backward": 26, "status_tensor": 0,
                      "layer_forward_sp": 15, "layer_backward_sp": 31,
                      "layer_forward_tp": 12, "layer_backward_tp": 29,
-                     "peer_alloc": 0, "peer_free": 0, "device_synchronize": 0, "ipc_handle": 0, "ipc_open": 0,
+                     "peer_alloc": 0, "peer_free": 0, "device_synchronize": 0, "enable_peer_access": 0, "ipc_handle": 0, "ipc_open": 0,
                      "ipc_close": 0, "tensor_from_ptr": 0}
 
 
@@ -97,6 +97,7 @@ def check_status(where: str = "") -> None:
             5: "peer flag wait expired (a peer never signalled)",
             6: "attention pipeline wait expired",
             7: "kernel rejected its arguments",
+            8: "GEMM gave up waiting for rows of its operand that another CTA was pulling",
         }
         detail = ""
         if code == 5:

@@ -51,8 +51,10 @@ def timed(fn, warmup, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_scatter", "attention", "reduce_scatter_adamw",
-                                       "gather_params", "gather_shadow", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_scatter", "gemm_allgather", "attention",
+                                       "reduce_scatter_adamw", "gather_params", "gather_shadow",
+                                       "rmsnorm"])
+    ap.add_argument("--gated", type=int, default=0, help="gemm_allgather: gate|up with SwiGLU epilogue")
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=17920)
     ap.add_argument("--k", type=int, default=1536)
@@ -94,6 +96,50 @@ def main():
         tflops = 2 * a.m * a.n * a.k / ms / 1e9
         out.update(shape=[a.m, a.n, a.k], owners=a.owners, seq=a.seq, ms=ms, tflops=tflops,
                    output_gbs=a.m * a.n * 4 / ms / 1e6, frac_of_sustained_cublas=tflops / sustained)
+    elif a.kernel == "gemm_allgather":
+        # all-gather fused into the GEMM; the `--owners` ranks' shard arenas are local tensors here
+        # (the multi-GPU path hands the same kernel peer pointers), so this measures the kernel's
+        # own pipeline without the link.  Compared with gather kernel + GEMM on the same data.
+        F = a.owners
+        rows = a.n // (8 * F) * (8 * F)
+        numel = rows * a.k
+        q = numel // F
+        W = (torch.randn(rows, a.k, device=dev) * 0.1).bfloat16()
+        arenas = [W.reshape(-1)[r * q:(r + 1) * q].clone() for r in range(F)]
+        ptrs = [t.data_ptr() for t in arenas]
+        A = torch.randn(a.m, a.k, device=dev).bfloat16()
+        full = torch.empty(numel, device=dev, dtype=torch.bfloat16)
+        side = torch.empty(4, device=dev)
+        if a.gated:
+            half = rows // 2
+            # gate and up are two parameters: each cut into F shards of its own
+            qh = half * a.k // F
+            arenas = [torch.cat([W[:half].reshape(-1)[r * qh:(r + 1) * qh],
+                                 W[half:].reshape(-1)[r * qh:(r + 1) * qh]]) for r in range(F)]
+            ptrs = [t.data_ptr() for t in arenas]
+            table = torch.tensor([[0, qh, half * a.k, 0, 0], [qh, qh, half * a.k, half * a.k, 0]],
+                                 dtype=torch.int64)
+            C = torch.empty(a.m, rows, device=dev, dtype=torch.bfloat16)
+            Hm = torch.empty(a.m, half, device=dev, dtype=torch.bfloat16)
+            fused = lambda: ops.gemm_allgather(A, C, None, ptrs, False, table, full, Hm, 0)   # noqa: E731
+
+            def two():
+                ops.gather_params(ptrs, table, full, side, ptrs)
+                ops.gemm_swiglu(A, full.view(rows, a.k), C, Hm)
+        else:
+            table = torch.tensor([[0, q, numel, 0, 0]], dtype=torch.int64)
+            C = torch.empty(a.m, rows, device=dev, dtype=torch.bfloat16)
+            fused = lambda: ops.gemm_allgather(A, C, None, ptrs, False, table, full, None, a.bn)   # noqa: E731
+
+            def two():
+                ops.gather_params(ptrs, table, full, side, ptrs)
+                ops.gemm(A, full.view(rows, a.k), C, False, False, None, None, False, 1.0, 0)
+        ms_fused = timed(fused, a.warmup, a.iters, flush=True)
+        ms_two = timed(two, a.warmup, a.iters, flush=True)
+        tflops = 2 * a.m * rows * a.k / ms_fused / 1e9
+        out.update(shape=[a.m, rows, a.k], owners=F, gated=a.gated, fused_ms=ms_fused,
+                   gather_then_gemm_ms=ms_two, tflops=tflops, weight_gbs=numel * 2 / ms_fused / 1e6,
+                   frac_of_sustained_cublas=tflops / sustained)
     elif a.kernel == "attention":
         D, W = 128, (a.hq + 2 * a.hkv) * 128
         rows = a.batch * a.seq

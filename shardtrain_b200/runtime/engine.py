@@ -229,7 +229,7 @@ class ShardedRuntime:
                  backward_prefetch=False, async_grad_rs=False, communication_policy="conservative",
                  directory=None, diagnostics_enabled=True, communication_backend="auto",
                  retain_parameters=False, compute_dtype=None, device_wait_seconds=2.0,
-                 wire_dtype="bf16"):
+                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=True):
         self.device = torch.device(device)
         self.reshard_after_forward = reshard_after_forward
         self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
@@ -248,6 +248,14 @@ class ShardedRuntime:
         if wire_dtype not in ("bf16", "fp32"):
             raise ValueError("wire_dtype must be bf16 or fp32")
         self.wire_dtype = wire_dtype
+        # sm_100a, FSDP degree > 1: whether a decoder layer's forward pulls q|k|v and gate|up
+        # from the owners' shards inside the consuming GEMMs instead of gathering them first
+        if fused_allgather not in ("auto", "on", "off"):
+            raise ValueError("fused_allgather must be auto, on or off")
+        self.fused_allgather = fused_allgather
+        # sm_100a, sequence parallel: the GEMM that consumes a sequence all-gather pulls the
+        # peers' slices itself (one kernel) instead of running after a gather kernel
+        self.fused_seq_gather = bool(fused_seq_gather)
         # time budget of every device-side wait on a peer (seconds; clamped by PeerMemory)
         self.device_wait_seconds = float(device_wait_seconds)
         rank = dist.get_rank() if dist.is_initialized() else 0

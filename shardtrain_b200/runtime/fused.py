@@ -55,6 +55,12 @@ class UnitPlan:
     shard_numel: int = 0
     gather_table: torch.Tensor | None = None
     reduce_table: torch.Tensor | None = None
+    # decoder layers: the gather table split for the "pull the weights inside the GEMM" forward
+    # -- rows of q|k|v and of gate|up (consumed by the fused all-gather GEMMs) and the rest (o,
+    # down and the vectors, still landed by the gather kernel)
+    ag_segs_qkv: torch.Tensor | None = None
+    ag_segs_gu: torch.Tensor | None = None
+    gather_table_rest: torch.Tensor | None = None
     # persistent materialisation state (allocated once at registration)
     full_bf16: torch.Tensor | None = None
     full_fp32: torch.Tensor | None = None
@@ -118,6 +124,13 @@ def build_plan(unit) -> UnitPlan:
     handles = [by_name[n] for n in ordered]
     plan.gather_table = segment_table(handles, plan.param_offsets, plan.fp32_names)
     plan.reduce_table = segment_table(handles, plan.grad_offsets, set(), mark_replicated=True)
+    qkv = [i for i, n in enumerate(ordered) if n.endswith(_LAYER_ORDER[:3])]
+    gu = [i for i, n in enumerate(ordered) if n.endswith(_LAYER_ORDER[4:6])]
+    if len(qkv) == 3 and len(gu) == 2:
+        rest = [i for i in range(len(ordered)) if i not in qkv + gu]
+        plan.ag_segs_qkv = plan.gather_table[qkv].contiguous()
+        plan.ag_segs_gu = plan.gather_table[gu].contiguous()
+        plan.gather_table_rest = plan.gather_table[rest].contiguous()
     return plan
 
 
@@ -201,6 +214,31 @@ class FusedExecutor:
         self._rope_cache = {}
         self._scratch = {}
         self.token_grad = torch.zeros(1, dtype=torch.float32, device=runtime.device)
+        self.rows_hint = None     # rows of the layer GEMMs' activation, known after the first input
+
+    # ------------------------------------------------------------------ fused all-gather -> GEMM
+    PULL_MAX_ROWS = 1024     # beyond this the weights would cross the link in several passes
+
+    def pulls_in_gemm(self, unit, phase) -> bool:
+        """Should this materialisation leave q|k|v and gate|up to the consuming GEMMs?  Only in
+        the forward of a decoder layer, with FSDP peers to pull from; `auto` also wants the
+        activation to fit the accumulators the kernel keeps in TMEM (<= 1024 rows)."""
+        mode = self.runtime.fused_allgather
+        plan = self.runtime.materializer.plans[unit.unit_id]
+        if mode == "off" or phase != "FWD" or self.peer.degree == 1 or plan.ag_segs_qkv is None:
+            return False
+        if mode == "on":
+            return True
+        return self.rows_hint is not None and self.rows_hint <= self.PULL_MAX_ROWS
+
+    def ag_arguments(self, unit, plan):
+        """The five trailing arguments of the layer-forward ops: empty unless this lease left
+        q|k|v and gate|up in the owners' arenas for the GEMMs to pull."""
+        if not unit.lease.extras.get("pull_in_gemm"):
+            return [], False, None, None, None
+        fp32 = self.runtime.wire_dtype == "fp32"
+        arenas = self.param_peer_ptrs if fp32 else self.shadow_peer_ptrs
+        return list(arenas), fp32, plan.ag_segs_qkv, plan.ag_segs_gu, plan.full_bf16
 
     # ------------------------------------------------------------------ allocation
     def allocate(self):
@@ -507,6 +545,7 @@ class FusedEmbeddingFn(torch.autograd.Function):
         ctx.save_for_backward(ids)
         hidden = ex.cfg.hidden_size
         flat = ids.reshape(-1).contiguous()
+        ex.rows_hint = flat.numel() * (ex.tp_degree if rt.sp else 1)
         out = torch.empty((*ids.shape, hidden), dtype=torch.float32, device=rt.device)
         base = handle.arena_offset * 4
         ptrs = [p + base for p in ex.param_peer_ptrs]
@@ -645,6 +684,10 @@ class FusedLayerFn(torch.autograd.Function):
             w["w_qkv"], w["b_qkv"], w["w_o"], w["w_gu"], w["w_down"], w["ln1"], w["ln2"])
         unit.prefetch_after_input(unit.forward_prefetch_handle, "FWD")
         ctx.ex, ctx.unit, ctx.index, ctx.tables, ctx.mask = ex, unit, index, tables, mask
+        ag = ex.ag_arguments(unit, plan)
+        # after this forward the unit's full buffer is complete either way (the pulling GEMMs
+        # mirror what they pull), so later readers of the lease take the plain path
+        unit.lease.extras["pull_in_gemm"] = False
         if ex.tp_degree > 1 and not ex.runtime.sp:
             # tensor parallel, replicated activations: partial sums are all-reduced by push
             tp = ex.tp_peer
@@ -654,7 +697,7 @@ class FusedLayerFn(torch.autograd.Function):
                 x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
                 ex.status, B, S, hq, hkv, cfg.rms_norm_eps, buf["push"][0], buf["push"][1],
                 buf["recv"][0], buf["recv"][1], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
-                tp.wait_us)
+                tp.wait_us, *ag)
             tp.epochs["sp_ag"] = epoch + 2
             ctx.dims = (B, S, H, inter)
             ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm)
@@ -670,7 +713,7 @@ class FusedLayerFn(torch.autograd.Function):
                 x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask,
                 ex.status, B, S_full, hq, hkv, cfg.rms_norm_eps, h1, h2, h1_ptrs, h2_ptrs,
                 buf["push"], buf["recv"], buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT,
-                tp.wait_us)
+                tp.wait_us, ex.runtime.fused_seq_gather, *ag)
             tp.epochs["sp_ag"] = epoch + 4
             ctx.dims = (B, S_full, H, inter)
             ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm)
@@ -678,7 +721,7 @@ class FusedLayerFn(torch.autograd.Function):
         # the 10 launches of the forward run from C++ (csrc/layer_executor.cpp)
         h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm = ops.layer_forward(
             x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask, ex.status,
-            B, S, hq, hkv, cfg.rms_norm_eps)
+            B, S, hq, hkv, cfg.rms_norm_eps, *ag)
 
         ctx.dims = (B, S, H, inter)
         ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm)
@@ -749,7 +792,7 @@ class FusedLayerFn(torch.autograd.Function):
             w["w_down"], w["ln1"], w["ln2"], gv["down"], gv["gate_up"], gv["ln2"], gv["o"],
             gv["bias"], gv["qkv"], gv["ln1"], cos, sin, positions, ctx.mask, ex.status, B, S_full,
             ex.hq, ex.hkv, dob, dmb, h1_ptrs, h2_ptrs, dob_ptrs, dmb_ptrs, buf["push"], buf["recv"],
-            buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT, tp.wait_us)
+            buf["flags"], ex.tp_rank, epoch, SP_FLAG_SLOT, tp.wait_us, ex.runtime.fused_seq_gather)
         tp.epochs["sp_ag"] = epoch + 4
         return (dx.view(B, S_full // ex.tp_degree, H), None, None, None, None, None,
                 *([ex.token_grad] * len(plan.names)))

@@ -267,21 +267,25 @@ class PeerMaterializer:
         lease.ag_storage = comm.buffer(plan.full_bf16, "fsdp_ag")
         lease.extras["full_bf16"], lease.extras["full_fp32"] = plan.full_bf16, plan.full_fp32
         ptrs = self.arenas.param_peer_ptrs
+        # a decoder layer's forward may pull q|k|v and gate|up inside its GEMMs: the gather
+        # kernel then lands only the other parameters
+        pull = self.arenas.pulls_in_gemm(unit, phase)
+        table = plan.gather_table_rest if pull else plan.gather_table
+        lease.extras["pull_in_gemm"] = pull
 
         def launch():
             # the shards depend on the optimizer's writes (and on every peer having finished
             # its own), never on activations queued on the compute stream
             runtime.wait_parameter_shards_ready()
-            if plan.gather_table.numel():     # empty when the unit's buffer aliases the shadow
+            if table.numel():     # empty when the unit's buffer aliases the shadow
                 shadows = [] if runtime.wire_dtype == "fp32" else self.arenas.shadow_peer_ptrs
-                self.ops.gather_params(ptrs, plan.gather_table, plan.full_bf16, plan.full_fp32,
-                                       shadows)
+                self.ops.gather_params(ptrs, table, plan.full_bf16, plan.full_fp32, shadows)
 
         # a buffer may be re-gathered only after its last reader on the compute stream
         after = (plan.last_reader,) if plan.last_reader is not None else ()
         lease.ag_ticket = comm.issue_kernel(
-            "fsdp", "fsdp_ag_cast", self.group, launch, channel="fsdp_ag", after_events=after,
-            numel=plan.shard_numel, leases=(lease.ag_storage,),
+            "fsdp", "fsdp_ag_partial" if pull else "fsdp_ag_cast", self.group, launch,
+            channel="fsdp_ag", after_events=after, numel=plan.shard_numel, leases=(lease.ag_storage,),
             group_role="parameter_materialization")
         return lease
 

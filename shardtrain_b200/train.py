@@ -36,7 +36,8 @@ def _runtime_rows(config, session):
         forward_prefetch=rc.forward_prefetch, backward_prefetch=rc.backward_prefetch,
         async_grad_rs=rc.async_grad_rs, communication_policy=rc.communication_policy,
         directory=session.directory, communication_backend=rc.communication_backend,
-        retain_parameters=rc.retain_parameters,
+        retain_parameters=rc.retain_parameters, fused_allgather=rc.fused_allgather,
+        wire_dtype=rc.wire_dtype, fused_seq_gather=rc.fused_seq_gather,
     )
     runtime.register(model, mesh, sp=config.parallel.sp_enabled)
     trainer = ShardedTrainer(model, runtime, tc.lr)

@@ -479,3 +479,145 @@ def test_gemm_broadcast_epilogue_writes_every_row_to_every_destination(ops):
     for d in dest:
         torch.testing.assert_close(d, want, atol=2e-2, rtol=2e-2)
         assert torch.equal(d, dest[0])
+
+
+def _shard_arenas(weights, degree, fp32):
+    """Cut each [rows, K] parameter into `degree` flat shards (q = ceil(numel / F), zero padded)
+    and lay the shards of all parameters out one after another in `degree` emulated rank arenas.
+    Returns (arenas, segment table rows [shard_off, q, numel, full_off, 0])."""
+    offsets, table, cursor, full_cursor = [], [], 0, 0
+    for w in weights:
+        numel = w.numel()
+        q = -(-numel // degree)
+        table.append([cursor, q, numel, full_cursor, 0])
+        offsets.append((cursor, q))
+        cursor += -(-q // 8) * 8 if q % 8 == 0 else q     # keep odd layouts odd on purpose
+        full_cursor += -(-numel // 8) * 8
+    dtype = torch.float32 if fp32 else torch.bfloat16
+    arenas = [torch.zeros(cursor + 8, device=DEV, dtype=dtype) for _ in range(degree)]
+    for w, (off, q) in zip(weights, offsets):
+        flat = w.reshape(-1).to(dtype)
+        for r in range(degree):
+            piece = flat[r * q:(r + 1) * q]
+            arenas[r][off:off + piece.numel()] = piece
+    return arenas, torch.tensor(table, dtype=torch.int64), full_cursor
+
+
+AG_CASES = [
+    # M, K, rows of each parameter, F, fp32 wire, bias, force_bn
+    (512, 1536, (1536, 256, 256), 8, False, True, 0),       # q|k|v of the 1.5B layer
+    (512, 1536, (1536, 256, 256), 8, False, True, 128),
+    (1024, 512, (512, 128, 128), 4, False, False, 64),      # eight row tiles, one pass
+    (1100, 256, (384,), 2, False, True, 128),               # three passes: later ones read `full`
+    (300, 392, (72, 40), 5, False, True, 0),                # K tail, shards that end mid-row (odd q)
+    (200, 264, (104,), 7, True, False, 0),                  # fp32 on the wire, unaligned shards
+    (512, 1536, (1536, 256, 256), 8, True, True, 0),        # fp32 on the wire, aligned
+]
+
+
+@pytest.mark.parametrize("case", AG_CASES, ids=[f"m{c[0]}k{c[1]}f{c[3]}{'w32' if c[4] else ''}bn{c[6]}" for c in AG_CASES])
+def test_allgather_fused_into_gemm_with_emulated_ranks(ops, case):
+    """out = A @ W^T where W's rows are pulled inside the GEMM from the F ranks' shard arenas
+    (local tensors stand in for the peers' memory; the kernel only reads them).  Checked
+    elementwise against the FP32 product, and the by-product copy of W against W itself."""
+    M, K, rows, degree, fp32, with_bias, bn = case
+    torch.manual_seed(1)
+    weights = [(torch.randn(r, K, device=DEV) * 0.5).bfloat16() for r in rows]
+    W = torch.cat(weights)
+    N = W.shape[0]
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV) if with_bias else None
+    arenas, table, full_numel = _shard_arenas(weights, degree, fp32)
+    full = torch.full((full_numel,), float("nan"), device=DEV, dtype=torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_allgather(a, out, bias, [t.data_ptr() for t in arenas], fp32, table, full, None, bn)
+    ref = a.float() @ W.float().t()
+    if with_bias:
+        ref = ref + bias
+    torch.testing.assert_close(out.float(), ref, atol=0.25, rtol=2e-2)
+    assert rel(out, ref) < 4e-3
+    # edge rows / columns elementwise (ragged tiles, last row tile)
+    torch.testing.assert_close(out[-3:].float(), ref[-3:], atol=0.25, rtol=2e-2)
+    torch.testing.assert_close(out[:, -5:].float(), ref[:, -5:], atol=0.25, rtol=2e-2)
+    # the pulled rows were mirrored into the local full buffer, bit for bit
+    cursor = 0
+    for w in weights:
+        assert torch.equal(full[cursor:cursor + w.numel()].view_as(w), w)
+        cursor += -(-w.numel() // 8) * 8
+    # same result as the two-kernel path (gather, then GEMM): bit-identical accumulation order
+    two = torch.empty_like(out)
+    ops.gemm(a, W, two, False, False, bias, None, False, 1.0, 0)
+    assert rel(out, two) < 2e-3
+
+
+@pytest.mark.parametrize("M,inter,K,degree", [(512, 896, 1536, 8), (300, 328, 256, 4), (1024, 256, 512, 2)])
+def test_allgather_fused_into_gate_up_gemm_with_swiglu(ops, M, inter, K, degree):
+    """Gated variant: W = gate|up pulled from the shard arenas, SwiGLU in the epilogue; gu and
+    h agree with the local gated GEMM on the gathered weight (each tile walks K from its own
+    starting block, so the fp32 sums differ in the last bits, not more)."""
+    torch.manual_seed(2)
+    gate = (torch.randn(inter, K, device=DEV) * 0.3).bfloat16()
+    up = (torch.randn(inter, K, device=DEV) * 0.3).bfloat16()
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    arenas, table, full_numel = _shard_arenas([gate, up], degree, False)
+    full = torch.zeros(full_numel, device=DEV, dtype=torch.bfloat16)
+    gu = torch.full((M, 2 * inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    h = torch.full((M, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_allgather(a, gu, None, [t.data_ptr() for t in arenas], False, table, full, h, 0)
+    w_gu = torch.cat([gate, up])
+    ref_gu = torch.empty_like(gu)
+    ref_h = torch.empty_like(h)
+    ops.gemm_swiglu(a, w_gu, ref_gu, ref_h)
+    torch.testing.assert_close(gu.float(), ref_gu.float(), atol=0.07, rtol=1.6e-2)
+    torch.testing.assert_close(h.float(), ref_h.float(), atol=0.07, rtol=1.6e-2)
+    assert rel(gu, ref_gu) < 1e-3 and rel(h, ref_h) < 2e-3
+    want = a.float() @ w_gu.float().t()
+    torch.testing.assert_close(gu.float(), want, atol=0.25, rtol=2e-2)
+    g32, u32 = gu[:, :inter].float(), gu[:, inter:].float()
+    torch.testing.assert_close(h.float(), torch.nn.functional.silu(g32).bfloat16().float() * u32,
+                               atol=0.05, rtol=2e-2)
+    assert torch.equal(full[:gate.numel()].view_as(gate), gate)      # the by-product copy
+
+
+def test_allgather_gemm_rejects_bad_arguments(ops):
+    a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16)
+    arenas, table, full_numel = _shard_arenas([w], 2, False)
+    out = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    ptrs = [t.data_ptr() for t in arenas]
+    with pytest.raises(RuntimeError):        # rows of the table do not add up to N
+        ops.gemm_allgather(a, torch.zeros(128, 72, device=DEV, dtype=torch.bfloat16), None, ptrs,
+                           False, table, None, None, 0)
+    with pytest.raises(RuntimeError):        # more row tiles than TMEM accumulators, no `full`
+        big = torch.zeros(1100, 64, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_allgather(big, torch.zeros(1100, 64, device=DEV, dtype=torch.bfloat16), None, ptrs,
+                           False, table, None, None, 128)
+    with pytest.raises(RuntimeError):        # misaligned arena
+        ops.gemm_allgather(a, out, None, [ptrs[0] + 2, ptrs[1]], False, table, None, None, 0)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("T,B,sl,K,N,b_mn", [(2, 2, 256, 512, 384, False), (4, 1, 96, 264, 520, False),
+                                             (8, 3, 64, 1536, 2048, False), (2, 2, 128, 256, 512, True)])
+def test_sequence_gather_fused_into_gemm_with_emulated_peers(ops, T, B, sl, K, N, b_mn):
+    """A is the sequence all-gather of T ranks' [B, sl, K] slices, pulled by the GEMM itself
+    (local tensors stand in for the peers' buffers).  The result and the gathered operand the
+    kernel leaves behind are checked against the FP32 product / the plain concatenation."""
+    torch.manual_seed(3)
+    slices = [torch.randn(B * sl, K, device=DEV).bfloat16() for _ in range(T)]
+    w = (torch.randn(K, N, device=DEV) if b_mn else torch.randn(N, K, device=DEV)).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    M = B * T * sl
+    a_dst = torch.full((M, K), float("nan"), device=DEV, dtype=torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):          # a second launch reuses the flag buffer with a new epoch
+        a_dst.fill_(float("nan"))
+        ops.gemm_seq_pull(a_dst, w, out, b_mn, bias, [s.data_ptr() for s in slices], B, sl, 0)
+    gathered = torch.stack([s.view(B, sl, K) for s in slices], dim=1).reshape(M, K)
+    assert torch.equal(a_dst, gathered)
+    ref = gathered.float() @ (w.float() if b_mn else w.float().t()) + bias
+    torch.testing.assert_close(out.float(), ref, atol=0.5, rtol=2e-2)
+    assert rel(out, ref) < 4e-3
+    two = torch.empty_like(out)
+    ops.gemm(gathered, w, two, False, b_mn, bias, None, False, 1.0, 0)
+    assert torch.equal(out, two)      # same tiles, same accumulation order as the plain GEMM

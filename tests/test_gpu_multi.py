@@ -18,10 +18,18 @@ CASES = [
     ("fsdp2", 2, ["--fsdp", 2, "--shape", "d128"]),
     ("fsdp2_untied", 2, ["--fsdp", 2, "--shape", "d128", "--tied", 0]),
     ("tp2_sp", 2, ["--fsdp", 1, "--tp", 2, "--sp", 1, "--shape", "d128tp"]),
+    ("tp2_sp_gather_kernel", 2, ["--fsdp", 1, "--tp", 2, "--sp", 1, "--shape", "d128tp",
+                                 "--seq-pull", 0]),
     ("tp2", 2, ["--fsdp", 1, "--tp", 2, "--sp", 0, "--shape", "d128tp"]),
     ("fsdp2_tp2_sp", 4, ["--fsdp", 2, "--tp", 2, "--sp", 1, "--shape", "d128tp"]),
     ("fsdp2_tp2", 4, ["--fsdp", 2, "--tp", 2, "--sp", 0, "--shape", "d128tp", "--tied", 0]),
     ("fsdp4", 4, ["--fsdp", 4, "--shape", "d128"]),
+    # q|k|v and gate|up pulled from the peers inside the forward GEMMs (fused all-gather -> GEMM)
+    ("fsdp2_pull", 2, ["--fsdp", 2, "--shape", "d128", "--fused-allgather", "on"]),
+    ("fsdp2_pull_fp32_wire", 2, ["--fsdp", 2, "--shape", "d128", "--fused-allgather", "on",
+                                 "--wire", "fp32"]),
+    ("fsdp2_tp2_sp_pull", 4, ["--fsdp", 2, "--tp", 2, "--sp", 1, "--shape", "d128tp",
+                              "--fused-allgather", "on"]),
 ]
 
 
@@ -39,3 +47,6 @@ def test_fused_executor_matches_dense_on_a_mesh(tmp_path, name, ranks, mesh):
         for row in record["rows"]:
             assert abs(row["loss"] - row["ref"]) < 2e-3
         assert "fsdp_ag_cast" in record["kinds"]          # the peer-memory materialiser ran
+        if "--fused-allgather" in mesh:
+            # the layers' forward gathers were partial: the GEMMs pulled the rest themselves
+            assert record["kinds"].get("fsdp_ag_partial") == 3 * 2 * 2     # steps x micro x layers

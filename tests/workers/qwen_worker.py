@@ -33,6 +33,9 @@ def main():
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--optimizer", default="adamw")
     ap.add_argument("--backend", default="auto")
+    ap.add_argument("--fused-allgather", default="auto")
+    ap.add_argument("--wire", default="bf16")
+    ap.add_argument("--seq-pull", type=int, default=1)
     ap.add_argument("--inject-inf-rank", type=int, default=-1,
                     help="this rank poisons one shard gradient with inf in step 1 (host-side injection)")
     ap.add_argument("--delay-rank", type=int, default=-1,
@@ -73,7 +76,9 @@ def main():
         rt = ShardedRuntime(device=ctx.device, reshard_after_forward=bool(a.reshard),
                             forward_prefetch=fp, backward_prefetch=bp, async_grad_rs=ar,
                             communication_policy=a.policy, directory=out,
-                            communication_backend=a.backend, compute_dtype=a.dtype)
+                            communication_backend=a.backend, compute_dtype=a.dtype,
+                            fused_allgather=a.fused_allgather, wire_dtype=a.wire,
+                            fused_seq_gather=bool(a.seq_pull))
         rt.register(model, ctx, sp=bool(a.sp))
         lr = 1e-3 if a.optimizer == "adamw" else 0.05
         tr = QwenTrainer(model, rt, lr=lr, optimizer=a.optimizer, accumulation_steps=a.accum,
