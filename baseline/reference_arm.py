@@ -128,7 +128,7 @@ def _run(args) -> None:
     if fsdp * tp != args.gpus:
         raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
     m = _measure(args, fsdp, tp, sp)
-    labels = bench.VALID_LABELS_PER_STEP
+    labels = bench.valid_labels(args)
     value = labels * 1000.0 / m["ms"]
     published = bench.PUBLISHED.get(args.gpus, {}).get(m["strategy"])
     line = {
@@ -138,8 +138,10 @@ def _run(args) -> None:
         "vs_baseline": value / published if published else None,
         "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "impl": "reference",
-        "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else ""),
-                   "global_batch": 16, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
+        "config": {"model": bench.MODELS[args.model]["label"]
+                            + (f" ({args.layers} layers: debug)" if args.layers else ""),
+                   "global_batch": args.global_batch, "seq_len": bench.MODELS[args.model]["seq_len"],
+                   "grad_accum": 2, "optimizer": "adamw",
                    "parallelism": m["strategy"], "valid_labels_per_step": labels,
                    "precision": "bf16 autocast GEMMs, math SDPA; fp32 shards, gradients, "
                                 "NCCL communication, AdamW(foreach=False) state",
@@ -154,7 +156,7 @@ def _run(args) -> None:
         "loss_first_last": m["losses"],
         "peak_memory_gib": m["peak"],
     }
-    hybrid = bench.HYBRID.get(args.gpus)
+    hybrid = bench.HYBRID.get(args.gpus) if args.model == "1.5b" else None
     if hybrid is not None and not args.strategy and not args.no_secondary:
         try:
             h = _measure(args, *hybrid)

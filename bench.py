@@ -39,6 +39,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="1.5b", choices=["1.5b", "7b"],
+                    help="1.5b: the headline workload (S512); 7b: Qwen2.5-7B S2048, meant for "
+                         "--gpus 8 --strategy F2T4/SP")
     ap.add_argument("--strategy", default="", help="F{dp}T{tp}[/SP]; default F{gpus}T1")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (not reportable)")
     ap.add_argument("--global-batch", type=int, default=16,
@@ -102,13 +105,28 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
+MODELS = {
+    # name: architecture, sequence length, default strategy on 8 GPUs
+    "1.5b": dict(label="Qwen2.5-1.5B", seq_len=512,
+                 arch=dict(vocab_size=151936, hidden_size=1536, num_heads=12, num_key_value_heads=2,
+                           mlp_hidden_size=8960, tie_word_embeddings=True)),
+    "7b": dict(label="Qwen2.5-7B", seq_len=2048,
+               arch=dict(vocab_size=152064, hidden_size=3584, num_heads=28, num_key_value_heads=4,
+                         mlp_hidden_size=18944, tie_word_embeddings=False)),
+}
+
+
+def valid_labels(args):
+    return args.global_batch * (MODELS[args.model]["seq_len"] - 1)
+
+
 def qwen15b_dict(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
     """The benchmark configuration as a plain mapping (shared by both arms)."""
     layers = args.layers or 28
+    spec = MODELS[args.model]
     return ({
-        "model": dict(model_type="qwen2", vocab_size=151936, layers=layers, hidden_size=1536,
-                      num_heads=12, num_key_value_heads=2, mlp_hidden_size=8960, seq_len=512,
-                      rope_theta=1000000.0, tie_word_embeddings=True, rms_norm_eps=1e-6),
+        "model": dict(model_type="qwen2", layers=layers, seq_len=spec["seq_len"],
+                      rope_theta=1000000.0, rms_norm_eps=1e-6, **spec["arch"]),
         "parallel": dict(fsdp_degree=fsdp, tp_degree=tp, sp_enabled=sp, device=device_backend[0],
                          backend=device_backend[1]),
         "runtime": dict(param_grouping="block", reshard_after_forward=True, forward_prefetch=True,
@@ -258,6 +276,7 @@ def run_ours(args):
     if fsdp * tp != args.gpus:
         raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
     m = measure_ours(args, fsdp, tp, sp)
+    VALID_LABELS_PER_STEP = valid_labels(args)
     value = VALID_LABELS_PER_STEP * 1000.0 / m["ms"]
     published = PUBLISHED.get(args.gpus, {}).get(m["strategy"])
     wire = ("fp32 parameter shards" if args.fp32_wire else
@@ -269,9 +288,11 @@ def run_ours(args):
         "vs_baseline": value / published if published else None,
         "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-1.5B" + (f" ({args.layers} layers: debug)" if args.layers else "")
+        "config": {"model": MODELS[args.model]["label"]
+                            + (f" ({args.layers} layers: debug)" if args.layers else "")
                             + (" (debug batch: labels/s not comparable)" if args.global_batch != 16 else ""),
-                   "global_batch": args.global_batch, "seq_len": 512, "grad_accum": 2, "optimizer": "adamw",
+                   "global_batch": args.global_batch, "seq_len": MODELS[args.model]["seq_len"],
+                   "grad_accum": 2, "optimizer": "adamw",
                    "parallelism": m["strategy"], "valid_labels_per_step": VALID_LABELS_PER_STEP,
                    "precision": "bf16 GEMM operands, fp32 accumulation; fp32 master shards, "
                                 "gradients and AdamW state; on the wire: " + wire +
@@ -295,7 +316,7 @@ def run_ours(args):
     }
     # the second strategy the headline metric names for this GPU count (F4T2/SP on 8, F2T2/SP on
     # 4, F1T2/SP on 2), same steps and warm-up; skipped when a strategy was asked for explicitly
-    hybrid = HYBRID.get(args.gpus)
+    hybrid = HYBRID.get(args.gpus) if args.model == "1.5b" else None
     if hybrid is not None and not args.strategy and not args.no_secondary:
         try:
             h = measure_ours(args, *hybrid)

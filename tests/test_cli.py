@@ -16,7 +16,7 @@ CONFIGS = ROOT / "configs"
 
 
 def test_every_preset_parses():
-    names = sorted(p.name for p in CONFIGS.glob("*.yaml") if p.name != "qwen25_1p5b_config.yaml")
+    names = sorted(p.name for p in CONFIGS.glob("*.yaml") if not p.name.endswith("_config.yaml"))
     assert {"qwen25_tiny.yaml", "qwen25_1p5b_b200.yaml", "correctness.yaml", "tp_sp.yaml",
             "runtime_cpu.yaml", "smoke_gloo.yaml"} <= set(names)
     for name in names:
@@ -28,6 +28,10 @@ def test_every_preset_parses():
     headline = load_config(CONFIGS / "qwen25_1p5b_b200.yaml")
     assert headline.parallel.strategy == "F8T1"
     assert headline.training.local_batch_size * headline.parallel.fsdp_degree == 8
+    large = load_config(CONFIGS / "qwen25_7b_b200.yaml")
+    large.validate(8, mode="runtime")
+    assert large.parallel.strategy == "F2T4/SP" and not large.model.tie_word_embeddings
+    assert large.training.local_batch_size * large.parallel.fsdp_degree * 2 == 16   # global batch
 
 
 def test_train_toy_reference_writes_step_rows(tmp_path):

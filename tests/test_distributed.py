@@ -71,6 +71,14 @@ def test_sharded_training_matches_dense(tmp_path, name, nproc, args):
         assert r["param_err"] < (2e-4 if adamw else 5e-6)
         assert r["shard_ok"] and r["live"] == 0
     assert_same_sequence_per_communicator(results, degree(args, "--fsdp"), degree(args, "--tp"))
+    # the offline auditor accepts the run's event logs (buffer lifetimes, collective order,
+    # per-step counts, policy edges, gradient-dispatch order, cross-rank sequences)
+    from shardtrain_b200.utils.audit import audit_event_logs
+
+    policy = args[args.index("--policy") + 1] if "--policy" in args else "conservative"
+    tied_model = not ("--tied" in args)
+    assert audit_event_logs(tmp_path, fsdp=degree(args, "--fsdp"), tp=degree(args, "--tp"), layers=2,
+                            tied=tied_model, policy=policy) == []
     first = results[0]
     layers, steps = 2, 3
     micro = 2 if "--accum" in args else 1
