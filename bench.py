@@ -55,6 +55,8 @@ def parse_args():
                     help="pull q|k|v and gate|up inside the forward GEMMs (FSDP degree > 1)")
     ap.add_argument("--no-seq-pull", action="store_true",
                     help="sequence parallel: gather kernel + GEMM instead of the pulling GEMM")
+    ap.add_argument("--nvls", default="off", choices=["auto", "off"],
+                    help="FSDP-only meshes: reduce gradients in the NVSwitch (multimem.ld_reduce)")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the second (hybrid TP/SP) strategy that follows the F{N}T1 pass")
     return ap.parse_args()
@@ -135,7 +137,7 @@ def qwen15b_dict(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
                         communication_backend=args.backend, retain_parameters=bool(args.retain),
                         fused_allgather=args.fused_allgather,
                         wire_dtype="fp32" if args.fp32_wire else "bf16",
-                        fused_seq_gather=not args.no_seq_pull),
+                        fused_seq_gather=not args.no_seq_pull, nvls=args.nvls),
         "training": dict(dtype="bf16", optimizer="adamw", lr=1e-5, steps=args.steps,
                          local_batch_size=args.global_batch // fsdp // 2, accumulation_steps=2,
                          seed=1234),
@@ -191,7 +193,7 @@ def measure_ours(args, fsdp, tp, sp):
             communication_backend=rc.communication_backend, retain_parameters=rc.retain_parameters,
             compute_dtype="bf16", device_wait_seconds=config.debug.distributed_timeout_seconds,
             wire_dtype=rc.wire_dtype, fused_allgather=rc.fused_allgather,
-            fused_seq_gather=rc.fused_seq_gather,
+            fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls,
         ).register(model, mesh if session.worker.launched else None, sp=sp)
         trainer = QwenTrainer(model, runtime, config.training.lr, dtype="bf16", optimizer="adamw",
                               accumulation_steps=config.training.accumulation_steps)
@@ -257,6 +259,7 @@ def measure_ours(args, fsdp, tp, sp):
             h2d=host_ids.numel() * host_ids.element_size() * fsdp,
             peak=torch.cuda.max_memory_allocated(device) / 2**30,
             executor=runtime.executor.name,
+            nvls=bool(getattr(runtime.fused, "nvls_active", False)),
             switches={"reshard_after_forward": rc.reshard_after_forward,
                       "forward_prefetch": rc.forward_prefetch,
                       "backward_prefetch": rc.backward_prefetch,
@@ -301,7 +304,7 @@ def run_ours(args):
                    "inputs": "token ids + all-ones attention_mask + position_ids, as the "
                              "reference benchmark passes them",
                    "runtime": {**m["switches"], "executor": m["executor"],
-                               "fused_allgather": args.fused_allgather},
+                               "fused_allgather": args.fused_allgather, "nvls": m["nvls"]},
                    "l2": "no explicit flush: each step streams >6 GB of parameters, "
                          "gradients and optimizer state per GPU group, far above the 126 MB L2"},
         "clocks": m["clocks"],

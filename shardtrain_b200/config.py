@@ -2,14 +2,15 @@
 
 The schema (section names, field names, defaults, override syntax `--section.field value`) is the
 one of the reference's `src/sharded_runtime/config.py:17-268`, so its YAML presets load unchanged.
-The validation rules are stated as a table of checks instead of a chain of `if`s.  Five optional
+The validation rules are stated as a table of checks instead of a chain of `if`s.  Six optional
 runtime fields are new and default to the reference behaviour: `communication_backend`
 ("auto" | "peer" | "nccl") selects the NVLink peer-memory kernels or the NCCL baseline path,
 `retain_parameters` keeps the gathered compute-dtype parameters for the whole optimizer step,
 `fused_allgather` ("auto" | "on" | "off") lets a decoder layer's forward GEMMs pull q|k|v and
 gate|up from the owning ranks' shards instead of gathering them first, `wire_dtype`
 ("bf16" | "fp32") picks what the parameter gather moves over NVLink, and `fused_seq_gather`
-lets the GEMM that consumes a sequence all-gather pull the peers' slices itself.
+lets the GEMM that consumes a sequence all-gather pull the peers' slices itself; `nvls`
+("auto" | "off") allows the gradient reduce-scatter of FSDP-only meshes to run inside the NVSwitch.
 
 This module never imports torch.
 """
@@ -79,6 +80,7 @@ class RuntimeConfig:
     fused_allgather: str = "auto"
     wire_dtype: str = "bf16"
     fused_seq_gather: bool = True
+    nvls: str = "off"
 
 
 @dataclass(frozen=True)
@@ -277,6 +279,10 @@ class Config:
             (
                 lambda: r.wire_dtype in {"bf16", "fp32"},
                 "runtime.wire_dtype must be bf16 or fp32",
+            ),
+            (
+                lambda: r.nvls in {"auto", "off"},
+                "runtime.nvls must be auto or off",
             ),
         ]
 

@@ -138,7 +138,8 @@ cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
                                         int* flags, cudaStream_t s, TpAxis tp = TpAxis{},
-                                        const int* status = nullptr);
+                                        const int* status = nullptr,
+                                        const float* multicast = nullptr);
 // Same, and applies AdamW to the owned shard in the same pass (last micro-step only).
 // `flags` (optional, int[2]) receives the gradient check of what was written: [0] non-finite
 // value, [1] non-zero shard padding.
@@ -148,7 +149,13 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
                                         cudaStream_t s, TpAxis tp = TpAxis{},
                                         void* shadow = nullptr,    // bf16 copy of p, same offsets
-                                        const int* status = nullptr);
+                                        const int* status = nullptr,
+                                        const float* multicast = nullptr);
+// `multicast` (both reductions, optional): NVLS multicast address of the gradient slots whose
+// unicast addresses `full_grads` lists (memory bound to an NVLink multicast object spanning
+// exactly the `degree` FSDP members).  TP-split parameters are then summed by the switch
+// (`multimem.ld_reduce`, 16 bytes at a time); TP-replicated parameters, unaligned tails and
+// everything else keep the fixed-order peer loads.
 // `status` (both reductions): when the word already holds a failure code on entry the kernel
 // returns without touching gradients or parameters (the data it would reduce may be stale).
 // ------------------------------------------------------------------ all-gather -> GEMM (gemm_allgather_sm100.cu)
@@ -221,7 +228,15 @@ struct AttnCall {
   const uint8_t* key_mask;  // optional [B, S] (1 = attend)
   int batch, seq, hq, hkv;
   float scale;
+  // Optional packed form of the key mask (takes precedence over key_mask): bit i of word w of
+  // sample b is key 32 w + i; `key_bits_pitch` words per sample (a multiple of 4, at least four
+  // per 128-key block; 16-byte aligned).  Written by launch_pack_key_mask, once per batch
+  // instead of one byte load per key, block and query row.
+  const uint32_t* key_bits;
+  int key_bits_pitch;
 };
+cudaError_t launch_pack_key_mask(const uint8_t* mask, uint32_t* bits, int batch, int seq, int pitch,
+                                 cudaStream_t s);
 cudaError_t launch_attention_fwd(const AttnCall& c, int* status, cudaStream_t s);
 struct AttnBwdCall {
   const void* qkv;
@@ -238,6 +253,8 @@ struct AttnBwdCall {
   const uint8_t* key_mask;
   int batch, seq, hq, hkv;
   float scale;
+  const uint32_t* key_bits;   // as in AttnCall
+  int key_bits_pitch;
 };
 cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t s);
 int attention_bwd_parts(int batch, int seq, int hq, int hkv);

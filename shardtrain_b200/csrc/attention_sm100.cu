@@ -71,7 +71,31 @@ struct FwdParams {
   int batch, seq, hq, hkv;
   float scale;
   int* status;
+  const uint32_t* key_bits;   // packed key mask (bit i of word w = key 32 w + i), see pack_key_mask
+  int bits_pitch;             // words per sample, a multiple of 4
 };
+
+// The 128 mask bits of key block j of sample b; all ones without a mask.  With a byte mask the
+// bits are assembled on the fly (slow path kept for callers that did not pack the mask).
+__device__ __forceinline__ void load_key_bits(const uint32_t* bits, int pitch, const uint8_t* bytes,
+                                              int seq, int b, int j, uint32_t (&w)[4]) {
+  if (bits != nullptr) {
+    const uint4 v = *reinterpret_cast<const uint4*>(bits + static_cast<int64_t>(b) * pitch + j * 4);
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else if (bytes != nullptr) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t word = 0;
+      for (int i = 0; i < 32; ++i) {
+        const int kv = j * 128 + c * 32 + i;
+        word |= (kv < seq && bytes[static_cast<int64_t>(b) * seq + kv] != 0) ? (1u << i) : 0u;
+      }
+      w[c] = word;
+    }
+  } else {
+    w[0] = w[1] = w[2] = w[3] = 0xffffffffu;
+  }
+}
 
 // smem: Q tile | K,V x 2 stages | P tile | barriers
 constexpr int kFwdSmem = kTile + 4 * kTile + kTile + 1024 + 256;
@@ -193,14 +217,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map, FwdParams p) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
       tmem_ld_wait();
-      const uint8_t* mask_row = p.key_mask != nullptr ? p.key_mask + b * p.seq : nullptr;
-      const bool plain = !diag && mask_row == nullptr;     // every key of the block is visible
+      // the block's 128 key-mask bits: one 16-byte load per thread (same address for the whole
+      // warp), and a block with every key visible takes the mask-free path
+      uint32_t mw[4];
+      load_key_bits(p.key_bits, p.bits_pitch, p.key_mask, p.seq, b, j, mw);
+      const bool all_on = (mw[0] & mw[1] & mw[2] & mw[3]) == 0xffffffffu;
+      const bool plain = !diag && all_on;     // every key of the block is visible
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 128; ++i) {
         const int kv = j * kBlk + i;
-        bool keep = plain || !diag || kv <= q_idx;
-        if (!plain && mask_row != nullptr && keep) keep = mask_row[min(kv, p.seq - 1)] != 0;
+        const bool keep = plain || ((!diag || kv <= q_idx) && ((mw[i >> 5] >> (i & 31)) & 1u));
         const float x = keep ? __uint_as_float(sv[i]) * p.scale : -INFINITY;
         sv[i] = __float_as_uint(x);
         mx = fmaxf(mx, x);
@@ -321,6 +348,8 @@ struct BwdParams {
   int* status;
   float* dkv_part;   // [parts, batch*seq, 2*hkv*128] fp32 partial dK|dV when the group is split
   int parts;         // CTAs sharing one kv head's query-head group (1: write bf16 directly)
+  const uint32_t* key_bits;
+  int bits_pitch;
 };
 
 // ---------------------------------------------------------------------------- dQ
@@ -418,6 +447,8 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap map_qkv,
       if (!ok) break;
       tc_fence_after_sync();
       const bool diag = (j == qb);
+      uint32_t mw[4];
+      load_key_bits(p.key_bits, p.bits_pitch, p.key_mask, p.seq, b, j, mw);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t s[32], d[32];
@@ -425,11 +456,11 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap map_qkv,
         tmem_ld_32x32(tdP + lane_base + c * 32, d);
         tmem_ld_wait();
         float ds[32];
+        const uint32_t word = mw[c];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int kv = j * kBlk + c * 32 + i;
-          bool keep = q_ok && (!diag || kv <= q_idx);
-          if (p.key_mask != nullptr && keep) keep = p.key_mask[b * p.seq + min(kv, p.seq - 1)] != 0;
+          const bool keep = q_ok && (!diag || kv <= q_idx) && ((word >> i) & 1u);
           const float pr = keep ? __expf(__uint_as_float(s[i]) * p.scale - lse) : 0.f;
           ds[i] = pr * (__uint_as_float(d[i]) - dlt) * p.scale;
         }
@@ -579,8 +610,11 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv,
     const int r = q * 32 + lane;              // key row inside the tile
     const int kv_idx = kb * kBlk + r;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
-    const bool kv_ok = kv_idx < p.seq &&
-                       (p.key_mask == nullptr || p.key_mask[b * p.seq + min(kv_idx, p.seq - 1)] != 0);
+    bool kv_ok = kv_idx < p.seq;
+    if (kv_ok && p.key_bits != nullptr)
+      kv_ok = (p.key_bits[static_cast<int64_t>(b) * p.bits_pitch + (kv_idx >> 5)] >> (kv_idx & 31)) & 1u;
+    else if (kv_ok && p.key_mask != nullptr)
+      kv_ok = p.key_mask[b * p.seq + kv_idx] != 0;
     bool ok = true;
     for (int t = 0; t < iters; ++t) {
       const int h = head0 + t / per_head;
@@ -726,8 +760,12 @@ cudaError_t launch_attention_fwd(const AttnCall& c, int* status, cudaStream_t s)
   if (!make_bf16_tensor_map(&map, c.qkv, rows, width, width, 64, kBlk)) return cudaErrorInvalidValue;
   static cudaError_t attr = opt_in_smem(attention_fwd_kernel, kFwdSmem);
   if (attr != cudaSuccess) return attr;
+  if (c.key_bits != nullptr &&
+      (c.key_bits_pitch < 4 * ((c.seq + kBlk - 1) / kBlk) || (c.key_bits_pitch % 4) ||
+       (reinterpret_cast<uintptr_t>(c.key_bits) & 15)))
+    return cudaErrorInvalidValue;
   FwdParams p{reinterpret_cast<__nv_bfloat16*>(c.out), c.lse, c.key_mask, c.batch, c.seq, c.hq,
-              c.hkv, c.scale, status};
+              c.hkv, c.scale, status, c.key_bits, c.key_bits_pitch};
   dim3 grid((c.seq + kBlk - 1) / kBlk, c.hq, c.batch);
   attention_fwd_kernel<<<grid, kThreads, kFwdSmem, s>>>(map, p);
   return cudaGetLastError();
@@ -757,8 +795,13 @@ cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t
     const int64_t need = static_cast<int64_t>(parts) * rows * 2 * c.hkv * kD;
     if (parts > 1 && c.dkv_accum_floats < need) return cudaErrorInvalidValue;
   }
+  if (c.key_bits != nullptr &&
+      (c.key_bits_pitch < 4 * nblk || (c.key_bits_pitch % 4) ||
+       (reinterpret_cast<uintptr_t>(c.key_bits) & 15)))
+    return cudaErrorInvalidValue;
   BwdParams p{c.lse, c.delta, reinterpret_cast<__nv_bfloat16*>(c.dqkv), c.key_mask, c.batch, c.seq,
-              c.hq, c.hkv, c.scale, status, parts > 1 ? c.dkv_accum : nullptr, parts};
+              c.hq, c.hkv, c.scale, status, parts > 1 ? c.dkv_accum : nullptr, parts,
+              c.key_bits, c.key_bits_pitch};
   attention_dkv_kernel<<<dim3(nblk, c.hkv * parts, c.batch), kThreads, kDkvSmem, s>>>(map_qkv,
                                                                                      map_do, p);
   attention_dq_kernel<<<dim3(nblk, c.hq, c.batch), kThreads, kDqSmem, s>>>(map_qkv, map_do, p);
@@ -768,6 +811,31 @@ cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t
     attention_dkv_finish_kernel<<<grid, 256, 0, s>>>(c.dkv_accum, parts, rows, c.hq, c.hkv,
                                                      reinterpret_cast<__nv_bfloat16*>(c.dqkv));
   }
+  return cudaGetLastError();
+}
+
+namespace {
+// bits[b, w] bit i = (mask[b, 32 w + i] != 0); words beyond the sequence are zero
+__global__ void pack_key_mask_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ bits,
+                                     int batch, int seq, int pitch) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= batch * pitch) return;
+  const int b = idx / pitch, w = idx - b * pitch;
+  uint32_t word = 0;
+  for (int i = 0; i < 32; ++i) {
+    const int kv = w * 32 + i;
+    if (kv < seq && mask[static_cast<int64_t>(b) * seq + kv] != 0) word |= 1u << i;
+  }
+  bits[idx] = word;
+}
+}  // namespace
+
+cudaError_t launch_pack_key_mask(const uint8_t* mask, uint32_t* bits, int batch, int seq, int pitch,
+                                 cudaStream_t s) {
+  if (batch < 1 || seq < 1 || pitch < 4 * ((seq + kBlk - 1) / kBlk) || (pitch % 4))
+    return cudaErrorInvalidValue;
+  const int total = batch * pitch;
+  pack_key_mask_kernel<<<(total + 127) / 128, 128, 0, s>>>(mask, bits, batch, seq, pitch);
   return cudaGetLastError();
 }
 

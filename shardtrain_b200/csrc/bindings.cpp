@@ -517,7 +517,7 @@ stb::TpAxis tp_axis(c10::ArrayRef<int64_t> full_ptrs, int64_t tp_degree, int64_t
 void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor& segs,
                     Tensor grad_shard, double scale, bool accumulate,
                     const c10::optional<Tensor>& flags, int64_t tp_degree, int64_t tp_rank,
-                    double rep_scale) {
+                    double rep_scale, int64_t multicast_ptr) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
   const auto tp = tp_axis(full_ptrs, tp_degree, tp_rank, rep_scale);
@@ -527,7 +527,8 @@ void reduce_scatter(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const Tensor
                                            static_cast<int>(rank), table.data() + i, n,
                                            grad_shard.data_ptr<float>(), grad_shard.numel(),
                                            static_cast<float>(scale), accumulate, flags_ptr(flags),
-                                           cur_stream(), tp, status_ptr()),
+                                           cur_stream(), tp, status_ptr(),
+                                           reinterpret_cast<const float*>(multicast_ptr)),
           "reduce_scatter");
   }
 }
@@ -537,7 +538,8 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
                           bool accumulate, double lr, double b1, double b2, double eps, double wd,
                           double bc1, double bc2, double gscale,
                           const c10::optional<Tensor>& flags, int64_t tp_degree, int64_t tp_rank,
-                          double rep_scale, const c10::optional<Tensor>& shadow) {
+                          double rep_scale, const c10::optional<Tensor>& shadow,
+                          int64_t multicast_ptr) {
   auto table = read_segs(segs);
   const auto pp = peer_ptrs(full_ptrs);
   const auto tp = tp_axis(full_ptrs, tp_degree, tp_rank, rep_scale);
@@ -555,7 +557,7 @@ void reduce_scatter_adamw(c10::ArrayRef<int64_t> full_ptrs, int64_t rank, const 
               m.data_ptr<float>(), v.data_ptr<float>(), grad_shard.numel(),
               static_cast<float>(scale), accumulate,
               adam_args(lr, b1, b2, eps, wd, bc1, bc2, gscale), flags_ptr(flags), cur_stream(), tp,
-              shadow_ptr, status_ptr()),
+              shadow_ptr, status_ptr(), reinterpret_cast<const float*>(multicast_ptr)),
           "reduce_scatter_adamw");
   }
 }
@@ -742,6 +744,36 @@ Tensor tensor_from_ptr(int64_t ptr, int64_t numel, int64_t dtype_code) {
 }
 
 #ifdef STB_WITH_ATTENTION
+// bits[b, w] bit i = (mask[b, 32 w + i] != 0); `bits` is int32 [B, pitch], pitch a multiple of 4
+// with at least four words per 128-key block.
+void pack_key_mask(const Tensor& mask, Tensor bits) {
+  need(mask, at::kByte, "mask");
+  need(bits, at::kInt, "bits");
+  TORCH_CHECK(mask.dim() == 2 && bits.dim() == 2 && mask.is_contiguous() && bits.is_contiguous() &&
+                  mask.size(0) == bits.size(0), "pack_key_mask: [B, S] uint8 -> [B, pitch] int32");
+  check(stb::launch_pack_key_mask(mask.data_ptr<uint8_t>(),
+                                  reinterpret_cast<uint32_t*>(bits.data_ptr<int>()),
+                                  static_cast<int>(mask.size(0)), static_cast<int>(mask.size(1)),
+                                  static_cast<int>(bits.size(1)), cur_stream()),
+        "pack_key_mask");
+}
+
+// `mask`: uint8 [B, S] key mask, or its packed int32 form (pack_key_mask)
+void set_mask(const c10::optional<Tensor>& mask, const uint8_t** bytes, const uint32_t** bits,
+              int* pitch) {
+  *bytes = nullptr;
+  *bits = nullptr;
+  *pitch = 0;
+  if (!mask.has_value()) return;
+  if (mask->scalar_type() == at::kInt) {
+    TORCH_CHECK(mask->dim() == 2 && mask->is_contiguous(), "packed key mask must be [B, words]");
+    *bits = reinterpret_cast<const uint32_t*>(mask->data_ptr<int>());
+    *pitch = static_cast<int>(mask->size(1));
+  } else {
+    *bytes = mask->data_ptr<uint8_t>();
+  }
+}
+
 void attention_fwd(const Tensor& qkv, Tensor out, Tensor lse, const c10::optional<Tensor>& mask,
                    int64_t batch, int64_t seq, int64_t hq, int64_t hkv, double scale) {
   need(qkv, at::kBFloat16, "qkv");
@@ -751,7 +783,7 @@ void attention_fwd(const Tensor& qkv, Tensor out, Tensor lse, const c10::optiona
   c.qkv = qkv.data_ptr();
   c.out = out.data_ptr();
   c.lse = lse.data_ptr<float>();
-  c.key_mask = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  set_mask(mask, &c.key_mask, &c.key_bits, &c.key_bits_pitch);
   c.batch = static_cast<int>(batch);
   c.seq = static_cast<int>(seq);
   c.hq = static_cast<int>(hq);
@@ -778,7 +810,7 @@ void attention_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, con
                      dkv_accum.numel() >= need;
   c.dkv_accum = split ? dkv_accum.data_ptr<float>() : nullptr;
   c.dkv_accum_floats = split ? dkv_accum.numel() : 0;
-  c.key_mask = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  set_mask(mask, &c.key_mask, &c.key_bits, &c.key_bits_pitch);
   c.batch = static_cast<int>(batch);
   c.seq = static_cast<int>(seq);
   c.hq = static_cast<int>(hq);
@@ -822,12 +854,13 @@ TORCH_LIBRARY(stb, m) {
         "int[] shadow_ptrs=[]) -> ()",
         &gather_params);
   m.def("reduce_scatter(int[] full_ptrs, int rank, Tensor segs, Tensor grad_shard, float scale, "
-        "bool accumulate, Tensor? flags, int tp_degree=1, int tp_rank=0, float rep_scale=1.0) -> ()",
+        "bool accumulate, Tensor? flags, int tp_degree=1, int tp_rank=0, float rep_scale=1.0, "
+        "int multicast_ptr=0) -> ()",
         &reduce_scatter);
   m.def("reduce_scatter_adamw(int[] full_ptrs, int rank, Tensor segs, Tensor grad_shard, Tensor p, "
         "Tensor m, Tensor v, float scale, bool accumulate, float lr, float b1, float b2, float eps, "
         "float wd, float bc1, float bc2, float gscale, Tensor? flags, int tp_degree=1, "
-        "int tp_rank=0, float rep_scale=1.0, Tensor? shadow=None) -> ()",
+        "int tp_rank=0, float rep_scale=1.0, Tensor? shadow=None, int multicast_ptr=0) -> ()",
         &reduce_scatter_adamw);
   m.def("gemm_allgather(Tensor a, Tensor out, Tensor? bias, int[] arena_ptrs, bool wire_fp32, "
         "Tensor segs, Tensor? full, Tensor? gated_out, int force_bn=0) -> ()",
@@ -846,6 +879,7 @@ TORCH_LIBRARY(stb, m) {
   m.def("ipc_close", &ipc_close);
   m.def("tensor_from_ptr", &tensor_from_ptr);
 #ifdef STB_WITH_ATTENTION
+  m.def("pack_key_mask", &pack_key_mask);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
 #endif

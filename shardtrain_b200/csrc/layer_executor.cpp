@@ -22,6 +22,24 @@ void ok(cudaError_t e, const char* what) {
   TORCH_CHECK(e == cudaSuccess, "shardtrain_b200 layer executor: ", what, ": ", cudaGetErrorString(e));
 }
 
+// The key mask of a layer call: a uint8 [B, S] tensor, or (faster) its packed int32 [B, pitch]
+// form with one bit per key (ops.pack_key_mask).
+struct MaskView {
+  const uint8_t* bytes = nullptr;
+  const uint32_t* bits = nullptr;
+  int pitch = 0;
+  explicit MaskView(const c10::optional<at::Tensor>& mask) {
+    if (!mask.has_value()) return;
+    if (mask->scalar_type() == at::kInt) {
+      TORCH_CHECK(mask->dim() == 2 && mask->is_contiguous(), "packed key mask must be [B, words]");
+      bits = reinterpret_cast<const uint32_t*>(mask->data_ptr<int>());
+      pitch = static_cast<int>(mask->size(1));
+    } else {
+      bytes = mask->data_ptr<uint8_t>();
+    }
+  }
+};
+
 // Optional "pull the weights inside the GEMM" plan of a layer forward: the FSDP ranks' arenas
 // and, for q|k|v and gate|up, the rows of the unit's gather table that describe those parameters.
 // Empty `arenas`: the weights were gathered beforehand and the plain GEMMs run.
@@ -271,7 +289,8 @@ std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const T
   cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
   Gemm g{st, status.data_ptr<int>()};
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
-  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const MaskView mv(mask);
+  const uint8_t* km = mv.bytes;
 
   Tensor h1 = at::empty({M, H}, bf), inv1 = at::empty({M}, f32);
   ok(stb::launch_rmsnorm_fwd(x2.data_ptr<float>(), ln1.data_ptr<float>(), h1.data_ptr(),
@@ -284,6 +303,8 @@ std::vector<Tensor> layer_forward(const Tensor& x2, const Tensor& w_qkv, const T
   stb::AttnCall ac{qkv.data_ptr(), attn.data_ptr(), lse.data_ptr<float>(), km, static_cast<int>(B),
                    static_cast<int>(S), static_cast<int>(hq), static_cast<int>(hkv),
                    static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)))};
+  ac.key_bits = mv.bits;
+  ac.key_bits_pitch = mv.pitch;
   ok(stb::launch_attention_fwd(ac, g.status, st), "attention_fwd");
   Tensor x_mid = at::empty({M, H}, f32);
   g.run(attn, w_o, x_mid, false, false, nullptr, &x2);
@@ -314,7 +335,8 @@ Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1,
   cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
   Gemm g{st, status.data_ptr<int>()};
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
-  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const MaskView mv(mask);
+  const uint8_t* km = mv.bytes;
   constexpr int kPartial = 592;
 
   Tensor d_out_b = at::empty({M, H}, bf);
@@ -353,6 +375,8 @@ Tensor layer_backward(const Tensor& d_out, const Tensor& x2, const Tensor& inv1,
   bc.dkv_accum = parts > 1 ? dkv_parts.data_ptr<float>() : nullptr;
   bc.dkv_accum_floats = parts > 1 ? dkv_parts.numel() : 0;
   bc.key_mask = km;
+  bc.key_bits = mv.bits;
+  bc.key_bits_pitch = mv.pitch;
   bc.batch = static_cast<int>(B);
   bc.seq = static_cast<int>(S);
   bc.hq = static_cast<int>(hq);
@@ -411,7 +435,8 @@ std::vector<Tensor> layer_forward_sp(
   Gemm g{st, status.data_ptr<int>()};
   SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
-  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const MaskView mv(mask);
+  const uint8_t* km = mv.bytes;
   const float feps = static_cast<float>(eps);
 
   Tensor inv1 = at::empty({Ml}, f32);
@@ -429,6 +454,8 @@ std::vector<Tensor> layer_forward_sp(
   stb::AttnCall ac{qkv.data_ptr(), attn.data_ptr(), lse.data_ptr<float>(), km, static_cast<int>(B),
                    static_cast<int>(S), static_cast<int>(hq), static_cast<int>(hkv),
                    static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)))};
+  ac.key_bits = mv.bits;
+  ac.key_bits_pitch = mv.pitch;
   ok(stb::launch_attention_fwd(ac, g.status, st), "attention_fwd");
   g.scatter(attn, w_o, false, push_ptrs, static_cast<int>(S));
   sp.barrier();                                   // every rank's partial rows have landed
@@ -474,7 +501,8 @@ Tensor layer_backward_sp(
   Gemm g{st, status.data_ptr<int>()};
   SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
-  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const MaskView mv(mask);
+  const uint8_t* km = mv.bytes;
   constexpr int kPartial = 592;
 
   ok(stb::launch_cast_f32_to_bf16(d_out.data_ptr<float>(), dob_local.data_ptr(), Ml * H, st), "cast");
@@ -532,6 +560,8 @@ Tensor layer_backward_sp(
   bc.dkv_accum = parts > 1 ? dkv_parts.data_ptr<float>() : nullptr;
   bc.dkv_accum_floats = parts > 1 ? dkv_parts.numel() : 0;
   bc.key_mask = km;
+  bc.key_bits = mv.bits;
+  bc.key_bits_pitch = mv.pitch;
   bc.batch = static_cast<int>(B);
   bc.seq = static_cast<int>(S);
   bc.hq = static_cast<int>(hq);
@@ -591,7 +621,8 @@ std::vector<Tensor> layer_forward_tp(
   Gemm g{st, status.data_ptr<int>()};
   SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
-  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const MaskView mv(mask);
+  const uint8_t* km = mv.bytes;
   const float feps = static_cast<float>(eps);
 
   Tensor h1 = at::empty({M, H}, bf), inv1 = at::empty({M}, f32);
@@ -605,6 +636,8 @@ std::vector<Tensor> layer_forward_tp(
   stb::AttnCall ac{qkv.data_ptr(), attn.data_ptr(), lse.data_ptr<float>(), km, static_cast<int>(B),
                    static_cast<int>(S), static_cast<int>(hq), static_cast<int>(hkv),
                    static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)))};
+  ac.key_bits = mv.bits;
+  ac.key_bits_pitch = mv.pitch;
   ok(stb::launch_attention_fwd(ac, g.status, st), "attention_fwd");
   g.broadcast(attn, w_o, false, push_a);
   sp.barrier();
@@ -645,7 +678,8 @@ Tensor layer_backward_tp(
   Gemm g{st, status.data_ptr<int>()};
   SpLink sp = make_link(st, g.status, flag_ptrs, tp_rank, epoch, flag_slot, wait_us);
   const int* pos = positions.has_value() ? positions->data_ptr<int>() : nullptr;
-  const uint8_t* km = mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr;
+  const MaskView mv(mask);
+  const uint8_t* km = mv.bytes;
   constexpr int kPartial = 592;
 
   Tensor d_out_b = at::empty({M, H}, bf);
@@ -688,6 +722,8 @@ Tensor layer_backward_tp(
   bc.dkv_accum = parts > 1 ? dkv_parts.data_ptr<float>() : nullptr;
   bc.dkv_accum_floats = parts > 1 ? dkv_parts.numel() : 0;
   bc.key_mask = km;
+  bc.key_bits = mv.bits;
+  bc.key_bits_pitch = mv.pitch;
   bc.batch = static_cast<int>(B);
   bc.seq = static_cast<int>(S);
   bc.hq = static_cast<int>(hq);

@@ -3,7 +3,9 @@
 //   * parameter all-gather + copy-out + fp32->bf16 cast  (src/sharded_runtime/runtime/materializer.py:31-114,
 //     src/sharded_runtime/runtime/layout.py:77-90)
 //   * gradient pack + reduce-scatter + 1/F scale + accumulate (+ AdamW)  (materializer.py:116-192,
-//     layout.py:93-106, src/sharded_runtime/training/qwen2_trainer.py:48)
+//     layout.py:93-106, src/sharded_runtime/training/qwen2_trainer.py:48); with a multicast
+//     address of the gradient slots the sum over the FSDP members is one `multimem.ld_reduce`
+//     per 16 bytes, carried out inside the NVSwitch
 //   * sequence-parallel activation gather / reduce-scatter (src/sharded_runtime/runtime/comm.py:781-884)
 //   * embedding rows fetched from the owning shard without gathering the table.
 // With degree 1 the same kernels read only local memory.  No kernel here waits on another GPU
@@ -166,7 +168,8 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int t
                                       float* __restrict__ p, float* __restrict__ m,
                                       float* __restrict__ v, float split_scale, float rep_scale,
                                       int accumulate, AdamWArgs a, int* __restrict__ flags,
-                                      __nv_bfloat16* __restrict__ shadow, const int* status) {
+                                      __nv_bfloat16* __restrict__ shadow, const int* status,
+                                      const float* __restrict__ multicast) {
   // A failure recorded earlier (a peer that never signalled) means the slots may hold stale
   // data: neither the gradient shard nor, with ADAMW, the parameters are touched.
   if (kernel_should_skip(status)) return;
@@ -194,7 +197,17 @@ __global__ void reduce_scatter_kernel(PeerPtrs full, int degree, int rank, int t
     for (int64_t i = base + threadIdx.x * step; i < end; i += blockDim.x * step) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       const int cnt = vec ? 4 : 1;
-      if (vec && i + 3 < valid) {
+      if (vec && i + 3 < valid && multicast != nullptr && !replicated) {
+        // NVLS: one load through the multicast address of the gradient slot; the NVSwitch reads
+        // the same 16 bytes of every member's slot, adds them and returns the sum, so only
+        // 1 / F of the gradient enters this GPU instead of (F - 1) / F
+        float4 t;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w)
+                     : "l"(multicast + sg.full_off + lo + i)
+                     : "memory");
+        acc[0] = t.x; acc[1] = t.y; acc[2] = t.z; acc[3] = t.w;
+      } else if (vec && i + 3 < valid) {
         // rotate the peer order by rank so the ranks do not all hit one peer at once
         for (int d = 0; d < n_src; ++d) {
           const int src = ((first + d) % n_src) * stride + offset;
@@ -509,15 +522,18 @@ bool valid_mesh(int degree, int rank, TpAxis tp) {
 cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int rank,
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         int64_t shard_total, float scale, bool accumulate,
-                                        int* flags, cudaStream_t s, TpAxis tp, const int* status) {
+                                        int* flags, cudaStream_t s, TpAxis tp, const int* status,
+                                        const float* multicast) {
   (void)shard_total;
   SegTable tab;
-  if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
+  if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs) ||
+      (reinterpret_cast<uintptr_t>(multicast) & 15))
     return cudaErrorInvalidValue;
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<false><<<grid, 256, 0, s>>>(
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, nullptr, nullptr, nullptr,
-      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags, nullptr, status);
+      scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags, nullptr, status,
+      multicast);
   return cudaGetLastError();
 }
 
@@ -525,16 +541,18 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
                                         const SegmentDesc* segs, int n_segs, float* grad_shard,
                                         float* p, float* m, float* v, int64_t shard_total,
                                         float scale, bool accumulate, AdamWArgs a, int* flags,
-                                        cudaStream_t s, TpAxis tp, void* shadow, const int* status) {
+                                        cudaStream_t s, TpAxis tp, void* shadow, const int* status,
+                                        const float* multicast) {
   (void)shard_total;
   SegTable tab;
-  if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs))
+  if (!valid_mesh(degree, rank, tp) || !fill_table(&tab, segs, n_segs) ||
+      (reinterpret_cast<uintptr_t>(multicast) & 15))
     return cudaErrorInvalidValue;
   dim3 grid(chunks_for(segs, n_segs, true), n_segs);
   reduce_scatter_kernel<true><<<grid, 256, 0, s>>>(
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, p, m, v, scale,
       tp.replicated_scale, accumulate ? 1 : 0, a, flags,
-      reinterpret_cast<__nv_bfloat16*>(shadow), status);
+      reinterpret_cast<__nv_bfloat16*>(shadow), status, multicast);
   return cudaGetLastError();
 }
 

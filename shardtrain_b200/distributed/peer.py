@@ -42,6 +42,7 @@ class PeerBuffer:
     ptrs: list[int]          # one device pointer per group member, index = group rank
     nbytes: int
     owner: object = None     # keeps an ordinary tensor alive in the single-member case
+    multicast_ptr: int = 0   # NVLS: one address that reaches every member's copy (0 = none)
 
     def tensor(self, ops, numel: int, dtype=torch.float32, offset_bytes: int = 0) -> torch.Tensor:
         return ops.tensor_from_ptr(self.local_ptr + offset_bytes, numel, _DTYPE_CODE[dtype])
@@ -63,6 +64,8 @@ class PeerMemory:
         self.epochs = {name: 0 for name in CHANNEL_SLOTS}
         self._allocations: list[PeerBuffer] = []
         self._opened: list[int] = []
+        self._multicast: list[PeerBuffer] = []    # kept until process exit (see alloc_multicast)
+        self.multicast_refusal = None
         self.flags = self.alloc(4096) if self.degree > 1 else None
         # inbox of the small all-reduce: [2 parities][8 senders][METRIC_WIDTH] doubles
         self.inbox = self.alloc(2 * 8 * METRIC_WIDTH * 8) if self.degree > 1 else None
@@ -88,6 +91,41 @@ class PeerMemory:
                 ptrs.append(opened)
         buf = PeerBuffer(local, ptrs, nbytes)
         self._allocations.append(buf)
+        return buf
+
+    def alloc_multicast(self, nbytes: int) -> PeerBuffer:
+        """Like `alloc`, for buffers that kernels also address through NVLS (`multimem.*`): the
+        memory comes from torch's symmetric-memory allocator, which binds it to an NVLink
+        multicast object spanning the group when the driver and the fabric allow it.  When they
+        do not (no NVSwitch, multicast refused, symmetric memory unavailable) this silently
+        returns an ordinary peer buffer with `multicast_ptr == 0`, and callers keep to plain
+        peer loads.  The tensor is never returned to torch before process exit."""
+        if self.degree == 1:
+            return self.alloc(nbytes)
+        nbytes = -(-int(nbytes) // 512) * 512
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            tensor = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            handle = symm_mem.rendezvous(tensor, self.group)
+            multicast = int(handle.multicast_ptr)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            if not multicast or len(ptrs) != self.degree:
+                raise RuntimeError("no multicast address")
+        except Exception as exc:  # noqa: BLE001 - any refusal means: plain peer memory
+            self.multicast_refusal = f"{type(exc).__name__}: {exc}"
+            # every member must take the same branch: agree on the outcome
+            verdicts: list = [None] * self.degree
+            dist.all_gather_object(verdicts, False, group=self.group)
+            return self.alloc(nbytes)
+        verdicts = [None] * self.degree
+        dist.all_gather_object(verdicts, True, group=self.group)
+        if not all(verdicts):
+            return self.alloc(nbytes)
+        tensor.zero_()
+        buf = PeerBuffer(ptrs[self.rank], ptrs, nbytes, owner=(tensor, handle),
+                         multicast_ptr=multicast)
+        self._multicast.append(buf)
         return buf
 
     def barrier(self, channel: str) -> None:

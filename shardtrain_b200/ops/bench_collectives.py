@@ -135,13 +135,13 @@ def sweep_fa(ops, peer, timer, sizes_mb, tflops, emit):
         del shard, shadow
 
 
-def sweep_fb(ops, peer, timer, sizes_mb, tflops, emit):
+def sweep_fb(ops, peer, timer, sizes_mb, tflops, emit, nvls=False):
     """Gradient reduce-scatter fused with accumulate + AdamW."""
     F, rank, dev = peer.degree, peer.rank, peer.device
     for size_mb in sizes_mb:
         numel = max(F * 4, (size_mb * MB // 4) // (F * 4) * (F * 4))
         q = numel // F
-        slot = peer.alloc(numel * 4)
+        slot = peer.alloc_multicast(numel * 4) if nvls else peer.alloc(numel * 4)
         grads = slot.tensor(ops, numel) if F > 1 else slot.owner.view(torch.float32)[:numel]
         grads.normal_()
         table = torch.tensor([[0, q, numel, 0, 0]], dtype=torch.int64)
@@ -151,10 +151,11 @@ def sweep_fb(ops, peer, timer, sizes_mb, tflops, emit):
         flags = torch.zeros(2, device=dev, dtype=torch.int32)
         torch.cuda.synchronize(dev)
 
-        def ours():
+        def ours(multicast=0):
             peer.barrier("fsdp_rs")
             ops.reduce_scatter_adamw(slot.ptrs, rank, table, g, p, m, v, 1.0 / F, False, 1e-5, 0.9,
-                                     0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, flags, 1, 0, 1.0, shadow)
+                                     0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, flags, 1, 0, 1.0, shadow,
+                                     multicast)
 
         leaf = torch.nn.Parameter(torch.randn(q, device=dev))
         leaf.grad = torch.zeros(q, device=dev)
@@ -170,12 +171,25 @@ def sweep_fb(ops, peer, timer, sizes_mb, tflops, emit):
             opt.step()
 
         t_ours, t_nccl = timer(ours), timer(nccl)
+        t_nvls = None
+        if slot.multicast_ptr:
+            # same reduction through the switch; the two must agree to fp32 summation order
+            p_ref = p.clone()
+            ours()
+            after_p2p = g.clone()
+            p.copy_(p_ref)
+            ours(slot.multicast_ptr)
+            torch.cuda.synchronize(dev)
+            nvls_err = ((g - after_p2p).abs().max() / after_p2p.abs().max().clamp_min(1e-12)).item()
+            t_nvls = timer(lambda: ours(slot.multicast_ptr))
         link = q * 4 * (F - 1)                    # this rank's slice pulled from every peer
         hbm = q * 4 * (F + 8) + q * 2             # slots read; g, p, m, v read + written; shadow
         floor = max(link / (NVLINK_GBS * 1e9), hbm / 6.5e12) * 1e6
         emit(dict(sweep="fb_reduce_scatter_adamw", unit_mb_fp32=size_mb, numel=numel, ranks=F,
                   fused_us=t_ours, nccl_adamw_us=t_nccl, floor_us=floor, frac=floor / t_ours,
-                  vs_nccl=t_nccl / t_ours, link_gbs=link / t_ours / 1e3))
+                  vs_nccl=t_nccl / t_ours, link_gbs=link / t_ours / 1e3,
+                  fused_nvls_us=t_nvls if t_nvls is not None else "n/a",
+                  nvls_vs_p2p_max_rel_diff=nvls_err if t_nvls is not None else "n/a"))
         del grads
 
 
@@ -258,6 +272,8 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--table", default="")
+    ap.add_argument("--nvls", action="store_true",
+                    help="fb: also time the reduction through the NVSwitch (multicast-bound slots)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -289,7 +305,7 @@ def main():
         if "fa" in which:
             sweep_fa(ops, peer, timer, sizes, tflops, emit)
         if "fb" in which:
-            sweep_fb(ops, peer, timer, sizes, tflops, emit)
+            sweep_fb(ops, peer, timer, sizes, tflops, emit, nvls=a.nvls)
         if which & {"fc", "fd"}:
             sweep_fc_fd(ops, peer, timer, shapes, tflops, emit, which)
         torch.cuda.synchronize(device)

@@ -187,7 +187,11 @@ class UnitState:
         self.reductions += 1
         self.annotate("BWD")
         self.state = "GRAD_REDUCING"
-        self.runtime.comm.event("unit_grads_ready", parameters=[h.spec.param_id for h in self.handles])
+        comm = self.runtime.comm
+        if comm.diagnostics_enabled:
+            # the stream this node runs on: autograd replays the stream of the bridge's forward
+            comm.event("unit_grads_ready", parameters=[h.spec.param_id for h in self.handles],
+                       issue_stream=comm.stream_name())
         self.runtime.materializer.reduce(self, grads)
         if self.runtime.retain_parameters and not self.runtime.last_microstep:
             # parameters do not change between micro-steps: keep the gathered copy
@@ -229,7 +233,7 @@ class ShardedRuntime:
                  backward_prefetch=False, async_grad_rs=False, communication_policy="conservative",
                  directory=None, diagnostics_enabled=True, communication_backend="auto",
                  retain_parameters=False, compute_dtype=None, device_wait_seconds=2.0,
-                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=True):
+                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=True, nvls="off"):
         self.device = torch.device(device)
         self.reshard_after_forward = reshard_after_forward
         self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
@@ -256,6 +260,12 @@ class ShardedRuntime:
         # sm_100a, sequence parallel: the GEMM that consumes a sequence all-gather pulls the
         # peers' slices itself (one kernel) instead of running after a gather kernel
         self.fused_seq_gather = bool(fused_seq_gather)
+        # sm_100a, FSDP-only meshes: reduce gradients inside the NVSwitch (`multimem.ld_reduce`
+        # over multicast-bound gradient slots).  "auto": when the fabric grants multicast, else
+        # plain peer loads; "off": never bind memory to a multicast object.
+        if nvls not in ("auto", "off"):
+            raise ValueError("nvls must be auto or off")
+        self.nvls = nvls
         # time budget of every device-side wait on a peer (seconds; clamped by PeerMemory)
         self.device_wait_seconds = float(device_wait_seconds)
         rank = dist.get_rank() if dist.is_initialized() else 0

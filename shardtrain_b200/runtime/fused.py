@@ -135,8 +135,8 @@ def build_plan(unit) -> UnitPlan:
 
 
 class GradSlot:
-    def __init__(self, local, peer_ptrs):
-        self.local, self.peer_ptrs = local, peer_ptrs
+    def __init__(self, local, peer_ptrs, multicast_ptr=0):
+        self.local, self.peer_ptrs, self.multicast_ptr = local, peer_ptrs, multicast_ptr
         self.holder = None
         self.last_rs = -10
 
@@ -151,12 +151,15 @@ class GradRing:
     reduction n+1.
     """
 
-    def __init__(self, peer: PeerMemory, ops, numel: int, count: int = 4):
+    def __init__(self, peer: PeerMemory, ops, numel: int, count: int = 4, multicast: bool = False):
+        """`multicast`: ask for slots that are also reachable through an NVLS multicast address
+        (falls back to plain peer memory when the fabric refuses)."""
         self.slots = []
         for _ in range(count):
-            buf = peer.alloc(numel * 4)
+            buf = peer.alloc_multicast(numel * 4) if multicast else peer.alloc(numel * 4)
             self.slots.append(GradSlot(buf.tensor(ops, numel) if peer.degree > 1
-                                       else buf.owner.view(torch.float32)[:numel], buf.ptrs))
+                                       else buf.owner.view(torch.float32)[:numel], buf.ptrs,
+                                       buf.multicast_ptr))
         self.events: list = []      # events[n]: completion of reduction n on the rs stream
 
     def acquire(self, unit_id, stream):
@@ -212,6 +215,7 @@ class FusedExecutor:
         self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
         self.check_flags = self._flags   # written by every reduce-scatter kernel
         self._rope_cache = {}
+        self._mask_cache = {}
         self._scratch = {}
         self.token_grad = torch.zeros(1, dtype=torch.float32, device=runtime.device)
         self.rows_hint = None     # rows of the layer GEMMs' activation, known after the first input
@@ -289,7 +293,13 @@ class FusedExecutor:
             if len(unit.handles) > 64:
                 raise ValueError("A unit may hold at most 64 parameters")
             plan.tokens = tuple(token_pool[base + i: base + i + 1] for i in range(len(unit.handles)))
-        self.ring = GradRing(self.reduce_peer, self.ops, _up(largest, 4), count=4)
+        # NVLS reduce-scatter: only where the multicast group is exactly the FSDP group (no TP
+        # axis) -- with TP the slots are shared by the whole mesh and a multicast sum would add
+        # the other TP coordinates' gradients of TP-split parameters
+        want_nvls = (rt.nvls != "off" and self.tp_degree == 1 and self.peer.degree > 1)
+        self.ring = GradRing(self.reduce_peer, self.ops, _up(largest, 4), count=4,
+                             multicast=want_nvls)
+        self.nvls_active = all(slot.multicast_ptr for slot in self.ring.slots) and want_nvls
         mat.bind(self.ops, self)
         ranges = rt.padding_ranges or [(0, 0)]
         self._pad_ranges = torch.tensor(ranges, dtype=torch.int64, device=rt.device).reshape(-1)
@@ -472,6 +482,27 @@ class FusedExecutor:
             self._scratch[key] = t
         return t
 
+    def key_mask_bits(self, attention_mask):
+        """Packed form of a [batch, sequence] key mask (one bit per key, int32 [B, pitch]) for
+        the attention kernels.  Every layer of every micro-step of a step presents the same mask
+        tensor: the packing runs once per (tensor, version) instead of three small kernels per
+        layer call."""
+        if attention_mask.ndim != 2:
+            raise ValueError("The sm_100a attention kernel takes a [batch, sequence] key mask")
+        key = (attention_mask.data_ptr(), attention_mask._version, tuple(attention_mask.shape))
+        hit = self._mask_cache.get(key)
+        if hit is None:
+            if len(self._mask_cache) > 8:
+                self._mask_cache.clear()
+            batch, seq = attention_mask.shape
+            pitch = 4 * ((seq + 127) // 128)
+            bits = torch.empty((batch, pitch), dtype=torch.int32, device=self.runtime.device)
+            as_bytes = attention_mask.to(self.runtime.device).ne(0).to(torch.uint8).contiguous()
+            self.ops.pack_key_mask(as_bytes, bits)
+            # the entry keeps the caller's tensor alive: its address cannot be reused meanwhile
+            hit = self._mask_cache[key] = (bits, attention_mask)
+        return hit[0]
+
     def rotary(self, position_ids, default_positions):
         """cos/sin tables (FP32, [rows, D/2]) for the RoPE kernel and an optional int32 row index
         per (batch, token).  Default positions 0..S-1 and a caller-supplied [1, S] row share one
@@ -512,11 +543,7 @@ class FusedExecutor:
     def layer(self, unit, index, x, tables, attention_mask):
         plan = self.runtime.materializer.plans[unit.unit_id]
         weights = [unit.forward_weight(n) for n in plan.names]
-        mask = None
-        if attention_mask is not None:
-            if attention_mask.ndim != 2:
-                raise ValueError("The sm_100a attention kernel takes a [batch, sequence] key mask")
-            mask = attention_mask.to(self.runtime.device).ne(0).to(torch.uint8).contiguous()
+        mask = self.key_mask_bits(attention_mask) if attention_mask is not None else None
         return FusedLayerFn.apply(x, self, unit, index, tables, mask, *weights)
 
     def final_norm(self, unit, x):

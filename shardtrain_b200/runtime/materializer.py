@@ -337,6 +337,9 @@ class PeerMaterializer:
         replicated_scale = 1.0 / self.degree if runtime.sp else 1.0 / (self.degree * arenas.tp_degree)
         tp = (arenas.tp_degree, arenas.tp_rank, replicated_scale)
 
+        # NVLS: the switch adds the members' slots (only when the ring got multicast addresses)
+        multicast = slot.multicast_ptr if getattr(arenas, "nvls_active", False) else 0
+
         def launch():
             arenas.reduce_peer.barrier("fsdp_rs")     # no-op for a single member
             if fuse_adamw:
@@ -344,10 +347,11 @@ class PeerMaterializer:
                 self.ops.reduce_scatter_adamw(
                     slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad, arenas.param,
                     arenas.exp_avg, arenas.exp_avg_sq, 1.0 / self.degree, not first, *hp,
-                    arenas.check_flags, *tp, arenas.shadow)
+                    arenas.check_flags, *tp, arenas.shadow, multicast)
             else:
                 self.ops.reduce_scatter(slot.peer_ptrs, self.rank, plan.reduce_table, arenas.grad,
-                                        1.0 / self.degree, not first, arenas.check_flags, *tp)
+                                        1.0 / self.degree, not first, arenas.check_flags, *tp,
+                                        multicast)
 
         comm = self.comm
         ticket = comm.issue_kernel(

@@ -180,6 +180,18 @@ def test_attention_forward_backward(ops, B, S, hq, hkv, masked):
     torch.testing.assert_close(dqkv[edge].float(), want[edge], atol=6e-2, rtol=5e-2)
     if masked == "padded":
         assert not dqkv.view(B, S, -1)[1].any()
+    if masked:
+        # the packed form of the mask (one bit per key) drives the same kernels to the same bits
+        bits = torch.empty(B, 4 * ((S + 127) // 128), device=DEV, dtype=torch.int32)
+        ops.pack_key_mask(mask, bits)
+        out_b, lse_b = torch.zeros_like(out), torch.zeros_like(lse)
+        ops.attention_fwd(qkv, out_b, lse_b, bits, B, S, hq, hkv, scale)
+        assert torch.equal(out_b, out) and torch.equal(lse_b, lse)
+        dqkv_b = torch.zeros_like(dqkv)
+        ops.attention_bwd(qkv, out, dout, lse, delta, dqkv_b, delta, bits, B, S, hq, hkv, scale)
+        assert torch.equal(dqkv_b, dqkv)
+        word = bits.view(B, -1)[0, 0].item() & 0xFFFFFFFF
+        assert word == sum(int(mask[0, i].item() != 0) << i for i in range(32))
     # with a scratch large enough the query-head group is split over several dK/dV CTAs per kv
     # head and the fp32 partial planes are added in a fixed order: same result, twice
     scratch = torch.full(((hq // hkv) * B * S * 2 * hkv * D,), float("nan"), device=DEV)

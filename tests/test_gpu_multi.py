@@ -28,6 +28,8 @@ CASES = [
     ("fsdp2_pull", 2, ["--fsdp", 2, "--shape", "d128", "--fused-allgather", "on"]),
     ("fsdp2_pull_fp32_wire", 2, ["--fsdp", 2, "--shape", "d128", "--fused-allgather", "on",
                                  "--wire", "fp32"]),
+    # gradient reduce-scatter through the NVSwitch (multimem.ld_reduce); healthy run only
+    ("fsdp2_nvls", 2, ["--fsdp", 2, "--shape", "d128", "--nvls", "auto"]),
     ("fsdp2_tp2_sp_pull", 4, ["--fsdp", 2, "--tp", 2, "--sp", 1, "--shape", "d128tp",
                               "--fused-allgather", "on"]),
 ]
@@ -47,6 +49,8 @@ def test_fused_executor_matches_dense_on_a_mesh(tmp_path, name, ranks, mesh):
         for row in record["rows"]:
             assert abs(row["loss"] - row["ref"]) < 2e-3
         assert "fsdp_ag_cast" in record["kinds"]          # the peer-memory materialiser ran
+        if "--nvls" in mesh and not record["nvls"]:
+            pytest.skip(f"the fabric refused multicast: {record['nvls_refusal']}")
         if "--fused-allgather" in mesh:
             # the layers' forward gathers were partial: the GEMMs pulled the rest themselves
             assert record["kinds"].get("fsdp_ag_partial") == 3 * 2 * 2     # steps x micro x layers

@@ -221,3 +221,82 @@ def test_executor_selection_rules(monkeypatch, caplog):
 def test_runtime_rejects_an_unknown_compute_dtype():
     with pytest.raises(ValueError, match="compute_dtype"):
         ShardedRuntime(device="cpu", compute_dtype="int8")
+
+
+def _dispatch_fixture():
+    """Four bare units in the state the gradient-dispatch schedule expects when unit 3 (the last)
+    is reducing: unit 3 entered backward and seeded the gather of unit 2; units 0..2 wait."""
+    from shardtrain_b200.runtime.engine import UnitState
+    from shardtrain_b200.runtime.materializer import MaterializationLease
+
+    rt = ShardedRuntime(device="cpu", backward_prefetch=True, async_grad_rs=True,
+                        communication_policy="stream_ordered")
+    rt.sp = True
+    assert rt.gradient_dispatch_prefetch
+    issued = []
+
+    def fake_prefetch(unit_id, phase):
+        unit = rt.units[unit_id]
+        issued.append((unit_id, phase))
+        if unit.lease is None:
+            unit.generation += 1
+            unit.lease = MaterializationLease(unit_id, rt.step_id, phase, unit.generation)
+            unit.state = f"{phase}_MATERIALIZING"
+
+    rt.prefetch = fake_prefetch
+    for uid in range(4):
+        unit = UnitState(rt, uid, None)
+        unit.forward_calls, unit.generation, unit.state = 1, 1, "RESHARDED"
+        rt.units.append(unit)
+    rt.step_id, rt.active = 0, True
+    rt.backward_entry_expected = rt.backward_dispatch_expected = 3
+    last = rt.units[3]
+    last.state, last.lease = "FWD_RETAINED", MaterializationLease(3, 0, "FWD", 1)
+    rt.validate_backward_prefetch_entry(last)
+    last.backward_calls, last.state = 1, "BWD_ACTIVE"
+    rt.backward_prefetch_entered(last)             # seeds the gather of unit 2
+    assert issued == [(2, "BWD")] and rt.backward_entry_expected == 2
+    last.reductions, last.state = 1, "GRAD_REDUCING"
+    return rt, issued
+
+
+def test_gradient_dispatch_issues_exactly_the_unit_two_below_the_owner():
+    rt, issued = _dispatch_fixture()
+    rt.dispatch_backward_prefetch(rt.units[3])
+    assert issued == [(2, "BWD"), (1, "BWD")] and rt.backward_dispatch_expected == 2
+    token = rt.backward_prefetch_tokens[(0, 2)]
+    assert (token["target_unit"], token["gradient_owner"], token["status"]) == (1, 3, "issued")
+    assert token["scheduling_boundary"] == "previous_gradient_dispatch"
+    # unit 2 may now enter: both tokens (its own seed and the one it needs for unit 1) are fresh
+    unit2 = rt.units[2]
+    rt.validate_backward_prefetch_entry(unit2)
+
+
+@pytest.mark.parametrize("fault,message", [
+    ("wrong_owner", "reduction order"),
+    ("entered", "arrived after current entry"),
+    ("completed", "Completed/unvisited"),
+    ("stale_token", "Stale gradient-dispatch token"),
+    ("owner_not_reducing", "Invalid gradient-dispatch owner"),
+])
+def test_invalid_gradient_dispatch_fails_before_any_extra_gather(fault, message):
+    """No dynamic fallback: a dispatch that does not fit the schedule raises, and it raises before
+    another gather is issued or a generation is consumed."""
+    rt, issued = _dispatch_fixture()
+    owner = rt.units[3]
+    if fault == "wrong_owner":
+        owner = rt.units[2]
+        owner.state, owner.backward_calls, owner.reductions = "GRAD_REDUCING", 1, 1
+    elif fault == "entered":
+        rt.units[2].backward_calls = 1
+    elif fault == "completed":
+        rt.units[1].reductions = 1
+    elif fault == "stale_token":
+        rt.units[2].generation += 1             # re-materialised behind the token's back
+    elif fault == "owner_not_reducing":
+        owner.state = "BWD_ACTIVE"
+    generations = [u.generation for u in rt.units]
+    with pytest.raises(RuntimeError, match=message):
+        rt.dispatch_backward_prefetch(owner)
+    assert issued == [(2, "BWD")]
+    assert [u.generation for u in rt.units] == generations

@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--fused-allgather", default="auto")
     ap.add_argument("--wire", default="bf16")
     ap.add_argument("--seq-pull", type=int, default=1)
+    ap.add_argument("--nvls", default="off")
     ap.add_argument("--inject-inf-rank", type=int, default=-1,
                     help="this rank poisons one shard gradient with inf in step 1 (host-side injection)")
     ap.add_argument("--delay-rank", type=int, default=-1,
@@ -78,7 +79,7 @@ def main():
                             communication_policy=a.policy, directory=out,
                             communication_backend=a.backend, compute_dtype=a.dtype,
                             fused_allgather=a.fused_allgather, wire_dtype=a.wire,
-                            fused_seq_gather=bool(a.seq_pull))
+                            fused_seq_gather=bool(a.seq_pull), nvls=a.nvls)
         rt.register(model, ctx, sp=bool(a.sp))
         lr = 1e-3 if a.optimizer == "adamw" else 0.05
         tr = QwenTrainer(model, rt, lr=lr, optimizer=a.optimizer, accumulation_steps=a.accum,
@@ -143,7 +144,9 @@ def main():
         (out / f"result.rank{worker.rank}.json").write_text(json.dumps(dict(
             rows=rows, param_err=err, events=events, kinds=kinds, seq=seq, shard_ok=shard_ok,
             live=len(rt.comm.live_buffers), names=[n for n, _ in model.named_parameters()][:4],
-            units=len(rt.units), leaves=len(rt.registry), errs=errs)))
+            units=len(rt.units), leaves=len(rt.registry), errs=errs,
+            nvls=bool(getattr(rt.fused, "nvls_active", False)),
+            nvls_refusal=getattr(getattr(rt.fused, "reduce_peer", None), "multicast_refusal", None))))
         rt.comm.flush_diagnostics()
         if ctx.device.type == "cuda":
             from shardtrain_b200 import ops
