@@ -108,6 +108,60 @@ __device__ __forceinline__ RowSource locate_row(const SegShared* segs, int n_seg
   return r;
 }
 
+// One 16-byte chunk of a weight stage by the general route: rows beyond the weight and the K
+// tail are zero filled; later passes read the local full buffer; otherwise the eight elements are
+// fetched from their owners (fp32 or bf16 arenas), one by one where a 16-byte piece could straddle
+// two owners or be misaligned.  Kept out of line: the common case never comes here.
+__device__ __noinline__ void copy_chunk_general(const AgParams& p, const SegShared* segs,
+                                                RowSource rs, uint8_t* dst, int k0, bool from_peers) {
+  __nv_bfloat16 v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = __float2bfloat16(0.f);
+  if (rs.seg >= 0 && k0 < p.K) {
+    const SegShared& sg = segs[rs.seg];
+    const uint32_t flat = rs.flat0 + static_cast<uint32_t>(k0);
+    const uint32_t q32 = static_cast<uint32_t>(sg.q);
+    const bool whole = sg.vec && k0 + 8 <= p.K;
+    if (!from_peers) {
+      const __nv_bfloat16* g = p.w.full + sg.full_off + flat;
+      for (int e = 0; e < 8 && k0 + e < p.K; ++e) v[e] = g[e];
+    } else if (whole && p.w.shadow[0] == nullptr && flat / q32 == (flat + 7) / q32) {
+      const uint32_t owner = flat / q32;
+      const float4* g = reinterpret_cast<const float4*>(p.w.shard[owner] + sg.shard_off +
+                                                        (flat - owner * q32));
+      const float4 lo = g[0], hi = g[1];
+      v[0] = __float2bfloat16(lo.x); v[1] = __float2bfloat16(lo.y);
+      v[2] = __float2bfloat16(lo.z); v[3] = __float2bfloat16(lo.w);
+      v[4] = __float2bfloat16(hi.x); v[5] = __float2bfloat16(hi.y);
+      v[6] = __float2bfloat16(hi.z); v[7] = __float2bfloat16(hi.w);
+    } else {
+      for (int e = 0; e < 8 && k0 + e < p.K; ++e) {
+        const uint32_t f = flat + e;
+        const uint32_t owner = f / q32;
+        const int64_t off = sg.shard_off + (f - owner * q32);
+        v[e] = p.w.shadow[0] != nullptr ? p.w.shadow[owner][off]
+                                        : __float2bfloat16(p.w.shard[owner][off]);
+      }
+    }
+  }
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(v);
+}
+
+// Mirror one landed chunk into the local full buffer, element by element where needed.
+__device__ __noinline__ void mirror_chunk_general(const AgParams& p, const SegShared* segs,
+                                                  RowSource rs, const uint8_t* chunk_smem, int k0) {
+  if (rs.seg < 0 || k0 >= p.K) return;
+  const SegShared& sg = segs[rs.seg];
+  const uint4 x = *reinterpret_cast<const uint4*>(chunk_smem);
+  __nv_bfloat16* g = p.w.full + sg.full_off + rs.flat0 + k0;
+  if (sg.vec && k0 + 8 <= p.K) {
+    *reinterpret_cast<uint4*>(g) = x;
+  } else {
+    const __nv_bfloat16* xv = reinterpret_cast<const __nv_bfloat16*>(&x);
+    for (int e = 0; e < 8 && k0 + e < p.K; ++e) g[e] = xv[e];
+  }
+}
+
 // Every CTA reads the whole of A, one k-block after the other.  If all CTAs walked K in the same
 // order they would ask the L2 for the same few lines at the same moment; each tile therefore
 // starts at its own k-block and wraps around (the sum over K does not depend on the order up to
@@ -116,7 +170,8 @@ __device__ __forceinline__ int k_rotation(int tile, int num_kb) { return (tile *
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
+gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
+                      const __grid_constant__ AgParams p) {
   using S = AgSmem<BN>;
   constexpr int NB = S::kBStages;
   if (kernel_should_skip(p.status)) return;
@@ -274,6 +329,7 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
       const int n0 = tile * tile_cols;
       const int rot = k_rotation(tile, num_kb);
       RowSource src[ROWS_PER_THREAD];
+      uint32_t row_off[ROWS_PER_THREAD];     // byte offset of this thread's chunk inside a stage
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         const int r = (t >> 3) + i * 16;     // row inside the tile
@@ -286,30 +342,54 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
           fused_row = n0 + r;
         }
         src[i] = locate_row(segs, p.w.n_segs, fused_row, p.N, p.K);
+        row_off[i] = static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
       }
       for (int pass = 0; pass < passes; ++pass, ++round) {
         const bool from_peers = pass == 0;
         const bool mirror = from_peers && p.w.full != nullptr;
+        // Per row, resolved once per pass: where the row's chunks are read from when the whole row
+        // sits in one place (one owner's bf16 shard, or the local full buffer on later passes)
+        // and 16-byte pieces are safe, and where they are mirrored to.  The per-stage loop is then
+        // a handful of instructions per chunk; anything else (fp32 on the wire, rows that
+        // straddle two owners, unaligned shards, the K tail) goes through copy_chunk_general.
+        const __nv_bfloat16* fast_src[ROWS_PER_THREAD];
+        __nv_bfloat16* mirror_dst[ROWS_PER_THREAD];
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+          fast_src[i] = nullptr;
+          mirror_dst[i] = nullptr;
+          if (src[i].seg < 0) continue;
+          const SegShared& sg = segs[src[i].seg];
+          if (!sg.vec) continue;
+          if (mirror) mirror_dst[i] = p.w.full + sg.full_off + src[i].flat0;
+          if (!from_peers) {
+            fast_src[i] = p.w.full + sg.full_off + src[i].flat0;
+          } else if (p.w.shadow[0] != nullptr) {
+            const uint32_t q32 = static_cast<uint32_t>(sg.q);
+            const uint32_t owner = src[i].flat0 / q32;
+            if ((src[i].flat0 + static_cast<uint32_t>(p.K) - 1) / q32 == owner)
+              fast_src[i] = p.w.shadow[owner] + sg.shard_off + (src[i].flat0 - owner * q32);
+          }
+        }
         // The copies of weight stage `done` (k-block `done_kb` of this pass) have landed for this
         // thread: mirror its chunks into the local full buffer, then hand the stage to the MMAs.
         auto publish = [&](int done, int done_kb) {
           if (mirror) {
             const uint8_t* st = b_tiles + (done % NB) * S::kBTile;
             const int dk0 = done_kb * kBK + chunk * 8;
+            if (dk0 + 8 <= p.K) {
 #pragma unroll
-            for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-              const int r = (t >> 3) + i * 16;
-              if (src[i].seg < 0 || dk0 >= p.K) continue;
-              const SegShared& sg = segs[src[i].seg];
-              const uint4 x =
-                  *reinterpret_cast<const uint4*>(st + r * 128 + ((chunk ^ (r & 7)) << 4));
-              __nv_bfloat16* g = p.w.full + sg.full_off + src[i].flat0 + dk0;
-              if (sg.vec && dk0 + 8 <= p.K) {
-                *reinterpret_cast<uint4*>(g) = x;
-              } else {
-                const __nv_bfloat16* xv = reinterpret_cast<const __nv_bfloat16*>(&x);
-                for (int e = 0; e < 8 && dk0 + e < p.K; ++e) g[e] = xv[e];
+              for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+                if (mirror_dst[i] != nullptr)
+                  *reinterpret_cast<uint4*>(mirror_dst[i] + dk0) =
+                      *reinterpret_cast<const uint4*>(st + row_off[i]);
+                else
+                  mirror_chunk_general(p, segs, src[i], st + row_off[i], dk0);
               }
+            } else {
+#pragma unroll
+              for (int i = 0; i < ROWS_PER_THREAD; ++i)
+                mirror_chunk_general(p, segs, src[i], st + row_off[i], dk0);
             }
           }
           fence_proxy_async();                 // generic-proxy writes -> visible to the tensor core
@@ -326,62 +406,20 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a, AgParams p) {
             break;
           }
           uint8_t* stage = b_tiles + sb * S::kBTile;
+          const uint32_t stage_addr = smem_u32(stage);
           const int k0 = kb * kBK + chunk * 8;
+          if (k0 + 8 <= p.K) {
 #pragma unroll
-          for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-            const int r = (t >> 3) + i * 16;
-            uint8_t* dst = stage + r * 128 + ((chunk ^ (r & 7)) << 4);
-            if (src[i].seg < 0 || k0 >= p.K) {
-              *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-              continue;
+            for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+              if (fast_src[i] != nullptr)
+                cp_async_16(stage_addr + row_off[i], fast_src[i] + k0);
+              else
+                copy_chunk_general(p, segs, src[i], stage + row_off[i], k0, from_peers);
             }
-            const SegShared& sg = segs[src[i].seg];
-            const uint32_t flat = src[i].flat0 + static_cast<uint32_t>(k0);
-            const uint32_t q32 = static_cast<uint32_t>(sg.q);
-            const bool whole = sg.vec && k0 + 8 <= p.K;     // one aligned 16-byte piece
-            if (!from_peers) {
-              // later passes: the first pass left the rows in the local full buffer
-              const __nv_bfloat16* g = p.w.full + sg.full_off + flat;
-              if (whole) {
-                cp_async_16(smem_u32(dst), g);
-              } else {
-                __nv_bfloat16 v[8];
+          } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = k0 + e < p.K ? g[e] : __float2bfloat16(0.f);
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(v);
-              }
-              continue;
-            }
-            if (whole && p.w.shadow[0] != nullptr) {
-              const uint32_t owner = flat / q32;
-              cp_async_16(smem_u32(dst), p.w.shadow[owner] + sg.shard_off + (flat - owner * q32));
-              continue;
-            }
-            // general path: fp32 on the wire, or shard boundaries that are not 8-element aligned
-            __nv_bfloat16 v[8];
-            if (whole) {
-              const uint32_t owner = flat / q32;
-              const float4* g = reinterpret_cast<const float4*>(p.w.shard[owner] + sg.shard_off +
-                                                                (flat - owner * q32));
-              const float4 lo = g[0], hi = g[1];
-              v[0] = __float2bfloat16(lo.x); v[1] = __float2bfloat16(lo.y);
-              v[2] = __float2bfloat16(lo.z); v[3] = __float2bfloat16(lo.w);
-              v[4] = __float2bfloat16(hi.x); v[5] = __float2bfloat16(hi.y);
-              v[6] = __float2bfloat16(hi.z); v[7] = __float2bfloat16(hi.w);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                v[e] = __float2bfloat16(0.f);
-                if (k0 + e < p.K) {
-                  const uint32_t f = flat + e;
-                  const uint32_t owner = f / q32;
-                  const int64_t off = sg.shard_off + (f - owner * q32);
-                  v[e] = p.w.shadow[0] != nullptr ? p.w.shadow[owner][off]
-                                                  : __float2bfloat16(p.w.shard[owner][off]);
-                }
-              }
-            }
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(v);
+            for (int i = 0; i < ROWS_PER_THREAD; ++i)
+              copy_chunk_general(p, segs, src[i], stage + row_off[i], k0, from_peers);
           }
           cp_async_commit();
           ++waiting;

@@ -194,24 +194,51 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
     if (lane == 0) {
       int it = 0;  // k-blocks issued so far, across tiles
       bool ok = true;
+      uint64_t ready_tiles = 0;   // PULL: row tiles of A whose groups were all seen landed
+      (void)ready_tiles;
       for (int unit = blockIdx.x; unit < sp.total_units && ok; unit += gridDim.x) {
         int tile, kb0, kb1, part, m0, n0;
         unit_work(unit, tile, kb0, kb1, part);
         tile_origin(tile, m0, n0);
         if constexpr (PULL) {
-          // the rows m0 .. m0 + 127 of A must have landed in the local buffer
-          const int g_first = m0 / kPullRows;
-          const int g_last = (min(M, m0 + kGemmBM) - 1) / kPullRows;
-          for (int g = g_first; g <= g_last && ok; ++g) {
-            if (!wait_flag_equal(pull.flags + g, pull.epoch, status)) {
-              if (status != nullptr) atomicCAS(status, kOk, kErrPullWait);
-              *abort_flag = 1;
-              ok = false;
+          // The rows m0 .. m0 + 127 of A must have landed in the local buffer.  All flags of the
+          // tile are read in one batch of independent relaxed loads (an acquire load per flag
+          // would serialise sixteen L2 round trips); one fence then orders the tile's TMA reads
+          // behind them.  Row tiles already seen complete are remembered.
+          const int m_tile = m0 / kGemmBM;
+          const bool known = m_tile < 64 && ((ready_tiles >> m_tile) & 1ull);
+          if (!known) {
+            const int g_first = m0 / kPullRows;
+            const int g_count = (min(M, m0 + kGemmBM) - 1) / kPullRows - g_first + 1;
+            const uint64_t t0 = global_ns();
+            for (uint32_t spin = 0;; ++spin) {
+              uint32_t seen[kGemmBM / kPullRows];
+#pragma unroll
+              for (int g = 0; g < kGemmBM / kPullRows; ++g) {
+                seen[g] = pull.epoch;
+                if (g < g_count)
+                  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];"
+                               : "=r"(seen[g]) : "l"(pull.flags + g_first + g) : "memory");
+              }
+              bool all = true;
+#pragma unroll
+              for (int g = 0; g < kGemmBM / kPullRows; ++g) all = all && seen[g] == pull.epoch;
+              if (all) break;
+              if ((spin & 63u) == 63u &&
+                  (status_failed(status) || global_ns() - t0 > kWaitBudgetNs)) {
+                if (status != nullptr) atomicCAS(status, kOk, kErrPullWait);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              __nanosleep(32);
             }
+            if (!ok) break;
+            if (m_tile < 64) ready_tiles |= 1ull << m_tile;
+            asm volatile("fence.acq_rel.gpu;" ::: "memory");
+            // generic-proxy stores of the pulling warps -> visible to the TMA (async proxy) reads
+            asm volatile("fence.proxy.async;" ::: "memory");
           }
-          if (!ok) break;
-          // generic-proxy stores of the pulling warps -> visible to the TMA (async proxy) reads
-          asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;

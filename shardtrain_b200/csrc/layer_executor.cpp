@@ -58,12 +58,12 @@ AgPlan make_ag_plan(c10::ArrayRef<int64_t> arenas, bool wire_fp32,
                     const c10::optional<at::Tensor>& full) {
   AgPlan plan;
   if (arenas.empty()) return plan;
-  TORCH_CHECK(segs_qkv.has_value() && segs_gu.has_value() && full.has_value(),
-              "fused all-gather: segment tables and the full buffer are required");
+  TORCH_CHECK((segs_qkv.has_value() || segs_gu.has_value()) && full.has_value(),
+              "fused all-gather: a segment table and the full buffer are required");
   plan.arenas.assign(arenas.begin(), arenas.end());
   plan.wire_fp32 = wire_fp32;
-  plan.segs_qkv = &*segs_qkv;
-  plan.segs_gu = &*segs_gu;
+  plan.segs_qkv = segs_qkv.has_value() ? &*segs_qkv : nullptr;     // either may stay with the
+  plan.segs_gu = segs_gu.has_value() ? &*segs_gu : nullptr;        // gather kernel
   plan.full = *full;
   return plan;
 }
@@ -171,7 +171,7 @@ struct Gemm {
   // q|k|v projection (+ bias), pulling the weights inside the GEMM when a plan is given
   void qkv_proj(const Tensor& a, const Tensor& w_qkv, Tensor& qkv, const float* bias,
                 const AgPlan& plan, const SeqPull& pull = SeqPull{}) const {
-    if (plan.on())
+    if (plan.on() && plan.segs_qkv != nullptr)
       allgather(a, qkv, bias, nullptr, plan, *plan.segs_qkv);
     else
       run(a, w_qkv, qkv, false, false, bias, nullptr, pull);
@@ -202,7 +202,7 @@ struct Gemm {
   // the fused kernel wins (31 us against 28 + 8 us at 512 rows).  Results are bit-identical.
   void gate_up(const Tensor& a, const Tensor& w_gu, Tensor& gu, Tensor& hm, cudaStream_t st,
                const AgPlan& plan = AgPlan{}, const SeqPull& pull = SeqPull{}) const {
-    if (plan.on()) {
+    if (plan.on() && plan.segs_gu != nullptr) {
       allgather(a, gu, nullptr, &hm, plan, *plan.segs_gu);
       return;
     }
@@ -424,7 +424,8 @@ std::vector<Tensor> layer_forward_sp(
   const int64_t T = static_cast<int64_t>(h1_ptrs.size());
   const int64_t Sl = S / T, Ml = B * Sl, M = B * S, H = x2.size(1), D = 128;
   // the sequence gather runs inside the consuming GEMM unless that GEMM already pulls its weights
-  const bool pull_a = seq_pull && !ag.on();
+  const bool pull_qkv = seq_pull && !(ag.on() && ag.segs_qkv != nullptr);
+  const bool pull_gu = seq_pull && !(ag.on() && ag.segs_gu != nullptr);
   const int64_t W = (hq + 2 * hkv) * D, inter = w_down.size(1);
   TORCH_CHECK(S % T == 0 && x2.size(0) == Ml && recv.dim() == 3 && recv.size(0) == T &&
                   recv.size(1) == Ml && recv.size(2) == H && recv.is_contiguous(),
@@ -444,10 +445,10 @@ std::vector<Tensor> layer_forward_sp(
                              inv1.data_ptr<float>(), Ml, H, feps, false, st), "rmsnorm");
   sp.barrier();                                   // every rank's h1 slice is written
   Tensor h_full = at::empty({M, H}, bf);
-  if (!pull_a) sp.gather(h1_ptrs, h_full, B, Sl);
+  if (!pull_qkv) sp.gather(h1_ptrs, h_full, B, Sl);
   Tensor qkv = at::empty({M, W}, bf);
   g.qkv_proj(h_full, w_qkv, qkv, b_qkv.data_ptr<float>(), ag,
-             pull_a ? SeqPull{h1_ptrs, B, Sl} : SeqPull{});
+             pull_qkv ? SeqPull{h1_ptrs, B, Sl} : SeqPull{});
   ok(stb::launch_rope(qkv.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), pos, M, S, hq,
                       hkv, D, false, st), "rope");
   Tensor attn = at::empty({M, hq * D}, bf), lse = at::empty({B, hq, S}, f32);
@@ -465,9 +466,9 @@ std::vector<Tensor> layer_forward_sp(
                                   h2_local.data_ptr(), inv2.data_ptr<float>(), Ml, H, feps, st),
      "slot sum + rmsnorm");
   sp.barrier();                                   // h2 slices written, receive slots consumed
-  if (!pull_a) sp.gather(h2_ptrs, h_full, B, Sl);
+  if (!pull_gu) sp.gather(h2_ptrs, h_full, B, Sl);
   Tensor gu = at::empty({M, 2 * inter}, bf), hm = at::empty({M, inter}, bf);
-  g.gate_up(h_full, w_gu, gu, hm, st, ag, pull_a ? SeqPull{h2_ptrs, B, Sl} : SeqPull{});
+  g.gate_up(h_full, w_gu, gu, hm, st, ag, pull_gu ? SeqPull{h2_ptrs, B, Sl} : SeqPull{});
   g.scatter(hm, w_down, false, push_ptrs, static_cast<int>(S));
   sp.barrier();
   Tensor out = at::empty({Ml, H}, f32);

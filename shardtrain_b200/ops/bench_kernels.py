@@ -51,7 +51,8 @@ def timed(fn, warmup, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_scatter", "gemm_allgather", "attention",
+    ap.add_argument("kernel", choices=["gemm", "gemm_scatter", "gemm_allgather", "gemm_seq_pull",
+                                       "attention",
                                        "reduce_scatter_adamw", "gather_params", "gather_shadow",
                                        "rmsnorm"])
     ap.add_argument("--gated", type=int, default=0, help="gemm_allgather: gate|up with SwiGLU epilogue")
@@ -140,6 +141,27 @@ def main():
         out.update(shape=[a.m, rows, a.k], owners=F, gated=a.gated, fused_ms=ms_fused,
                    gather_then_gemm_ms=ms_two, tflops=tflops, weight_gbs=numel * 2 / ms_fused / 1e6,
                    frac_of_sustained_cublas=tflops / sustained)
+    elif a.kernel == "gemm_seq_pull":
+        # sequence all-gather fused into the GEMM: `--owners` local slices stand in for the peers'
+        T = a.owners
+        sl = a.m // T
+        slices = [torch.randn(sl, a.k, device=dev).bfloat16() for _ in range(T)]
+        ptrs = [t.data_ptr() for t in slices]
+        B = (torch.randn(a.n, a.k, device=dev) * 0.1).bfloat16()
+        A_dst = torch.empty(T * sl, a.k, device=dev, dtype=torch.bfloat16)
+        C = torch.empty(T * sl, a.n, device=dev, dtype=torch.bfloat16)
+        ms_fused = timed(lambda: ops.gemm_seq_pull(A_dst, B, C, False, None, ptrs, 1, sl, a.bn),
+                         a.warmup, a.iters, flush=True)
+
+        def two():
+            ops.seq_gather(ptrs, A_dst, 1, sl, a.k * 2)
+            ops.gemm(A_dst, B, C, False, False, None, None, False, 1.0, a.bn)
+        ms_two = timed(two, a.warmup, a.iters, flush=True)
+        ms_gemm = timed(lambda: ops.gemm(A_dst, B, C, False, False, None, None, False, 1.0, a.bn),
+                        a.warmup, a.iters, flush=True)
+        tflops = 2 * T * sl * a.n * a.k / ms_fused / 1e9
+        out.update(shape=[T * sl, a.n, a.k], owners=T, fused_ms=ms_fused, gather_then_gemm_ms=ms_two,
+                   gemm_only_ms=ms_gemm, tflops=tflops, frac_of_sustained_cublas=tflops / sustained)
     elif a.kernel == "attention":
         D, W = 128, (a.hq + 2 * a.hkv) * 128
         rows = a.batch * a.seq

@@ -11,10 +11,14 @@ forward / backward prefetch lists, autocast compute, AdamW(foreach=False), the s
 initialisation, the same synthetic batch and the same record layout (`benchmark.rank{r}.json`,
 `"engine": "native_fsdp2"`).
 
-Scope: FSDP meshes and FSDP x TP meshes without sequence parallelism (DTensor Colwise / Rowwise
-plan on the projections, `fully_shard` on the FSDP axis of a 2-D device mesh).  The reference's
-sequence-parallel plan with its shared gathered input is not reproduced; SP is refused with a
-configuration error.
+Scope: FSDP meshes, FSDP x TP meshes (DTensor Colwise / Rowwise plan on the projections,
+`fully_shard` on the FSDP axis of a 2-D device mesh) and FSDP x TP meshes with sequence
+parallelism: the residual stream, the norms, the embedding output and the logits are sharded
+along the sequence (`SequenceParallel` norms, replicated DTensor embedding / head weights whose
+gradients DTensor sums over the TP axis), each of the attention and MLP blocks gathers its input
+ONCE for all of its column-parallel projections (compute dtype forward, FP32 for the adjoint's
+reduce-scatter: `src/sharded_runtime/training/qwen2_native_baseline.py:164-278`), and the
+row-parallel projections reduce-scatter their output back to the sequence shard.
 """
 
 from __future__ import annotations
@@ -63,25 +67,113 @@ def materialize_same_source(model, device) -> None:
             raise RuntimeError(f"Buffer {name} cannot be materialised from a meta tensor")
 
 
-def parallelize_tensor_axis(model, tp_mesh) -> None:
-    """Megatron-style TP without SP through DTensor: q/k/v/gate/up column-wise, o/down row-wise
-    (all-reduce inside RowwiseParallel); activations, norms, embedding and head stay replicated."""
-    from torch.distributed.tensor.parallel import (ColwiseParallel, RowwiseParallel,
-                                                   parallelize_module)
+def _gather_sequence_once():
+    """A DTensor parallel style for a block (attention or MLP) under sequence parallelism: its
+    input -- this rank's [B, S/T, H] slice -- becomes one replicated DTensor that every
+    column-parallel projection inside the block consumes, so the block gathers once, not once
+    per projection, and the adjoints of all projections meet in one reduce-scatter.  The gather
+    moves the autocast compute dtype; the adjoint is reduced in FP32.  Only DTensor's own
+    `redistribute` is used (its `forward_dtype` / `backward_dtype` arguments are what
+    `PrepareModuleInput` does not expose)."""
+    from torch.distributed.tensor import DTensor, Replicate, Shard
+    from torch.distributed.tensor.parallel import ParallelStyle
+
+    class GatherSequenceOnce(ParallelStyle):
+        def _apply(self, module, device_mesh):
+            def gather(_module, args):
+                x = args[0]
+                local = x if isinstance(x, DTensor) else DTensor.from_local(
+                    x, device_mesh, [Shard(1)], run_check=False)
+                kind = x.device.type
+                forward_dtype = (torch.get_autocast_dtype(kind) if torch.is_autocast_enabled(kind)
+                                 else x.dtype)
+                full = local.redistribute(placements=[Replicate()], forward_dtype=forward_dtype,
+                                          backward_dtype=torch.float32)
+                return (full, *args[1:])
+
+            module.register_forward_pre_hook(gather)
+            return module
+
+    return GatherSequenceOnce()
+
+
+def parallelize_tensor_axis(model, tp_mesh, *, sequence_parallel: bool = False) -> None:
+    """Megatron-style TP through DTensor: q/k/v/gate/up column-wise, o/down row-wise.  Without
+    SP activations, norms, embedding and head stay replicated and RowwiseParallel all-reduces;
+    with SP everything outside the two blocks of a layer works on this rank's sequence slice
+    (see the module docstring)."""
+    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+    from torch.distributed.tensor.parallel import (ColwiseParallel, PrepareModuleInput,
+                                                   PrepareModuleOutput, RowwiseParallel,
+                                                   SequenceParallel, parallelize_module)
 
     degree = tp_mesh.size()
+    cfg = model.config
+    if (cfg.num_attention_heads % degree or cfg.num_key_value_heads % degree
+            or cfg.intermediate_size % degree):
+        raise ConfigError("attention heads, KV heads and the MLP width must be divisible by the "
+                          "TP degree")
+    row_output = Shard(1) if sequence_parallel else Replicate()
     plan = {"self_attn.q_proj": ColwiseParallel(), "self_attn.k_proj": ColwiseParallel(),
-            "self_attn.v_proj": ColwiseParallel(), "self_attn.o_proj": RowwiseParallel(),
+            "self_attn.v_proj": ColwiseParallel(),
+            "self_attn.o_proj": RowwiseParallel(output_layouts=row_output),
             "mlp.gate_proj": ColwiseParallel(), "mlp.up_proj": ColwiseParallel(),
-            "mlp.down_proj": RowwiseParallel()}
+            "mlp.down_proj": RowwiseParallel(output_layouts=row_output)}
+    if sequence_parallel:
+        plan.update({"self_attn": _gather_sequence_once(), "mlp": _gather_sequence_once(),
+                     "input_layernorm": SequenceParallel(use_local_output=True),
+                     "post_attention_layernorm": SequenceParallel(use_local_output=True)})
     for layer in model.model.layers:
-        attention = layer.self_attn
-        if attention.num_heads % degree or attention.num_key_value_heads % degree:
-            raise ConfigError("attention heads must be divisible by the TP degree")
         parallelize_module(layer, tp_mesh, plan)
         # the module reshapes its local projection outputs: it now owns 1/T of the heads
-        attention.num_heads //= degree
-        attention.num_key_value_heads //= degree
+        layer.self_attn.num_heads //= degree
+        layer.self_attn.num_key_value_heads //= degree
+    if not sequence_parallel:
+        return
+    parallelize_module(model.model.norm, tp_mesh, SequenceParallel(use_local_output=True))
+    # Embedding and head: replicated weights as DTensors (one shared Parameter when tied), fed
+    # with sequence-sharded DTensors, so that the weight gradient -- a partial sum over this
+    # rank's positions -- is summed over the TP axis by DTensor before FSDP reduces it.
+    embedding, head = model.model.embed_tokens, model.lm_head
+    tied = head.weight is embedding.weight
+    shared = torch.nn.Parameter(distribute_tensor(embedding.weight, tp_mesh, [Replicate()]))
+    embedding.weight = shared
+    head.weight = shared if tied else torch.nn.Parameter(
+        distribute_tensor(head.weight, tp_mesh, [Replicate()]))
+    parallelize_module(embedding, tp_mesh, PrepareModuleInput(
+        input_layouts=Shard(1), desired_input_layouts=Shard(1), use_local_output=False))
+    parallelize_module(embedding, tp_mesh, PrepareModuleOutput(
+        output_layouts=Shard(1), desired_output_layouts=Shard(1), use_local_output=True))
+    # The head is a Linear over [B, S/T, H]: DTensor would have to flatten a sharded sequence
+    # dimension into the rows, which it refuses.  The rows of a linear layer are independent, so
+    # the local slice goes in as the row shard of a 2-D DTensor (row order is irrelevant to the
+    # weight gradient) and the local logits come back in the slice's own shape.
+    from torch.distributed.tensor import DTensor
+
+    def rows_in(_module, args):
+        x = args[0]
+        head._native_local_shape = x.shape[:-1]
+        return (DTensor.from_local(x.reshape(-1, x.shape[-1]), tp_mesh, [Shard(0)], run_check=False),)
+
+    def rows_out(_module, _args, out):
+        return out.to_local().reshape(*head._native_local_shape, out.shape[-1])
+
+    head.register_forward_pre_hook(rows_in)
+    head.register_forward_hook(rows_out)
+    rank, width = tp_mesh.get_local_rank(), None
+
+    def slice_ids(_module, args):
+        ids = args[0]
+        nonlocal width
+        width = ids.shape[1] // degree
+        if ids.shape[1] % degree:
+            raise ValueError("sequence length must be divisible by the TP degree")
+        return (ids[:, rank * width:(rank + 1) * width].contiguous(), *args[1:])
+
+    # runs before the layout hook registered above: the model hands the embedding the whole
+    # [B, S] ids, the embedding sees this rank's columns
+    embedding.register_forward_pre_hook(slice_ids, prepend=True)
+    model._native_sequence_parallel = (rank, degree)
 
 
 def shard_with_fsdp2(model, mesh, *, reshard_after_forward, forward_prefetch, backward_prefetch):
@@ -130,22 +222,48 @@ class NativeStepResult:
 class NativeQwenTrainer:
     """Gradient accumulation with a global-token loss denominator, finite vote, AdamW."""
 
-    def __init__(self, model, lr, *, dtype, optimizer, accumulation_steps, device, group):
+    def __init__(self, model, lr, *, dtype, optimizer, accumulation_steps, device, group,
+                 loss_group=None):
+        """`group`: the ranks that hold different batches (FSDP axis).  `loss_group`: the ranks
+        whose loss parts add up to the global loss -- the FSDP axis, or the whole mesh when the
+        sequence is sharded over the TP axis as well."""
         self.model, self.device, self.group = model, device, group
+        self.loss_group = loss_group if loss_group is not None else group
         self.accumulation_steps, self.step_id = accumulation_steps, 0
         self.compute_dtype = resolve_qwen_compute_dtype(dtype, device)
-        if dtype == "fp16":
-            raise ConfigError("The native baseline runs fp32 or bf16 (no loss scaler)")
+        # fp16: a dynamic loss scale kept by hand (torch's GradScaler does not know that the
+        # gradients are sharded DTensors whose finiteness must be voted over the mesh): start at
+        # 128, halve and skip the update on overflow, double after 2000 clean steps
+        # (`src/sharded_runtime/training/qwen2_native_baseline.py:392-505`).
+        self.loss_scale = 128.0 if dtype == "fp16" else 1.0
+        self.dynamic_scale = dtype == "fp16"
+        self.growth_interval, self.clean_steps = 2000, 0
         make = {"adamw": lambda p: torch.optim.AdamW(p, lr=lr, foreach=False),
                 "sgd": lambda p: torch.optim.SGD(p, lr=lr, foreach=False)}
         if optimizer not in make:
             raise ConfigError("Qwen optimizer must be sgd or adamw")
         self.optimizer = make[optimizer](model.parameters())
 
-    def _sum(self, value):
-        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            dist.all_reduce(value, group=self.group)
+    def _sum(self, value, group=None):
+        group = self.group if group is None else group
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(value, group=group)
         return value
+
+    def _loss_part(self, logits, labels):
+        """Summed next-token cross-entropy of this rank's logits.  Under sequence parallelism the
+        logits cover this rank's positions only: the labels are shifted over the *whole*
+        sequence first (the label of a slice's last position lives in the next slice)."""
+        shard = getattr(self.model, "_native_sequence_parallel", None)
+        if shard is None:
+            return causal_lm_loss_parts(logits, labels)[0]
+        rank, degree = shard
+        shifted = torch.nn.functional.pad(labels[:, 1:], (0, 1), value=-100)
+        width = labels.shape[1] // degree
+        mine = shifted[:, rank * width:(rank + 1) * width]
+        return torch.nn.functional.cross_entropy(
+            logits.float().reshape(-1, logits.shape[-1]), mine.reshape(-1), ignore_index=-100,
+            reduction="sum")
 
     def train_step(self, input_ids, labels, *, attention_mask=None, position_ids=None):
         batch = input_ids.shape[0]
@@ -162,23 +280,34 @@ class NativeQwenTrainer:
             mask = attention_mask[lo:hi] if attention_mask is not None else None
             with torch.autocast(self.device.type, dtype=self.compute_dtype, enabled=enabled):
                 out = self.model(input_ids[lo:hi], attention_mask=mask, position_ids=position_ids)
-            part, _ = causal_lm_loss_parts(out.logits, labels[lo:hi])
+            part = self._loss_part(out.logits, labels[lo:hi])
             # FSDP averages gradients over the group: scale so the result is the global mean
-            (part * world / count.to(part.dtype)).backward()
+            (part * (self.loss_scale * world) / count.to(part.dtype)).backward()
             total += part.detach().to(torch.float64)
-        loss = self._sum(total) / count
+        loss = self._sum(total, self.loss_group) / count
         finite = torch.isfinite(loss).to(torch.float64)
         for parameter in self.model.parameters():
             grad = parameter.grad
             if grad is not None:
                 local = grad.to_local() if hasattr(grad, "to_local") else grad
+                if self.loss_scale != 1.0:
+                    local.mul_(1.0 / self.loss_scale)      # unscale in place before the vote
                 finite = finite * torch.isfinite(local).all().to(torch.float64)
-        if dist.is_initialized() and world > 1:
-            dist.all_reduce(finite, op=dist.ReduceOp.MIN, group=self.group)
+        if dist.is_initialized() and dist.get_world_size(self.loss_group) > 1:
+            dist.all_reduce(finite, op=dist.ReduceOp.MIN, group=self.loss_group)
         row = torch.stack([finite, loss, count]).cpu().tolist()
         overflow = not bool(row[0])
         if not overflow:
             self.optimizer.step()
+        if self.dynamic_scale:
+            if overflow:                      # every rank saw the same vote: same new scale
+                self.loss_scale, self.clean_steps = self.loss_scale * 0.5, 0
+            else:
+                self.clean_steps += 1
+                if self.clean_steps == self.growth_interval:
+                    self.loss_scale, self.clean_steps = self.loss_scale * 2.0, 0
+        elif overflow:
+            raise FloatingPointError("Nonfinite native baseline loss or gradients")
         self.step_id += 1
         return NativeStepResult(self.step_id, float(row[1]), int(row[2]), overflow,
                                 self.accumulation_steps)
@@ -190,8 +319,8 @@ def run(config: Config, *, warmup: int = 0, peak_tflops_per_gpu: float | None = 
     ranks reduced outside the timer, CUDA-event span)."""
     if config.model.model_type != "qwen2":
         raise ConfigError("The native baseline requires model.model_type=qwen2")
-    if config.parallel.sp_enabled:
-        raise ConfigError("The native baseline covers FSDP and FSDP x TP meshes without SP")
+    if config.parallel.sp_enabled and config.parallel.tp_degree < 2:
+        raise ConfigError("Sequence parallelism needs a TP degree of at least 2")
     if type(warmup) is not int or warmup < 0:
         raise ConfigError("warmup must be a nonnegative integer")
     rank = WorkerEnvironment.read().rank
@@ -217,20 +346,24 @@ def run(config: Config, *, warmup: int = 0, peak_tflops_per_gpu: float | None = 
             model = build_qwen_model(config.model, tc.seed)
             parameters = sum(p.numel() for p in model.parameters())
             materialize_same_source(model, device)
-            group = None
+            group = loss_group = None
             if session.worker.launched:
                 degrees = (config.parallel.fsdp_degree, config.parallel.tp_degree)
                 mesh = init_device_mesh(device.type, degrees, mesh_dim_names=("fsdp", "tp"))
                 if degrees[1] > 1:
-                    parallelize_tensor_axis(model, mesh["tp"])
+                    parallelize_tensor_axis(model, mesh["tp"],
+                                            sequence_parallel=config.parallel.sp_enabled)
                 payload["sharding"] = shard_with_fsdp2(
                     model, mesh["fsdp"], reshard_after_forward=rc.reshard_after_forward,
                     forward_prefetch=rc.forward_prefetch, backward_prefetch=rc.backward_prefetch)
                 payload["sharding"]["tensor_parallel_degree"] = degrees[1]
+                payload["sharding"]["sequence_parallel"] = config.parallel.sp_enabled
                 group = mesh["fsdp"].get_group()      # TP ranks of a replica see the same batch
+                # with SP every rank of the mesh holds a different part of the loss
+                loss_group = dist.group.WORLD if config.parallel.sp_enabled else group
             trainer = NativeQwenTrainer(model, tc.lr, dtype=tc.dtype, optimizer=tc.optimizer,
                                         accumulation_steps=tc.accumulation_steps, device=device,
-                                        group=group)
+                                        group=group, loss_group=loss_group)
             draw = torch.Generator().manual_seed(tc.seed + ctx.coordinate.fsdp)
             ids = torch.randint(model.config.vocab_size,
                                 (tc.local_batch_size * tc.accumulation_steps, config.model.seq_len),

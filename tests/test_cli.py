@@ -181,9 +181,10 @@ def test_native_fsdp2_baseline_matches_the_sharded_runtime_single_rank(tmp_path)
         assert a["valid_tokens"] == b["valid_tokens"]
     assert native["performance"]["model_unique_parameters"] == \
         ours["performance"]["model_unique_parameters"]
-    with pytest.raises(ConfigError, match="without SP"):
+    with pytest.raises(ConfigError, match="WORLD_SIZE=1 does not match"):
         qwen2_native_baseline.run(load_config(
-            CONFIGS / "qwen25_tiny.yaml", ["--parallel.tp_degree", "2", "--parallel.sp_enabled", "true"]))
+            CONFIGS / "qwen25_tiny.yaml", ["--parallel.tp_degree", "2", "--parallel.sp_enabled", "true",
+                                           "--debug.output_dir", str(tmp_path / "refused")]))
 
 
 @pytest.mark.distributed
@@ -237,3 +238,58 @@ def test_native_baseline_fsdp_x_tp_mesh_matches_runtime(tmp_path):
         assert all(r["status"] == "completed" for r in records)
         losses[module] = [row["loss"] for row in records[0]["steps"]]
     assert losses["qwen2_native_baseline"] == pytest.approx(losses["qwen2_benchmark"], rel=1e-5)
+
+
+@pytest.mark.distributed
+def test_native_baseline_sequence_parallel_mesh_matches_runtime(tmp_path):
+    """F2 x T2 with sequence parallelism on 4 gloo ranks: DTensor SequenceParallel norms, one
+    gathered input per block, row-parallel outputs scattered back to the sequence shard --
+    against this package's runtime on the same mesh, same weights, same batches."""
+    common = ["--config", CONFIGS / "qwen25_tiny.yaml", "--warmup", "0", "--parallel.fsdp_degree", "2",
+              "--parallel.tp_degree", "2", "--parallel.sp_enabled", "true", "--training.steps", "3",
+              "--training.accumulation_steps", "2", "--training.local_batch_size", "2"]
+    losses = {}
+    for module in ("qwen2_native_baseline", "qwen2_benchmark"):
+        out = tmp_path / module
+        code, log = run_workers(f"shardtrain_b200.training.{module}", 4, common + ["--debug.output_dir", out])
+        assert code == 0, log[-3000:]
+        records = [json.loads((out / f"benchmark.rank{r}.json").read_text()) for r in range(4)]
+        assert all(r["status"] == "completed" for r in records)
+        assert len({tuple(row["loss"] for row in r["steps"]) for r in records}) == 1   # all ranks agree
+        losses[module] = [row["loss"] for row in records[0]["steps"]]
+        if module == "qwen2_native_baseline":
+            assert records[0]["sharding"]["sequence_parallel"] is True
+    # three optimizer steps: the engines stay together only if the TP-replicated parameters
+    # (embedding, norms) received the gradient summed over the sequence shards
+    assert losses["qwen2_native_baseline"] == pytest.approx(losses["qwen2_benchmark"], rel=2e-5)
+    assert losses["qwen2_benchmark"][2] < losses["qwen2_benchmark"][0]
+
+
+def test_native_trainer_loss_scale_backs_off_and_skips_on_overflow():
+    """The native engine's hand-kept fp16 loss scale: an overflow skips the update and halves the
+    scale, clean steps leave it alone until the growth interval doubles it (CPU: the dtype is
+    forced after construction, only the bookkeeping is exercised)."""
+    import torch
+
+    from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+    from shardtrain_b200.training.qwen2_native_baseline import NativeQwenTrainer
+
+    torch.manual_seed(0)
+    model = Qwen2CausalLM(Qwen2ModelConfig(vocab_size=64, hidden_size=32, intermediate_size=64,
+                                           num_hidden_layers=1, num_attention_heads=4,
+                                           num_key_value_heads=2))
+    trainer = NativeQwenTrainer(model, 1e-3, dtype="fp32", optimizer="adamw", accumulation_steps=1,
+                                device=torch.device("cpu"), group=None)
+    trainer.dynamic_scale, trainer.loss_scale, trainer.growth_interval = True, 128.0, 2
+    ids = torch.randint(0, 64, (2, 8))
+    before = [p.detach().clone() for p in model.parameters()]
+    hook = model.lm_head.weight.register_hook(lambda g: torch.full_like(g, float("inf")))
+    skipped = trainer.train_step(ids, ids)
+    hook.remove()
+    assert skipped.overflow and trainer.loss_scale == 64.0
+    assert all(torch.equal(a, b) for a, b in zip(before, model.parameters()))
+    first = trainer.train_step(ids, ids)
+    assert not first.overflow and trainer.loss_scale == 64.0
+    assert not all(torch.equal(a, b) for a, b in zip(before, model.parameters()))
+    trainer.train_step(ids, ids)
+    assert trainer.loss_scale == 128.0            # two clean steps: the scale grew back
