@@ -19,7 +19,7 @@ import torch.distributed as dist
 from torch import nn
 from torch.nn import functional as F
 
-from shardtrain_b200.models.transformer_block import masked_softmax_attention
+from shardtrain_b200.models.transformer_block import causal_attention_heads, gated_mlp
 from shardtrain_b200.parallel.model import ROW_PROJECTIONS, supported_blocks, validate_blocks
 from shardtrain_b200.runtime.engine import UnitState
 from shardtrain_b200.runtime.qwen2_adapter import ParameterPartition
@@ -57,13 +57,11 @@ def block_forward(runtime, unit, block, prefix, x):
     attention = block.attention
     h = _norm(unit, prefix + "attention_norm.weight", x, block.attention_norm.eps)
     q, k, v = _column(runtime, unit, prefix + "attention.", ("q_proj", "k_proj", "v_proj"), h, "qkv")
-    batch, seq, width = q.shape
-    q, k, v = (t.reshape(batch, seq, -1, attention.head_dim).transpose(1, 2) for t in (q, k, v))
-    mixed = masked_softmax_attention(q, k, v).transpose(1, 2).contiguous().reshape(batch, seq, width)
+    mixed = causal_attention_heads(q, k, v, attention.head_dim)
     x = x + _row(runtime, unit, prefix + "attention.out_proj.weight", mixed)
     h = _norm(unit, prefix + "mlp_norm.weight", x, block.mlp_norm.eps)
     gate, up = _column(runtime, unit, prefix + "mlp.", ("gate_proj", "up_proj"), h, "gate_up")
-    x = x + _row(runtime, unit, prefix + "mlp.down_proj.weight", F.silu(gate) * up)
+    x = x + _row(runtime, unit, prefix + "mlp.down_proj.weight", gated_mlp(gate, up))
     return unit.post_forward(x)
 
 

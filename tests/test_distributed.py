@@ -135,3 +135,18 @@ def test_rank_skew_does_not_change_results(tmp_path):
         record = json.loads((tmp_path / f"result.rank{rank}.json").read_text())
         assert record["param_err"] < 1e-5
         assert all(abs(row["loss"] - row["ref"]) < 1e-4 for row in record["rows"])
+
+
+@pytest.mark.parametrize("sp", [0, 1], ids=["tp", "tp_sp"])
+def test_legacy_synchronous_tp_path_follows_the_dense_model(tmp_path, sp):
+    """The blocking TP / TP+SP conversion of the toy stack (column / row linears over the
+    conjugate collective maps, shared sequence gather, replicated-gradient SUM) on 2 gloo ranks:
+    losses and reassembled parameters track the unsharded trainer for three SGD steps."""
+    code, log = run_workers("tests.workers.tp_sp_worker", 2, ["--out", tmp_path, "--sp", sp])
+    assert code == 0, log[-3000:]
+    for rank in range(2):
+        record = json.loads((tmp_path / f"tp.rank{rank}.json").read_text())
+        for row in record["rows"]:
+            assert row["loss"] == pytest.approx(row["ref"], rel=2e-6)
+        assert record["worst"] < 2e-6
+        assert record["column_dim"] == 0 and record["heads"] == 2 and record["local_rows"] == 16

@@ -300,3 +300,36 @@ def test_invalid_gradient_dispatch_fails_before_any_extra_gather(fault, message)
         rt.dispatch_backward_prefetch(owner)
     assert issued == [(2, "BWD")]
     assert [u.generation for u in rt.units] == generations
+
+
+def test_toy_reference_path_matches_frozen_golden_values():
+    """Frozen numbers of the seeded toy stack (2 blocks, hidden 16, 4 heads, MLP 32, sequence 8,
+    model seed 1234, batch seed 77): forward values, the functional oracle, and three SGD steps
+    of the reference trainer.  A change of initialisation order, of the block math or of the
+    trainer's loss / accumulation arithmetic shows up here even if it is self-consistent."""
+    from shardtrain_b200.config import ModelConfig
+    from shardtrain_b200.models.reference import build_reference_model, synthetic_batch
+    from shardtrain_b200.training.reference import dense_oracle
+    from shardtrain_b200.training.trainer import Trainer
+
+    cfg = ModelConfig(layers=2, hidden_size=16, num_heads=4, mlp_hidden_size=32, seq_len=8)
+    model = build_reference_model(cfg, 1234)
+    x = synthetic_batch(cfg, 2, 77)
+    out = model(x)
+    oracle = dense_oracle(x, dict(model.named_parameters()), cfg)[-1]
+    torch.testing.assert_close(out, oracle, atol=2e-6, rtol=1e-5)
+    golden_row = torch.tensor([-1.31182373, 0.02675569, -0.54071665, -0.76120323, -2.77202582, 1.2404623])
+    torch.testing.assert_close(out[0, 0, :6], golden_row, atol=2e-6, rtol=1e-5)
+    assert out.square().mean().item() == pytest.approx(1.06242466, rel=2e-6)
+    assert out.sum().item() == pytest.approx(-38.966568, rel=2e-6)
+    trainer = Trainer(model, 0.05, 2)
+    steps = [trainer.train_step(x) for _ in range(3)]
+    golden_steps = [(1.06242466, 0.60632238, 12.5600424), (1.04437137, 0.58500424, 12.5583124),
+                    (1.02754593, 0.56574057, 12.5568729)]
+    for got, (loss, grad_l2, param_l2) in zip(steps, golden_steps):
+        assert got.loss == pytest.approx(loss, rel=3e-6)
+        assert got.gradient_l2 == pytest.approx(grad_l2, rel=3e-6)
+        assert got.parameter_l2 == pytest.approx(param_l2, rel=1e-6)
+    weight = dict(model.named_parameters())["1.mlp.down_proj.weight"][0, :4]
+    torch.testing.assert_close(weight, torch.tensor([0.17048123, -0.1423282, 0.11148591, 0.17114937]),
+                               atol=2e-7, rtol=1e-5)
