@@ -1,11 +1,12 @@
-"""Process-group ownership for one worker: default group, four role communicators, device binding.
+"""Process-group ownership for one worker: the default group, four role communicators, device
+binding, and a teardown that never waits for a peer.
 
-Mirrors the behaviour of the reference's `DistributedContext`
+Behaviour kept from the reference's `DistributedContext`
 (`src/sharded_runtime/distributed/context.py:45-211`): the context must create the default group
-itself, every rank creates every communicator in `Topology.creation_order`, close callbacks run
-before destruction, and cleanup never issues a barrier (a missing peer must not hang it).
-On CUDA it can additionally build the NVLink peer-memory tables used by the fused kernels
-(`shardtrain_b200.distributed.peer`).
+itself, every rank creates every communicator in `Topology.creation_order` (creation is
+collective), close callbacks run before any group is destroyed, and cleanup issues no barrier
+(after a failure some peer may never arrive).  The teardown is a list of labelled steps; each
+step's failure is logged and collected in `cleanup_errors` without stopping the later steps.
 """
 
 from __future__ import annotations
@@ -22,6 +23,8 @@ import torch.distributed as dist
 from shardtrain_b200.config import ConfigError, ParallelConfig
 from shardtrain_b200.distributed.topology import GROUP_ROLES, Topology
 
+_LAUNCHER_VARIABLES = ("RANK", "LOCAL_RANK", "WORLD_SIZE")
+
 
 @dataclass(frozen=True)
 class WorkerEnvironment:
@@ -32,15 +35,15 @@ class WorkerEnvironment:
 
     @classmethod
     def read(cls, environ: Mapping[str, str] | None = None) -> "WorkerEnvironment":
+        """The torchrun variables: all three or none (a plain single-process run)."""
         env = os.environ if environ is None else environ
-        names = ("RANK", "LOCAL_RANK", "WORLD_SIZE")
-        have = [n in env for n in names]
-        if not any(have):
+        present = [name for name in _LAUNCHER_VARIABLES if name in env]
+        if not present:
             return cls()
-        if not all(have):
+        if len(present) != len(_LAUNCHER_VARIABLES):
             raise ConfigError("torchrun requires RANK, LOCAL_RANK and WORLD_SIZE together")
         try:
-            rank, local_rank, world = (int(env[n]) for n in names)
+            rank, local_rank, world = (int(env[name]) for name in _LAUNCHER_VARIABLES)
         except ValueError as exc:
             raise ConfigError("torchrun rank environment values must be integers") from exc
         if world <= 0 or not 0 <= rank < world or local_rank < 0:
@@ -48,14 +51,21 @@ class WorkerEnvironment:
         return cls(rank, local_rank, world, True)
 
 
+def _backend_problem(backend: str) -> str | None:
+    """Why this PyTorch build cannot serve `backend` (None: it can)."""
+    if not os.environ.get("MASTER_ADDR") or not os.environ.get("MASTER_PORT"):
+        return "torchrun launch requires MASTER_ADDR and MASTER_PORT"
+    if not dist.is_available():
+        return "This PyTorch build does not support torch.distributed"
+    available = {"nccl": dist.is_nccl_available, "gloo": dist.is_gloo_available}.get(backend)
+    if available is not None and not available():
+        return f"{'NCCL' if backend == 'nccl' else 'Gloo'} is unavailable in this PyTorch build"
+    return None
+
+
 class DistributedContext:
-    def __init__(
-        self,
-        parallel: ParallelConfig,
-        worker: WorkerEnvironment,
-        timeout_seconds: int,
-        logger: logging.Logger,
-    ) -> None:
+    def __init__(self, parallel: ParallelConfig, worker: WorkerEnvironment, timeout_seconds: int,
+                 logger: logging.Logger) -> None:
         self.logger, self.parallel, self.worker = logger, parallel, worker
         self.topology = Topology(parallel.fsdp_degree, parallel.tp_degree)
         if self.topology.world_size != worker.world_size:
@@ -64,55 +74,49 @@ class DistributedContext:
         self.device = torch.device("cpu")
         self.cleanup_errors: list[str] = []
         self._callbacks: list[Callable[[], None]] = []
-        self._groups: list[Any] = []
+        self._groups: list[Any] = []          # the role communicators this rank belongs to
         self._owns_default = False
         self._closed = False
-        for role in GROUP_ROLES:
-            setattr(self, f"{role}_group", None)
+        self._forget_groups()
         try:
-            self._bind_device()
+            self.device = self._bound_device()
             if dist.is_initialized():
                 raise RuntimeError("DistributedContext requires ownership of an uninitialized group")
             if worker.launched:
                 self._create_groups(timedelta(seconds=timeout_seconds))
-            logger.info(
-                "Context ready: rank=%d local_rank=%d coordinate=%s device=%s groups=%s",
-                worker.rank, worker.local_rank, self.coordinate, self.device,
-                self.topology.groups_for_rank(worker.rank),
-            )
         except BaseException:
             self.close()
             raise
+        logger.info("Context ready: rank=%d local_rank=%d coordinate=%s device=%s groups=%s",
+                    worker.rank, worker.local_rank, self.coordinate, self.device,
+                    self.topology.groups_for_rank(worker.rank))
 
     # ------------------------------------------------------------------ setup
-    def _bind_device(self) -> None:
+    def _forget_groups(self) -> None:
+        for role in GROUP_ROLES:
+            setattr(self, f"{role}_group", None)
+
+    def _bound_device(self) -> torch.device:
         if self.parallel.device != "cuda":
-            return
+            return torch.device("cpu")
         if not torch.cuda.is_available():
             raise ConfigError("CUDA was requested but is unavailable")
-        if self.worker.local_rank >= torch.cuda.device_count():
+        index = self.worker.local_rank
+        if index >= torch.cuda.device_count():
             raise ConfigError("LOCAL_RANK exceeds the number of visible CUDA devices")
-        torch.cuda.set_device(self.worker.local_rank)
-        self.device = torch.device("cuda", self.worker.local_rank)
+        torch.cuda.set_device(index)
+        return torch.device("cuda", index)
 
     def _create_groups(self, timeout: timedelta) -> None:
         backend = self.parallel.backend
-        if not os.environ.get("MASTER_ADDR") or not os.environ.get("MASTER_PORT"):
-            raise ConfigError("torchrun launch requires MASTER_ADDR and MASTER_PORT")
-        if not dist.is_available():
-            raise ConfigError("This PyTorch build does not support torch.distributed")
-        if backend == "nccl" and not dist.is_nccl_available():
-            raise ConfigError("NCCL is unavailable in this PyTorch build")
-        if backend == "gloo" and not dist.is_gloo_available():
-            raise ConfigError("Gloo is unavailable in this PyTorch build")
-        kwargs = {}
-        if backend == "nccl":
-            kwargs["device_id"] = self.device
-        dist.init_process_group(
-            backend=backend, rank=self.worker.rank, world_size=self.worker.world_size,
-            timeout=timeout, **kwargs,
-        )
+        problem = _backend_problem(backend)
+        if problem is not None:
+            raise ConfigError(problem)
+        options = {"device_id": self.device} if backend == "nccl" else {}
+        dist.init_process_group(backend=backend, rank=self.worker.rank,
+                                world_size=self.worker.world_size, timeout=timeout, **options)
         self._owns_default = True
+        # group creation is collective over the default group: every rank walks the whole list
         for role, members in self.topology.creation_order:
             self.logger.debug("Creating %s group ranks=%s", role, members)
             group = dist.new_group(ranks=list(members), backend=backend, timeout=timeout)
@@ -132,18 +136,19 @@ class DistributedContext:
             raise RuntimeError("Cannot use a closed DistributedContext")
         report = {}
         for role, members in self.topology.groups_for_rank(self.worker.rank).items():
-            mine = torch.tensor([float(self.worker.rank + 1)], device=self.device)
-            parts = [torch.empty_like(mine) for _ in members]
+            token = torch.tensor([float(self.worker.rank + 1)], device=self.device)
+            seen = [torch.empty_like(token) for _ in members]
             if self._owns_default:
                 group = getattr(self, f"{role}_group")
-                dist.all_gather(parts, mine, group=group)
-                dist.all_reduce(mine, op=dist.ReduceOp.SUM, group=group)
+                dist.all_gather(seen, token, group=group)
+                dist.all_reduce(token, op=dist.ReduceOp.SUM, group=group)
             else:
-                parts[0].copy_(mine)
-            total, seen = mine.item(), [p.item() for p in parts]
-            if total != sum(r + 1 for r in members) or seen != [float(r + 1) for r in members]:
-                raise AssertionError(f"{role} collective mismatch: {total}, {seen}")
-            report[role] = {"ranks": list(members), "sum": total, "gather": seen}
+                seen[0].copy_(token)
+            total, gathered = token.item(), [t.item() for t in seen]
+            expected = [float(r + 1) for r in members]
+            if total != sum(expected) or gathered != expected:
+                raise AssertionError(f"{role} collective mismatch: {total}, {gathered}")
+            report[role] = {"ranks": list(members), "sum": total, "gather": gathered}
         self.logger.info("Collective smoke passed: %s", report)
         return report
 
@@ -155,35 +160,33 @@ class DistributedContext:
             raise TypeError("DistributedContext close callback must be callable")
         self._callbacks.append(callback)
 
+    # ------------------------------------------------------------------ teardown
+    def _teardown_steps(self):
+        """(label, log message, action) in execution order.  No step waits for a peer."""
+        for index, callback in enumerate(self._callbacks):
+            yield (f"close callback {index}", f"Failed to run local close callback {index}", callback)
+        for group in reversed(self._groups):
+            yield ("destroy subgroup", "Failed to destroy subgroup",
+                   lambda group=group: dist.destroy_process_group(group))
+        if self._owns_default:
+            yield ("destroy default group", "Failed to destroy default process group",
+                   dist.destroy_process_group)
+
     def close(self) -> None:
         if self._closed:
             return
         self._closed = True
-        callbacks, self._callbacks = self._callbacks, []
-        for index, callback in enumerate(callbacks):
+        steps = list(self._teardown_steps())
+        self._callbacks = []
+        for label, message, action in steps:
             try:
-                callback()
-            except Exception as exc:  # noqa: BLE001
-                self.cleanup_errors.append(f"close callback {index}: {exc!r}")
-                self.logger.exception("Failed to run local close callback %d", index)
-        # No barrier here: after a failure some peer may never arrive.
-        for group in reversed(self._groups):
-            try:
-                dist.destroy_process_group(group)
-            except Exception as exc:  # noqa: BLE001
-                self.cleanup_errors.append(f"destroy subgroup: {exc!r}")
-                self.logger.exception("Failed to destroy subgroup")
+                action()
+            except Exception as exc:  # noqa: BLE001 - collected; later steps still run
+                self.cleanup_errors.append(f"{label}: {exc!r}")
+                self.logger.exception(message)
         self._groups.clear()
-        if self._owns_default:
-            try:
-                dist.destroy_process_group()
-            except Exception as exc:  # noqa: BLE001
-                self.cleanup_errors.append(f"destroy default group: {exc!r}")
-                self.logger.exception("Failed to destroy default process group")
-            finally:
-                self._owns_default = False
-        for role in GROUP_ROLES:
-            setattr(self, f"{role}_group", None)
+        self._owns_default = False
+        self._forget_groups()
         self.logger.info("Context closed")
 
     def __enter__(self) -> "DistributedContext":
