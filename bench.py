@@ -53,8 +53,8 @@ def parse_args():
                     help="gather parameters from the fp32 shards instead of their bf16 shadow")
     ap.add_argument("--fused-allgather", default="auto", choices=["auto", "on", "off"],
                     help="pull q|k|v and gate|up inside the forward GEMMs (FSDP degree > 1)")
-    ap.add_argument("--no-seq-pull", action="store_true",
-                    help="sequence parallel: gather kernel + GEMM instead of the pulling GEMM")
+    ap.add_argument("--seq-pull", action="store_true",
+                    help="sequence parallel: the pulling GEMM instead of gather kernel + GEMM")
     ap.add_argument("--nvls", default="off", choices=["auto", "off"],
                     help="FSDP-only meshes: reduce gradients in the NVSwitch (multimem.ld_reduce)")
     ap.add_argument("--no-secondary", action="store_true",
@@ -137,7 +137,7 @@ def qwen15b_dict(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
                         communication_backend=args.backend, retain_parameters=bool(args.retain),
                         fused_allgather=args.fused_allgather,
                         wire_dtype="fp32" if args.fp32_wire else "bf16",
-                        fused_seq_gather=not args.no_seq_pull, nvls=args.nvls),
+                        fused_seq_gather=args.seq_pull, nvls=args.nvls),
         "training": dict(dtype="bf16", optimizer="adamw", lr=1e-5, steps=args.steps,
                          local_batch_size=args.global_batch // fsdp // 2, accumulation_steps=2,
                          seed=1234),

@@ -79,7 +79,7 @@ class RuntimeConfig:
     retain_parameters: bool = False
     fused_allgather: str = "auto"
     wire_dtype: str = "bf16"
-    fused_seq_gather: bool = True
+    fused_seq_gather: bool = False
     nvls: str = "off"
 
 

@@ -11,6 +11,10 @@ namespace stb {
 // Streaming multiprocessors of the current device (queried once per process; grids are sized from
 // it instead of from a constant).
 int sm_count();
+// Every kernel launch site of this library counts itself: the number of kernels launched by this
+// process so far (benchmarks report the difference over their timed region).
+void count_launch();
+int64_t launches_total();
 
 // ------------------------------------------------------------------ GEMM (gemm_sm100.cu)
 struct GemmCall {
@@ -27,6 +31,9 @@ struct GemmCall {
   float alpha;
   int force_bn;  // 0 = rule, else 128, 192 or 256
   int split_k;   // K-split of the tail wave's tiles: 0 = rule, 1 = never, n = exactly n
+  // 0 = plain outputs leave through TMA stores staged in shared memory when the output's base
+  // and pitch allow it; -1 = always the per-thread row stores
+  int staged_store;
   // Gated (SwiGLU) forward: b = fused [2 * gated_inter, K] gate|up weight (K-major), out = [M, 2 *
   // gated_inter] bf16 (gate|up), gated_out = [M, gated_inter] bf16 = silu(gate) * up.  N must be
   // 2 * gated_inter.

@@ -768,6 +768,7 @@ cudaError_t launch_attention_fwd(const AttnCall& c, int* status, cudaStream_t s)
               c.hkv, c.scale, status, c.key_bits, c.key_bits_pitch};
   dim3 grid((c.seq + kBlk - 1) / kBlk, c.hq, c.batch);
   attention_fwd_kernel<<<grid, kThreads, kFwdSmem, s>>>(map, p);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -788,6 +789,7 @@ cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t
   attention_delta_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(c.out), reinterpret_cast<const __nv_bfloat16*>(c.dout),
       c.delta, c.batch, c.seq, c.hq);
+  count_launch();
   const int nblk = (c.seq + kBlk - 1) / kBlk;
   int parts = 1;
   if (c.dkv_accum != nullptr) {
@@ -804,12 +806,15 @@ cudaError_t launch_attention_bwd(const AttnBwdCall& c, int* status, cudaStream_t
               c.key_bits, c.key_bits_pitch};
   attention_dkv_kernel<<<dim3(nblk, c.hkv * parts, c.batch), kThreads, kDkvSmem, s>>>(map_qkv,
                                                                                      map_do, p);
+  count_launch();
   attention_dq_kernel<<<dim3(nblk, c.hq, c.batch), kThreads, kDqSmem, s>>>(map_qkv, map_do, p);
+  count_launch();
   if (parts > 1) {
     const int64_t work = rows * (2 * c.hkv * kD / 8);
     const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, sm_count() * 8));
     attention_dkv_finish_kernel<<<grid, 256, 0, s>>>(c.dkv_accum, parts, rows, c.hq, c.hkv,
                                                      reinterpret_cast<__nv_bfloat16*>(c.dqkv));
+    count_launch();
   }
   return cudaGetLastError();
 }
@@ -836,6 +841,7 @@ cudaError_t launch_pack_key_mask(const uint8_t* mask, uint32_t* bits, int batch,
     return cudaErrorInvalidValue;
   const int total = batch * pitch;
   pack_key_mask_kernel<<<(total + 127) / 128, 128, 0, s>>>(mask, bits, batch, seq, pitch);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -44,7 +44,8 @@ Tensor status_tensor_op() { return status_tensor(); }
 
 void gemm(const Tensor& a, const Tensor& b, Tensor out, bool a_mn, bool b_mn,
           const c10::optional<Tensor>& bias, const c10::optional<Tensor>& residual,
-          bool accumulate, double alpha, int64_t force_bn, int64_t split_k) {
+          bool accumulate, double alpha, int64_t force_bn, int64_t split_k,
+          bool staged_store) {
   need(a, at::kBFloat16, "a");
   need(b, at::kBFloat16, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm operands must be 2-D");
@@ -72,6 +73,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, bool a_mn, bool b_mn,
   c.alpha = static_cast<float>(alpha);
   c.force_bn = static_cast<int>(force_bn);
   c.split_k = static_cast<int>(split_k);
+  c.staged_store = staged_store ? 0 : -1;
   if (bias.has_value()) {
     need(*bias, at::kFloat, "bias");
     TORCH_CHECK(bias->numel() == c.N, "bias length mismatch");
@@ -708,6 +710,7 @@ int64_t peer_alloc(int64_t nbytes) {
 }
 void peer_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
 void device_synchronize() { check(cudaDeviceSynchronize(), "device_synchronize"); }
+int64_t launch_count() { return stb::launches_total(); }
 // Let kernels on the current device dereference pointers into `peer_device`'s memory (one
 // process driving two GPUs; across processes the CUDA-IPC mappings above do the same).
 void enable_peer_access(int64_t peer_device) {
@@ -827,7 +830,7 @@ TORCH_LIBRARY(stb, m) {
   m.def("status_reset", &status_reset);
   m.def("status_tensor", &status_tensor_op);
   m.def("gemm(Tensor a, Tensor b, Tensor out, bool a_mn, bool b_mn, Tensor? bias, Tensor? residual, "
-        "bool accumulate, float alpha, int force_bn, int split_k=0) -> ()",
+        "bool accumulate, float alpha, int force_bn, int split_k=0, bool staged_store=True) -> ()",
         &gemm);
   m.def("gemm_scatter", &gemm_scatter);
   m.def("gemm_seq_pull", &gemm_seq_pull);
@@ -873,6 +876,7 @@ TORCH_LIBRARY(stb, m) {
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);
   m.def("device_synchronize", &device_synchronize);
+  m.def("launch_count", &launch_count);
   m.def("enable_peer_access", &enable_peer_access);
   m.def("ipc_handle", &ipc_handle);
   m.def("ipc_open", &ipc_open);

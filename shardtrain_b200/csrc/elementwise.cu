@@ -503,10 +503,13 @@ cudaError_t launch_rmsnorm_fwd(const float* x, const float* w, void* y, float* i
                                int cols, float eps, bool y_fp32, cudaStream_t s) {
   if (cols % 4) return cudaErrorInvalidValue;
   const int threads = cols >= 1024 ? 256 : 128;
-  if (y_fp32)
+  if (y_fp32) {
     rmsnorm_fwd_kernel<true><<<rows, threads, 0, s>>>(x, w, y, inv, cols, eps);
-  else
+    count_launch();
+  } else {
     rmsnorm_fwd_kernel<false><<<rows, threads, 0, s>>>(x, w, y, inv, cols, eps);
+    count_launch();
+  }
   return cudaGetLastError();
 }
 
@@ -519,6 +522,7 @@ cudaError_t launch_slot_sum_rmsnorm(const float* slots, int n_slots, int64_t slo
   slot_sum_rmsnorm_kernel<<<rows, threads, 0, s>>>(slots, n_slots, slot_stride, residual, sum_out, w,
                                                    reinterpret_cast<__nv_bfloat16*>(y), inv, cols,
                                                    eps);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -530,12 +534,14 @@ cudaError_t launch_rmsnorm_bwd(const float* dy, const float* x, const float* w, 
   const size_t smem = (cols + 32) * sizeof(float);
   rmsnorm_bwd_kernel<<<partial_rows, threads, smem, s>>>(dy, x, w, inv, dres_in, dx_out,
                                                          dw_partial, rows, cols);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_colsum_f32(const float* partial, float* out, int rows, int cols,
                               bool accumulate, cudaStream_t s) {
   colsum_f32_kernel<<<(cols + 31) / 32, dim3(32, 8), 0, s>>>(partial, out, rows, cols, accumulate);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -545,8 +551,10 @@ cudaError_t launch_colsum_bf16(const void* x, int64_t ldx, float* out, int rows,
   dim3 grid((cols / 2 + 127) / 128, scratch_rows);
   colsum_bf16_partial_kernel<<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
                                                   scratch, rows, cols);
+  count_launch();
   colsum_f32_kernel<<<(cols + 31) / 32, dim3(32, 8), 0, s>>>(scratch, out, scratch_rows, cols,
                                                              accumulate);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -556,6 +564,7 @@ cudaError_t launch_rope(void* qkv, const float* cos, const float* sin, const int
   const int64_t work = static_cast<int64_t>(rows) * (hq + hkv) * (d / 4);
   rope_kernel<<<static_cast<int>((work + 255) / 256), 256, 0, s>>>(
       reinterpret_cast<__nv_bfloat16*>(qkv), cos, sin, positions, rows, seq, hq, hkv, d, inverse);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -564,6 +573,7 @@ cudaError_t launch_swiglu_fwd(const void* gu, void* h, int rows, int inter, cuda
   const int64_t work = static_cast<int64_t>(rows) * (inter / 8);
   swiglu_fwd_kernel<<<grid_for(work, 256, sm_count() * 16), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(gu), reinterpret_cast<__nv_bfloat16*>(h), rows, inter);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -574,6 +584,7 @@ cudaError_t launch_swiglu_bwd(const void* dh, const void* gu, void* dgu, int row
   swiglu_bwd_kernel<<<grid_for(work, 256, sm_count() * 16), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(dh), reinterpret_cast<const __nv_bfloat16*>(gu),
       reinterpret_cast<__nv_bfloat16*>(dgu), rows, inter);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -582,6 +593,7 @@ cudaError_t launch_ce_fwd(const void* logits, int64_t ld, const int64_t* labels,
   if (vocab % 8 || ld % 8) return cudaErrorInvalidValue;
   ce_fwd_kernel<<<rows, 512, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, labels,
                                      lse, loss_rows, vocab);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -590,45 +602,53 @@ cudaError_t launch_ce_bwd(void* logits, int64_t ld, const int64_t* labels, const
   if (vocab % 8 || ld % 8) return cudaErrorInvalidValue;
   ce_bwd_kernel<<<rows, 512, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, labels, lse,
                                      scale, vocab);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_sum_f32(const float* x, float* out, int n, bool accumulate, cudaStream_t s) {
   sum_f32_kernel<<<1, 1024, 0, s>>>(x, out, n, accumulate);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_embedding_scatter_add(const float* dx, const int64_t* ids, float* dw, int rows,
                                          int cols, int64_t vocab, int64_t pad_id, cudaStream_t s) {
   embedding_scatter_add_kernel<<<rows, 256, 0, s>>>(dx, ids, dw, rows, cols, vocab, pad_id);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_cast_f32_to_bf16(const float* x, void* y, int64_t n, cudaStream_t s) {
   cast_f32_bf16_kernel<<<grid_for(n / 4 + 1, 256, sm_count() * 16), 256, 0, s>>>(
       x, reinterpret_cast<__nv_bfloat16*>(y), n);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_add_f32(const float* a, const float* b, float* out, int64_t n, cudaStream_t s) {
   add_f32_kernel<<<grid_for(n / 4 + 1, 256, sm_count() * 16), 256, 0, s>>>(a, b, out, n);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_adamw(float* p, const float* g, float* m, float* v, int64_t n, AdamWArgs a,
                          cudaStream_t s) {
   adamw_kernel<<<grid_for(n / 4 + 1, 256, sm_count() * 16), 256, 0, s>>>(p, g, m, v, n, a);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_sgd(float* p, const float* g, int64_t n, float lr, cudaStream_t s) {
   sgd_kernel<<<grid_for(n, 256, sm_count() * 16), 256, 0, s>>>(p, g, n, lr);
+  count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_grad_check(const float* g, int64_t n, const int64_t* pad_ranges, int n_ranges,
                               int* flags, cudaStream_t s) {
   grad_check_kernel<<<grid_for(n, 256, sm_count() * 8), 256, 0, s>>>(g, n, pad_ranges, n_ranges, flags);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -559,6 +559,7 @@ cudaError_t launch_bn(const AgGemmCall& c, int mt, int* status, cudaStream_t str
   const int n_tiles = (span + tile_cols - 1) / tile_cols;
   const int grid = std::min(n_tiles, sm_count());
   kernel<<<grid, kThreads, smem, stream>>>(ta, p);
+  count_launch();
   return cudaGetLastError();
 }
 

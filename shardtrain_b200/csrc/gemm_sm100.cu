@@ -1,6 +1,7 @@
 // Host launcher of the tcgen05 GEMM: builds the TMA tensor maps and picks the tile width.
 #include <algorithm>
 #include <array>
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -55,12 +56,15 @@ constexpr size_t kMapCacheLimit = 8192;
 
 }  // namespace
 
-bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
-                          int64_t ld, int box_cols, int box_rows) {
+namespace {
+
+bool make_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                     int box_cols, int box_rows, bool fp32) {
   EncodeTiledFn fn = encode_tiled();
   if (fn == nullptr) return false;
+  const int64_t esize = fp32 ? 4 : 2;
   const MapKey key{{static_cast<int64_t>(reinterpret_cast<uintptr_t>(base)), rows, cols, ld,
-                    box_cols, box_rows}};
+                    box_cols, box_rows + (fp32 ? (1 << 20) : 0)}};
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
     auto it = g_map_cache.find(key);
@@ -70,18 +74,32 @@ bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int6
     }
   }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld * esize)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   std::lock_guard<std::mutex> lock(g_map_mutex);
   if (g_map_cache.size() >= kMapCacheLimit) g_map_cache.clear();
   g_map_cache.emplace(key, *map);
   return true;
 }
+
+}  // namespace
+
+bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
+                          int64_t ld, int box_cols, int box_rows) {
+  return make_tensor_map(map, base, rows, cols, ld, box_cols, box_rows, false);
+}
+
+namespace {
+std::atomic<int64_t> g_launches{0};
+}
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int64_t launches_total() { return g_launches.load(std::memory_order_relaxed); }
 
 int sm_count() {
   static int n = [] {
@@ -202,6 +220,17 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   ep.scatter_seq_local = c.scatter_seq_local;
   ep.scatter_broadcast = c.scatter_broadcast ? 1 : 0;
   for (int i = 0; i < 8; ++i) ep.scatter_out[i] = i < ep.scatter_degree ? c.scatter_out[i] : nullptr;
+  // Plain outputs leave through TMA stores of 32 x 128-byte boxes (32 fp32 or 64 bf16 columns).
+  // `staged_store` = -1 in the call keeps the per-thread row stores (tests compare the two).
+  CUtensorMap tc = ta;
+  ep.staged_store = 0;
+  if (c.staged_store >= 0 && ep.scatter_degree == 0 && ep.gated_inter == 0 && !c.accumulate &&
+      (c.ldo * (c.out_fp32 ? 4 : 2)) % 16 == 0) {
+    if (make_tensor_map(&tc, c.out, c.M, c.N, c.ldo, c.out_fp32 ? 32 : 64, 32, c.out_fp32))
+      ep.staged_store = 1;
+    else
+      tc = ta;
+  }
 
   constexpr int smem = GemmSmem<BN>::kTotal;
   const int m_tiles = (c.M + kGemmBM - 1) / kGemmBM;
@@ -241,8 +270,9 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
         attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       });
       if (attr_err != cudaSuccess) return attr_err;
-      kernel<<<grid, kGemmThreads + kPullThreads, smem, stream>>>(ta, tb, ep, sp, pull, c.M, c.N,
-                                                                 c.K, status);
+      kernel<<<grid, kGemmThreads + kPullThreads, smem, stream>>>(ta, tb, tc, ep, sp, pull, c.M,
+                                                                 c.N, c.K, status);
+      count_launch();
       return cudaGetLastError();
     }
   }
@@ -253,7 +283,8 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
     attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return attr_err;
-  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, ep, sp, c.M, c.N, c.K, status);
+  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, tc, ep, sp, c.M, c.N, c.K, status);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -43,6 +43,11 @@ struct GemmEpilogue {
   // Broadcast variant (tensor parallelism without sequence parallelism: the partial sums are
   // all-reduced, every rank needs every row): row m is stored at row m of *every* scatter_out.
   int scatter_broadcast;
+  // Staged store: the epilogue warps transpose each 32-row band through 128B-swizzled shared
+  // memory and hand whole 32 x 128-byte boxes to TMA stores (`tma_c`), instead of every thread
+  // storing 16-byte pieces of its own row.  Set by the launcher for plain bf16 / fp32 outputs
+  // (no scatter, no gating, no accumulate) whose base and pitch TMA accepts.
+  int staged_store;
 };
 
 // Tail split.  A persistent grid of G CTAs runs floor(tiles / G) full waves of whole tiles; the
@@ -104,14 +109,19 @@ struct GemmSmem {
   // tiles + barriers (full, empty, accumulator full/empty) + tmem pointer + abort flag, plus
   // 1 KB alignment slack
   // + 4 KB per epilogue warp to transpose scattered output rows into 128-byte row segments
+  // (the staging area sits right after the operand tiles, so it is 1 KB aligned as the 128B
+  // swizzle of the TMA stores needs; two buffers per warp where shared memory allows)
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kScatterStageBytes = 4 * 4096;
+  static constexpr int kStoreBufs = (BN == 192) ? 1 : 2;
+  static constexpr int kScatterStageBytes = 4 * kStoreBufs * 4096;
   static constexpr int kTotal = kStages * kStageBytes + 1024 + kBarrierBytes + kScatterStageBytes;
+  static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
 template <int BN, bool A_MN, bool B_MN, bool PULL>
 __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
                                                        const CUtensorMap& tma_b,
+                                                       const CUtensorMap& tma_c,
                                                        const GemmEpilogue& ep, const GemmSplit& sp,
                                                        const GemmPull& pull, int M, int N, int K,
                                                        int* __restrict__ status) {
@@ -127,7 +137,8 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* tiles = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+  uint8_t* store_stage = smem + STAGES * S::kStageBytes;   // [4 warps][kStoreBufs][4 KB]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(store_stage + S::kScatterStageBytes);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;   // [2]
   uint64_t* acc_empty = acc_full + 2;        // [2], 128 arrivals each
@@ -180,6 +191,7 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
     fence_proxy_async();
     prefetch_tensormap(&tma_a);
     prefetch_tensormap(&tma_b);
+    if (ep.staged_store) prefetch_tensormap(&tma_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, S::kTmemCols);
@@ -369,6 +381,7 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
     const int q = warp & 3;
     const int row = q * 32 + lane;
     int local = 0;
+    int sbuf = 0;          // staged store: which of this warp's staging buffers is written next
     bool ok = true;
     int* last_flag = reinterpret_cast<int*>(tmem_ptr + 2);   // shared: "this CTA reduces the tile"
     for (int unit = blockIdx.x; unit < sp.total_units; unit += gridDim.x, ++local) {
@@ -381,6 +394,7 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
       const uint32_t tmem_d = tmem_base + ab * BN;
       const int64_t g_row = static_cast<int64_t>(m0) + row;
       const bool row_ok = ok && g_row < M;
+      const bool warp_ok = __all_sync(0xffffffffu, ok);
       // Scatter epilogue: after the shared-memory transpose lane l stores rows 4k + l/8 (k = 0..7)
       // of its warp's 32-row band; their destinations (owner buffer, row inside it) do not
       // depend on the column chunk, so they are resolved once per tile.
@@ -415,8 +429,7 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
           // L2, ruinous for stores that cross NVLink.  The warp's 32x32 block goes through
           // shared memory (XOR-swizzled 16-byte slots, conflict free both ways) and leaves as
           // four full 128-byte row segments per instruction.
-          float* stage = reinterpret_cast<float*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes) +
-                         q * 1024;
+          float* stage = reinterpret_cast<float*>(store_stage) + q * (S::kStoreBufs * 1024);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             float4 x;
@@ -444,6 +457,88 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
             }
           }
           __syncwarp();
+          return;
+        }
+        if (ep.staged_store) {
+          // Staged store.  Rows past M and columns past N may hold anything in shared memory:
+          // the TMA store does not write the part of a box that lies outside the tensor.
+          const int band_row = m0 + q * 32;
+          if (!warp_ok || band_row >= M) return;          // warp-uniform
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ep.alpha;
+          if (ep.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < N) v[i] += __ldg(ep.bias + col0 + i);
+          }
+          uint8_t* stage = store_stage + (q * S::kStoreBufs + sbuf) * 4096;
+          if (ep.out_fp32) {
+            if (ep.residual != nullptr && row_ok) {
+              const float* rs = reinterpret_cast<const float*>(ep.residual) + g_row * ep.ldo + col0;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                if (col0 + i >= N) break;
+                const float4 y = *reinterpret_cast<const float4*>(rs + i);
+                v[i] += y.x; v[i + 1] += y.y; v[i + 2] += y.z; v[i + 3] += y.w;
+              }
+            }
+            // the store that last read this buffer must have finished reading it
+            if (lane == 0) bulk_wait_group_read<S::kStoreBufs - 1>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tma_c, stage, col0, band_row);
+              bulk_commit_group();
+            }
+            sbuf = (sbuf + 1) % S::kStoreBufs;
+            return;
+          }
+          // bf16: two 32-column chunks fill the two halves of one buffer of 128-byte rows
+          if (ep.residual != nullptr && row_ok) {
+            const __nv_bfloat16* rs =
+                reinterpret_cast<const __nv_bfloat16*>(ep.residual) + g_row * ep.ldo + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i >= N) break;
+              const uint4 y = *reinterpret_cast<const uint4*>(rs + i);
+              const __nv_bfloat162* yb = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(yb[j]);
+                v[i + 2 * j] += f.x;
+                v[i + 2 * j + 1] += f.y;
+              }
+            }
+          }
+          const int half = c & 1;
+          if (half == 0) {
+            if (lane == 0) bulk_wait_group_read<S::kStoreBufs - 1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 pk;
+            pk.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+            pk.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+            pk.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+            pk.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+            *reinterpret_cast<uint4*>(stage + lane * 128 + (((half * 4 + j) ^ (lane & 7)) << 4)) = pk;
+          }
+          if (half == 1 || col0 + 32 >= N) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tma_c, stage, col0 - half * 32, band_row);
+              bulk_commit_group();
+            }
+            sbuf = (sbuf + 1) % S::kStoreBufs;
+          }
           return;
         }
         if (!row_ok) return;
@@ -608,6 +703,9 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
         emit(r, c);
       }
     }
+    // this warp's staged stores must have read their shared memory and written their rows
+    // before the CTA retires
+    if (lane == 0) bulk_wait_group<0>();
   }
 
   tc_fence_before_sync();
@@ -621,19 +719,22 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
-                         const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep, GemmSplit sp,
+                         const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_c, GemmEpilogue ep, GemmSplit sp,
                          int M, int N, int K, int* __restrict__ status) {
-  gemm_bf16_tcgen05_body<BN, A_MN, B_MN, false>(tma_a, tma_b, ep, sp, GemmPull{}, M, N, K, status);
+  gemm_bf16_tcgen05_body<BN, A_MN, B_MN, false>(tma_a, tma_b, tma_c, ep, sp, GemmPull{}, M, N, K,
+                                                status);
 }
 
 // The same GEMM with four more warps that pull the A operand from its owners (see GemmPull).
 template <int BN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads + kPullThreads, 1)
 gemm_pull_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
-                              const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep,
+                              const __grid_constant__ CUtensorMap tma_b,
+                              const __grid_constant__ CUtensorMap tma_c, GemmEpilogue ep,
                               GemmSplit sp, GemmPull pull, int M, int N, int K,
                               int* __restrict__ status) {
-  gemm_bf16_tcgen05_body<BN, false, B_MN, true>(tma_a, tma_b, ep, sp, pull, M, N, K, status);
+  gemm_bf16_tcgen05_body<BN, false, B_MN, true>(tma_a, tma_b, tma_c, ep, sp, pull, M, N, K, status);
 }
 
 }  // namespace stb

@@ -511,6 +511,7 @@ cudaError_t launch_gather_params(PeerPtrs shards, int degree, const SegmentDesc*
   dim3 grid(chunks_for(segs, n_segs, false), n_segs);
   gather_params_kernel<<<grid, 256, 0, s>>>(shards, sh, shadows != nullptr ? 1 : 0, degree, tab,
                                             reinterpret_cast<__nv_bfloat16*>(full_bf16), full_fp32);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -534,6 +535,7 @@ cudaError_t launch_reduce_scatter_grads(PeerPtrs full_grads, int degree, int ran
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, nullptr, nullptr, nullptr,
       scale, tp.replicated_scale, accumulate ? 1 : 0, AdamWArgs{}, flags, nullptr, status,
       multicast);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -553,6 +555,7 @@ cudaError_t launch_reduce_scatter_adamw(PeerPtrs full_grads, int degree, int ran
       full_grads, degree, rank, tp.degree, tp.rank, tab, grad_shard, p, m, v, scale,
       tp.replicated_scale, accumulate ? 1 : 0, a, flags,
       reinterpret_cast<__nv_bfloat16*>(shadow), status, multicast);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -561,6 +564,7 @@ cudaError_t launch_embedding_gather_sharded(PeerPtrs shards, int degree, int64_t
                                             cudaStream_t s) {
   if (degree < 1 || degree > kMaxPeers || q < 1) return cudaErrorInvalidValue;
   embedding_gather_sharded_kernel<<<rows, 256, 0, s>>>(shards, degree, q, ids, out, cols);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -573,6 +577,7 @@ cudaError_t launch_seq_gather(const void* const* peers, int degree, void* out, i
   const int grid = static_cast<int>(std::min<int64_t>((total + 1023) / 1024, sm_count() * 8));
   seq_gather_kernel<<<grid, 256, 0, s>>>(vp, degree, reinterpret_cast<uint4*>(out), batch,
                                          seq_local, row_bytes / 16);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -586,6 +591,7 @@ cudaError_t launch_seq_reduce_scatter_f32(const float* const* peers, int degree,
   const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, sm_count() * 8));
   seq_reduce_scatter_kernel<<<grid, 256, 0, s>>>(fp, degree, rank, residual, out, batch, seq_local,
                                                  cols);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -603,6 +609,7 @@ cudaError_t launch_peer_allreduce_small(uint32_t* const* flag_pads, double* cons
   }
   peer_allreduce_small_kernel<<<1, 32, 0, s>>>(fp, ip, degree, rank, epoch, slot, in, out, n,
                                                min_mask, status, budget_ns);
+  count_launch();
   return cudaGetLastError();
 }
 
@@ -613,6 +620,7 @@ cudaError_t launch_peer_barrier(uint32_t* const* flag_pads, int degree, int rank
   FlagPeers fp;
   for (int i = 0; i < degree; ++i) fp.p[i] = flag_pads[i];
   peer_barrier_kernel<<<1, 32, 0, s>>>(fp, degree, rank, epoch, slot, status, budget_ns);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -24,50 +24,22 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
-# kernels launched per op call (ops not listed launch one)
-_KERNELS_PER_CALL = {"colsum_bf16": 2, "attention_bwd": 3, "status_read": 0, "status_reset": 0,
-                     "layer_forward": 10, "layer_backward": 26, "status_tensor": 0,
-                     "layer_forward_sp": 15, "layer_backward_sp": 31,
-                     "layer_forward_tp": 12, "layer_backward_tp": 29,
-                     "peer_alloc": 0, "peer_free": 0, "device_synchronize": 0, "enable_peer_access": 0, "ipc_handle": 0, "ipc_open": 0,
-                     "ipc_close": 0, "tensor_from_ptr": 0}
+class LaunchCounter:
+    """Reads the extension's own launch counter: every kernel launch site of the library counts
+    itself, so `launches` is the exact number of this package's kernels launched by this process."""
 
-
-class CountingOps:
-    """Proxy over `torch.ops.stb` that counts this package's kernel launches (benchmarks)."""
-
-    def __init__(self, namespace):
-        self._ns = namespace
-        self.launches = 0
-        self._cache = {}
-
-    def __getattr__(self, name):
-        fn = self._cache.get(name)
-        if fn is None:
-            target = getattr(self._ns, name)
-            weight = _KERNELS_PER_CALL.get(name, 1)
-
-            def fn(*args, _t=target, _w=weight):
-                self.launches += _w
-                return _t(*args)
-
-            self._cache[name] = fn
-        return fn
-
-
-_counter = None
+    @property
+    def launches(self) -> int:
+        return int(_load_namespace().launch_count())
 
 
 def enable_launch_counting():
-    """Make `load()` return a counting proxy (call before the runtime is registered)."""
-    global _counter
-    if _counter is None:
-        _counter = CountingOps(_load_namespace())
-    return _counter
+    """Counter whose `launches` attribute benchmarks read before and after their timed region."""
+    return LaunchCounter()
 
 
 def load():
-    return _counter if _counter is not None else _load_namespace()
+    return _load_namespace()
 
 
 def _load_namespace():

@@ -63,6 +63,10 @@ def main():
     ap.add_argument("--b-mn", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--flush", type=int, default=0, help="gemm: scrub the L2 between iterations")
+    ap.add_argument("--out-fp32", type=int, default=0, help="gemm: fp32 output (dW / residual stream)")
+    ap.add_argument("--staged", type=int, default=1,
+                    help="gemm: 1 = outputs leave through staged TMA stores, 0 = per-thread row stores")
     ap.add_argument("--owners", type=int, default=2, help="gemm_scatter: sequence owners (local buffers)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=512)
@@ -79,11 +83,12 @@ def main():
     if a.kernel == "gemm":
         A = torch.randn(a.k if a.a_mn else a.m, a.m if a.a_mn else a.k, device=dev).bfloat16()
         B = torch.randn(a.k if a.b_mn else a.n, a.n if a.b_mn else a.k, device=dev).bfloat16()
-        C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        C = torch.empty(a.m, a.n, device=dev, dtype=torch.float32 if a.out_fp32 else torch.bfloat16)
         ms = timed(lambda: ops.gemm(A, B, C, bool(a.a_mn), bool(a.b_mn), None, None, False, 1.0, a.bn,
-                                    a.split_k), a.warmup, a.iters, flush=False)
+                                    a.split_k, bool(a.staged)), a.warmup, a.iters, flush=bool(a.flush))
         tflops = 2 * a.m * a.n * a.k / ms / 1e9
-        out.update(shape=[a.m, a.n, a.k], a_mn=a.a_mn, b_mn=a.b_mn, ms=ms, tflops=tflops,
+        out.update(shape=[a.m, a.n, a.k], a_mn=a.a_mn, b_mn=a.b_mn, out_fp32=a.out_fp32,
+                   staged=a.staged, ms=ms, tflops=tflops, output_gbs=C.numel() * C.element_size() / ms / 1e6,
                    frac_of_burst_cublas=tflops / burst, frac_of_sustained_cublas=tflops / sustained)
     elif a.kernel == "gemm_scatter":
         # row-parallel GEMM with the sequence-scatter epilogue; the owners' receive buffers are

@@ -233,7 +233,7 @@ class ShardedRuntime:
                  backward_prefetch=False, async_grad_rs=False, communication_policy="conservative",
                  directory=None, diagnostics_enabled=True, communication_backend="auto",
                  retain_parameters=False, compute_dtype=None, device_wait_seconds=2.0,
-                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=True, nvls="off"):
+                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=False, nvls="off"):
         self.device = torch.device(device)
         self.reshard_after_forward = reshard_after_forward
         self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
@@ -258,7 +258,9 @@ class ShardedRuntime:
             raise ValueError("fused_allgather must be auto, on or off")
         self.fused_allgather = fused_allgather
         # sm_100a, sequence parallel: the GEMM that consumes a sequence all-gather pulls the
-        # peers' slices itself (one kernel) instead of running after a gather kernel
+        # peers' slices itself (one kernel) instead of running after a gather kernel.  Off by
+        # default: on two B200s the pulling GEMM was 7-9 % slower per training step than the
+        # gather kernel followed by the plain GEMM (its producer has to poll arrival flags)
         self.fused_seq_gather = bool(fused_seq_gather)
         # sm_100a, FSDP-only meshes: reduce gradients inside the NVSwitch (`multimem.ld_reduce`
         # over multicast-bound gradient slots).  "auto": when the fabric grants multicast, else

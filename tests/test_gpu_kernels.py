@@ -77,6 +77,34 @@ def test_tcgen05_gemm(ops, case):
     close_on_edges(out, ref, atol=(2e-4 if out_fp32 else 2e-2) * scale, rtol=1e-5 if out_fp32 else 1e-2)
 
 
+@pytest.mark.parametrize("out_fp32", [False, True], ids=["bf16", "fp32"])
+@pytest.mark.parametrize("shape", [(300, 584, 328, 192), (512, 17920, 512, 256), (130, 40, 64, 128),
+                                   (1000, 520, 264, 0)], ids=lambda s: "x".join(map(str, s)))
+def test_gemm_staged_tma_store_equals_row_stores_and_stays_inside_the_output(ops, shape, out_fp32):
+    """Plain outputs leave through TMA stores of 32-row boxes staged in shared memory.  Same bits
+    as the per-thread row stores; a box that overhangs the ragged edge of the output (rows past
+    M, columns past N) must not touch the memory around it."""
+    M, N, K, bn = shape
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = torch.randn(N, K, device=DEV).bfloat16()
+    dtype = torch.float32 if out_fp32 else torch.bfloat16
+    bias = torch.randn(N, device=DEV)
+    pitch = N + 24                                    # columns N.. of every row are a guard band
+    res = torch.randn(M, pitch, device=DEV).to(dtype)[:, :N]      # same row pitch as the output
+    outs = []
+    for staged in (False, True):
+        plane = torch.full((M + 40, pitch), 7.0, device=DEV, dtype=dtype)
+        out = plane[:M, :N]
+        ops.gemm(a, b, out, False, False, bias, res, False, 1.0, bn, 1, staged)
+        assert torch.all(plane[M:] == 7.0) and torch.all(plane[:, N:] == 7.0)
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1])
+    want = a.float() @ b.float().t() + bias + res.float()
+    close_on_edges(outs[1], want, atol=(2e-4 if out_fp32 else 2e-2) * math.sqrt(K),
+                   rtol=1e-5 if out_fp32 else 1e-2)
+
+
 SPLIT_CASES = [
     # M, N, K, a_mn, b_mn, out_fp32, bias, residual, force_bn, split_k
     (512, 1536, 8960, False, False, True, False, True, 256, 0),     # 24 tiles -> 6-way split

@@ -18,8 +18,8 @@ CASES = [
     ("fsdp2", 2, ["--fsdp", 2, "--shape", "d128"]),
     ("fsdp2_untied", 2, ["--fsdp", 2, "--shape", "d128", "--tied", 0]),
     ("tp2_sp", 2, ["--fsdp", 1, "--tp", 2, "--sp", 1, "--shape", "d128tp"]),
-    ("tp2_sp_gather_kernel", 2, ["--fsdp", 1, "--tp", 2, "--sp", 1, "--shape", "d128tp",
-                                 "--seq-pull", 0]),
+    ("tp2_sp_pulling_gemm", 2, ["--fsdp", 1, "--tp", 2, "--sp", 1, "--shape", "d128tp",
+                                "--seq-pull", 1]),
     ("tp2", 2, ["--fsdp", 1, "--tp", 2, "--sp", 0, "--shape", "d128tp"]),
     ("fsdp2_tp2_sp", 4, ["--fsdp", 2, "--tp", 2, "--sp", 1, "--shape", "d128tp"]),
     ("fsdp2_tp2", 4, ["--fsdp", 2, "--tp", 2, "--sp", 0, "--shape", "d128tp", "--tied", 0]),
@@ -31,7 +31,7 @@ CASES = [
     # gradient reduce-scatter through the NVSwitch (multimem.ld_reduce); healthy run only
     ("fsdp2_nvls", 2, ["--fsdp", 2, "--shape", "d128", "--nvls", "auto"]),
     ("fsdp2_tp2_sp_pull", 4, ["--fsdp", 2, "--tp", 2, "--sp", 1, "--shape", "d128tp",
-                              "--fused-allgather", "on"]),
+                              "--fused-allgather", "on", "--seq-pull", 1]),
 ]
 
 

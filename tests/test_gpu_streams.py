@@ -84,10 +84,17 @@ def test_delayed_next_unit_gather_blocks_neither_the_reduce_scatter_nor_its_cons
     sees its data (host launch order is not a completion wait)."""
     comm = coordinator("stream_ordered")
     compute = comm.streams["compute"]
+    # the first use of a kernel loads its module on the host (tens of milliseconds): run every op
+    # of the timed part once, so that what is timed below is device ordering, not the host
+    warm = timed_collective(comm, "tp", "fake_seq_reduce_scatter", "sp_rs", delay=1000)
+    with torch.cuda.stream(compute):
+        comm.consume(warm[0], consumer="warm_up")
+        assert ((warm[3] * 2).sum().item(), (warm[3] + 1).sum().item()) == (8, 8)
     torch.cuda.synchronize()
     origin = torch.cuda.Event(enable_timing=True)
     origin.record()
-    gather = timed_collective(comm, "fsdp", "fake_param_gather", "fsdp_ag", delay=4 * DELAY_CYCLES)
+    # ~30 ms of device sleep: far longer than any hiccup of the host between the launches below
+    gather = timed_collective(comm, "fsdp", "fake_param_gather", "fsdp_ag", delay=20 * DELAY_CYCLES)
     scatter = timed_collective(comm, "tp", "fake_seq_reduce_scatter", "sp_rs", delay=0)
     with torch.cuda.stream(compute):
         comm.consume(scatter[0], consumer="row_linear_output")

@@ -35,7 +35,7 @@ def main():
     ap.add_argument("--backend", default="auto")
     ap.add_argument("--fused-allgather", default="auto")
     ap.add_argument("--wire", default="bf16")
-    ap.add_argument("--seq-pull", type=int, default=1)
+    ap.add_argument("--seq-pull", type=int, default=0)
     ap.add_argument("--nvls", default="off")
     ap.add_argument("--inject-inf-rank", type=int, default=-1,
                     help="this rank poisons one shard gradient with inf in step 1 (host-side injection)")
