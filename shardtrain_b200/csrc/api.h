@@ -105,6 +105,17 @@ cudaError_t launch_sgd(float* p, const float* g, int64_t n, float lr, cudaStream
 cudaError_t launch_grad_check(const float* g, int64_t n, const int64_t* pad_ranges, int n_ranges,
                               int* flags, cudaStream_t s);
 
+// Packing for the library-collective (NCCL) path: `table` is an int64 device tensor with one row
+// {start in slot, shard length q, numel, offset in the flat output} per parameter of the unit.
+// unpack: rank-major gather buffer [degree, slot] -> the unit's parameters, contiguous in `out`.
+// pack: full gradients (device array of pointers) -> destination-major [degree, slot], zero padded.
+// `largest`: the largest numel (unpack) or shard length q (pack) in the table, for the grid size.
+cudaError_t launch_unpack_gathered(const float* packed, int64_t slot, const int64_t* table,
+                                   int n_params, int64_t largest, float* out, cudaStream_t s);
+cudaError_t launch_pack_gradients(const int64_t* grads, const int64_t* table, int n_params, int degree,
+                                  int64_t slot, int64_t used, int64_t largest, float* packed,
+                                  cudaStream_t s);
+
 // ------------------------------------------------------------------ shard <-> full (peer.cu)
 // One entry per parameter of a unit.  The FSDP shard of parameter j on rank r is elements
 // [r*q, min((r+1)*q, numel)) of the TP-local flattened tensor, stored at shard_off in every

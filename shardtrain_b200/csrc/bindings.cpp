@@ -440,6 +440,38 @@ void sgd(Tensor p, const Tensor& g, double lr) {
         "sgd");
 }
 
+void unpack_gathered(const Tensor& packed, int64_t slot, const Tensor& table, int64_t largest,
+                     Tensor out) {
+  need(packed, at::kFloat, "packed");
+  need(out, at::kFloat, "out");
+  need(table, at::kLong, "table");
+  TORCH_CHECK(table.dim() == 2 && table.size(1) == 4 && table.is_contiguous(), "table must be [n, 4]");
+  TORCH_CHECK(packed.is_contiguous() && out.is_contiguous() && packed.numel() % slot == 0,
+              "packed buffer must be whole rank slots");
+  const c10::cuda::CUDAGuard guard(packed.device());
+  check(stb::launch_unpack_gathered(packed.data_ptr<float>(), slot, table.data_ptr<int64_t>(),
+                                    static_cast<int>(table.size(0)), largest, out.data_ptr<float>(),
+                                    at::cuda::getCurrentCUDAStream().stream()),
+        "unpack_gathered");
+}
+
+void pack_gradients(const Tensor& grad_ptrs, const Tensor& table, int64_t degree, int64_t slot,
+                    int64_t used, int64_t largest, Tensor packed) {
+  need(grad_ptrs, at::kLong, "grad_ptrs");
+  need(table, at::kLong, "table");
+  need(packed, at::kFloat, "packed");
+  TORCH_CHECK(table.dim() == 2 && table.size(1) == 4 && table.is_contiguous() &&
+                  grad_ptrs.numel() == table.size(0),
+              "table must be [n, 4] with one gradient pointer per row");
+  TORCH_CHECK(packed.is_contiguous() && packed.numel() == degree * slot, "packed has the wrong length");
+  const c10::cuda::CUDAGuard guard(packed.device());
+  check(stb::launch_pack_gradients(grad_ptrs.data_ptr<int64_t>(), table.data_ptr<int64_t>(),
+                                   static_cast<int>(table.size(0)), static_cast<int>(degree), slot,
+                                   used, largest, packed.data_ptr<float>(),
+                                   at::cuda::getCurrentCUDAStream().stream()),
+        "pack_gradients");
+}
+
 void grad_check(const Tensor& g, const Tensor& pad_ranges, Tensor flags) {
   need(g, at::kFloat, "g");
   need(pad_ranges, at::kLong, "pad_ranges");
@@ -877,6 +909,8 @@ TORCH_LIBRARY(stb, m) {
   m.def("peer_free", &peer_free);
   m.def("device_synchronize", &device_synchronize);
   m.def("launch_count", &launch_count);
+  m.def("unpack_gathered", &unpack_gathered);
+  m.def("pack_gradients", &pack_gradients);
   m.def("enable_peer_access", &enable_peer_access);
   m.def("ipc_handle", &ipc_handle);
   m.def("ipc_open", &ipc_open);

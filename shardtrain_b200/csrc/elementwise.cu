@@ -499,6 +499,46 @@ inline int grid_for(int64_t work, int threads, int cap = 0) {
 
 }  // namespace
 
+// ----------------------------------------------------------------------------- NCCL-path packing
+// The library all-gather / reduce-scatter of the portable path work on one packed buffer per
+// unit: `degree` rank slots of `slot` elements, parameter p's shard at [start_p, start_p + q_p)
+// of every slot.  One launch per unit moves all its parameters (table rows: start, q, numel,
+// offset in the flat output).
+__global__ void unpack_gathered_kernel(const float* __restrict__ packed, int64_t slot,
+                                       const int64_t* __restrict__ table, float* __restrict__ out) {
+  const int64_t* row = table + 4 * blockIdx.y;
+  const int64_t start = row[0], q = row[1], numel = row[2], off = row[3];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < numel; i += stride) {
+    const int64_t r = i / q;
+    out[off + i] = packed[r * slot + start + (i - r * q)];
+  }
+}
+
+// Full gradients (one pointer per parameter) -> destination-major reduce-scatter input with zero
+// padding.  blockIdx.y == n_params clears the unused tail [used, slot) of every rank slot.
+__global__ void pack_gradients_kernel(const int64_t* __restrict__ grads,
+                                      const int64_t* __restrict__ table, int n_params, int degree,
+                                      int64_t slot, int64_t used, float* __restrict__ packed) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (static_cast<int>(blockIdx.y) == n_params) {
+    const int64_t pad = slot - used;
+    for (int64_t i = first; i < pad * degree; i += stride) {
+      const int64_t r = i / pad;
+      packed[r * slot + used + (i - r * pad)] = 0.f;
+    }
+    return;
+  }
+  const int64_t* row = table + 4 * blockIdx.y;
+  const int64_t start = row[0], q = row[1], numel = row[2];
+  const float* g = reinterpret_cast<const float*>(grads[blockIdx.y]);
+  for (int64_t i = first; i < q * degree; i += stride) {
+    const int64_t r = i / q;
+    packed[r * slot + start + (i - r * q)] = i < numel ? g[i] : 0.f;
+  }
+}
+
 cudaError_t launch_rmsnorm_fwd(const float* x, const float* w, void* y, float* inv, int rows,
                                int cols, float eps, bool y_fp32, cudaStream_t s) {
   if (cols % 4) return cudaErrorInvalidValue;
@@ -648,6 +688,25 @@ cudaError_t launch_sgd(float* p, const float* g, int64_t n, float lr, cudaStream
 cudaError_t launch_grad_check(const float* g, int64_t n, const int64_t* pad_ranges, int n_ranges,
                               int* flags, cudaStream_t s) {
   grad_check_kernel<<<grid_for(n, 256, sm_count() * 8), 256, 0, s>>>(g, n, pad_ranges, n_ranges, flags);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_unpack_gathered(const float* packed, int64_t slot, const int64_t* table,
+                                   int n_params, int64_t largest, float* out, cudaStream_t s) {
+  if (n_params < 1 || slot < 1) return cudaErrorInvalidValue;
+  dim3 grid(grid_for(largest, 256, sm_count() * 4), n_params);
+  unpack_gathered_kernel<<<grid, 256, 0, s>>>(packed, slot, table, out);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_gradients(const int64_t* grads, const int64_t* table, int n_params, int degree,
+                                  int64_t slot, int64_t used, int64_t largest, float* packed,
+                                  cudaStream_t s) {
+  if (n_params < 1 || degree < 1 || slot < used) return cudaErrorInvalidValue;
+  dim3 grid(grid_for(largest * degree, 256, sm_count() * 4), n_params + 1);
+  pack_gradients_kernel<<<grid, 256, 0, s>>>(grads, table, n_params, degree, slot, used, packed);
   count_launch();
   return cudaGetLastError();
 }

@@ -33,6 +33,7 @@ namespace stb {
 
 bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
                           int64_t ld, int box_cols, int box_rows);
+bool make_bf16_store_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld);
 
 namespace {
 
@@ -50,6 +51,7 @@ struct AgSmem {
   static constexpr int kBStages = BN == 128 ? 5 : 8;
   static constexpr int kBarrierBytes = 512;
   static constexpr int kTotal = kBStages * kBTile + kAStages * kATile + 1024 + kBarrierBytes;
+  static_assert(kBStages * kBTile >= 4 * 12288, "the epilogue stages 12 KB per warp in the weight stages");
 };
 
 struct AgParams {
@@ -62,6 +64,11 @@ struct AgParams {
   int M, N, K;
   int mt;                 // row tiles of A per pass (accumulators alive in TMEM)
   int* status;
+  // Staged epilogue: 32 x 32 bf16 boxes leave through TMA stores from shared memory (the weight
+  // stages, which are idle once a pass's MMAs have completed).  Plain mode uses `map_out`; gated
+  // mode one map per plane (gate half, up half, product).
+  int staged;
+  CUtensorMap map_out, map_up, map_h;
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
@@ -447,9 +454,16 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
         if (ok) ok = mbar_wait(acc_full, round & 1, p.status, kErrEpilogueAccumWait);
         tc_fence_after_sync();
         const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+        // Every MMA of this pass has completed (acc_full), so every thread's mirror reads of the
+        // weight stages have too (a stage is handed over only after them): the stage memory is
+        // free until the next pass and serves as the staging area, 12 KB per warp.
+        const bool staged = p.staged != 0 && __all_sync(0xffffffffu, ok);
+        uint8_t* stage_base = b_tiles + q4 * 12288;
+        int issued = 0;
         for (int m = 0; m < m_count && ok; ++m) {
           const int64_t g_row = static_cast<int64_t>(m_first + m) * kBM + row_in_tile;
           const bool row_ok = g_row < p.M;
+          const int band_row = (m_first + m) * kBM + q4 * 32;
           const uint32_t acc = tmem_base + lane_base + m * BN;
           if (gated) {
             __nv_bfloat16* gu_row = reinterpret_cast<__nv_bfloat16*>(p.out) + g_row * p.ldo;
@@ -461,10 +475,18 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
               tmem_ld_32x32(acc + BN / 2 + c * 32, ru);
               tmem_ld_wait();
               const int col0 = n0 + c * 32;
-              if (!row_ok || col0 >= p.gated_inter) continue;
+              if (staged ? (band_row >= p.M || col0 >= p.gated_inter)
+                         : (!row_ok || col0 >= p.gated_inter))
+                continue;
+              // staged: two sets of three 2 KB boxes per warp, one bulk group per chunk
+              uint8_t* slot = stage_base + (issued & 1) * 6144;
+              if (staged) {
+                if (lane == 0) bulk_wait_group_read<1>();
+                __syncwarp();
+              }
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
-                if (col0 + i >= p.gated_inter) break;
+                if (!staged && col0 + i >= p.gated_inter) break;
                 uint4 pg, pu, ph;
                 uint32_t* wg = &pg.x;
                 uint32_t* wu = &pu.x;
@@ -480,9 +502,27 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
                   const float sy = __bfloat162float(__float2bfloat16(g.y / (1.f + __expf(-g.y))));
                   wh[j] = pack_bf16x2(sx * u.x, sy * u.y);
                 }
-                *reinterpret_cast<uint4*>(gu_row + col0 + i) = pg;
-                *reinterpret_cast<uint4*>(gu_row + p.gated_inter + col0 + i) = pu;
-                *reinterpret_cast<uint4*>(h_row + col0 + i) = ph;
+                if (staged) {
+                  const int at = lane * 64 + (((i >> 3) ^ ((lane >> 1) & 3)) << 4);
+                  *reinterpret_cast<uint4*>(slot + at) = pg;
+                  *reinterpret_cast<uint4*>(slot + 2048 + at) = pu;
+                  *reinterpret_cast<uint4*>(slot + 4096 + at) = ph;
+                } else {
+                  *reinterpret_cast<uint4*>(gu_row + col0 + i) = pg;
+                  *reinterpret_cast<uint4*>(gu_row + p.gated_inter + col0 + i) = pu;
+                  *reinterpret_cast<uint4*>(h_row + col0 + i) = ph;
+                }
+              }
+              if (staged) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_2d(&p.map_out, slot, col0, band_row);
+                  tma_store_2d(&p.map_up, slot + 2048, col0, band_row);
+                  tma_store_2d(&p.map_h, slot + 4096, col0, band_row);
+                  bulk_commit_group();
+                }
+                ++issued;
               }
             }
           } else {
@@ -492,7 +532,7 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
               tmem_ld_32x32(acc + c * 32, r);
               tmem_ld_wait();
               const int col0 = n0 + c * 32;
-              if (!row_ok || col0 >= p.N) continue;
+              if (staged ? (band_row >= p.M || col0 >= p.N) : (!row_ok || col0 >= p.N)) continue;
               float v[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -500,6 +540,30 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                   if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+              }
+              if (staged) {
+                // four 2 KB boxes per warp in rotation, one bulk group each
+                uint8_t* slot = stage_base + (issued & 3) * 2048;
+                if (lane == 0) bulk_wait_group_read<3>();
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 pk;
+                  pk.x = pack_bf16x2(v[i], v[i + 1]);
+                  pk.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                  pk.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                  pk.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                  *reinterpret_cast<uint4*>(slot + lane * 64 +
+                                            (((i >> 3) ^ ((lane >> 1) & 3)) << 4)) = pk;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_2d(&p.map_out, slot, col0, band_row);
+                  bulk_commit_group();
+                }
+                ++issued;
+                continue;
               }
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + g_row * p.ldo + col0;
 #pragma unroll
@@ -517,9 +581,15 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         tc_fence_before_sync();
         mbar_arrive(acc_empty);   // TMEM reads done (or skipped): the MMA warp may start the next round
+        if (p.staged != 0) {
+          // the stores must have read their boxes before any producer refills the weight stages
+          if (lane == 0) bulk_wait_group_read<0>();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
       }
     }
     cp_async_wait<0>();
+    if (lane == 0) bulk_wait_group<0>();   // staged stores written before the CTA retires
   }
 
   tc_fence_before_sync();
@@ -546,6 +616,15 @@ cudaError_t launch_bn(const AgGemmCall& c, int mt, int* status, cudaStream_t str
   p.K = c.K;
   p.mt = mt;
   p.status = status;
+  p.map_out = p.map_up = p.map_h = ta;
+  if (p.gated_inter > 0) {
+    const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(c.out);
+    p.staged = make_bf16_store_map(&p.map_out, gu, c.M, p.gated_inter, c.ldo) &&
+               make_bf16_store_map(&p.map_up, gu + p.gated_inter, c.M, p.gated_inter, c.ldo) &&
+               make_bf16_store_map(&p.map_h, c.gated_out, c.M, p.gated_inter, p.gated_inter);
+  } else {
+    p.staged = make_bf16_store_map(&p.map_out, c.out, c.M, c.N, c.ldo);
+  }
   auto kernel = gemm_allgather_kernel<BN>;
   constexpr int smem = AgSmem<BN>::kTotal;
   static std::once_flag once;

@@ -58,13 +58,16 @@ constexpr size_t kMapCacheLimit = 8192;
 
 namespace {
 
+enum MapKind { kMapBf16 = 0, kMapF32 = 1, kMapBf16Swizzle64 = 2 };
+
 bool make_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
-                     int box_cols, int box_rows, bool fp32) {
+                     int box_cols, int box_rows, MapKind kind) {
   EncodeTiledFn fn = encode_tiled();
   if (fn == nullptr) return false;
+  const bool fp32 = kind == kMapF32;
   const int64_t esize = fp32 ? 4 : 2;
   const MapKey key{{static_cast<int64_t>(reinterpret_cast<uintptr_t>(base)), rows, cols, ld,
-                    box_cols, box_rows + (fp32 ? (1 << 20) : 0)}};
+                    box_cols, box_rows + (static_cast<int64_t>(kind) << 20)}};
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
     auto it = g_map_cache.find(key);
@@ -79,7 +82,8 @@ bool make_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t c
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  kind == kMapBf16Swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -92,7 +96,14 @@ bool make_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t c
 
 bool make_bf16_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
                           int64_t ld, int box_cols, int box_rows) {
-  return make_tensor_map(map, base, rows, cols, ld, box_cols, box_rows, false);
+  return make_tensor_map(map, base, rows, cols, ld, box_cols, box_rows, kMapBf16);
+}
+
+// Map for staged epilogue stores of bf16 planes: boxes of 32 rows x 32 columns (64-byte rows,
+// 64B swizzle).
+bool make_bf16_store_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
+                         int64_t ld) {
+  return make_tensor_map(map, base, rows, cols, ld, 32, 32, kMapBf16Swizzle64);
 }
 
 namespace {
@@ -222,14 +233,29 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
   for (int i = 0; i < 8; ++i) ep.scatter_out[i] = i < ep.scatter_degree ? c.scatter_out[i] : nullptr;
   // Plain outputs leave through TMA stores of 32 x 128-byte boxes (32 fp32 or 64 bf16 columns).
   // `staged_store` = -1 in the call keeps the per-thread row stores (tests compare the two).
-  CUtensorMap tc = ta;
+  // The SwiGLU epilogue stores 32-column boxes (64-byte rows, 64B swizzle) of three planes: the
+  // gate half and the up half of `out` (a map each, so that a box at the ragged end of the gate
+  // half cannot spill into the up half) and `gated_out`.
+  CUtensorMap tc = ta, tc_up = ta, tc_h = ta;
   ep.staged_store = 0;
-  if (c.staged_store >= 0 && ep.scatter_degree == 0 && ep.gated_inter == 0 && !c.accumulate &&
+  if (c.staged_store >= 0 && ep.scatter_degree == 0 && !c.accumulate &&
       (c.ldo * (c.out_fp32 ? 4 : 2)) % 16 == 0) {
-    if (make_tensor_map(&tc, c.out, c.M, c.N, c.ldo, c.out_fp32 ? 32 : 64, 32, c.out_fp32))
+    bool made;
+    if (ep.gated_inter > 0) {
+      const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(c.out);
+      made = make_tensor_map(&tc, gu, c.M, ep.gated_inter, c.ldo, 32, 32, kMapBf16Swizzle64) &&
+             make_tensor_map(&tc_up, gu + ep.gated_inter, c.M, ep.gated_inter, c.ldo, 32, 32,
+                             kMapBf16Swizzle64) &&
+             make_tensor_map(&tc_h, c.gated_out, c.M, ep.gated_inter, ep.gated_inter, 32, 32,
+                             kMapBf16Swizzle64);
+    } else {
+      made = make_tensor_map(&tc, c.out, c.M, c.N, c.ldo, c.out_fp32 ? 32 : 64, 32,
+                             c.out_fp32 ? kMapF32 : kMapBf16);
+    }
+    if (made)
       ep.staged_store = 1;
     else
-      tc = ta;
+      tc = tc_up = tc_h = ta;
   }
 
   constexpr int smem = GemmSmem<BN>::kTotal;
@@ -270,8 +296,8 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
         attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       });
       if (attr_err != cudaSuccess) return attr_err;
-      kernel<<<grid, kGemmThreads + kPullThreads, smem, stream>>>(ta, tb, tc, ep, sp, pull, c.M,
-                                                                 c.N, c.K, status);
+      kernel<<<grid, kGemmThreads + kPullThreads, smem, stream>>>(ta, tb, tc, tc_up, tc_h, ep, sp,
+                                                                 pull, c.M, c.N, c.K, status);
       count_launch();
       return cudaGetLastError();
     }
@@ -283,7 +309,8 @@ cudaError_t launch_variant(const GemmCall& c, int* status, cudaStream_t stream) 
     attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return attr_err;
-  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, tc, ep, sp, c.M, c.N, c.K, status);
+  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, tc, tc_up, tc_h, ep, sp, c.M, c.N, c.K,
+                                               status);
   count_launch();
   return cudaGetLastError();
 }

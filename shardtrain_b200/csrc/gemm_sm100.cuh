@@ -122,6 +122,8 @@ template <int BN, bool A_MN, bool B_MN, bool PULL>
 __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
                                                        const CUtensorMap& tma_b,
                                                        const CUtensorMap& tma_c,
+                                                       const CUtensorMap& tma_c_up,
+                                                       const CUtensorMap& tma_c_h,
                                                        const GemmEpilogue& ep, const GemmSplit& sp,
                                                        const GemmPull& pull, int M, int N, int K,
                                                        int* __restrict__ status) {
@@ -191,7 +193,13 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
     fence_proxy_async();
     prefetch_tensormap(&tma_a);
     prefetch_tensormap(&tma_b);
-    if (ep.staged_store) prefetch_tensormap(&tma_c);
+    if (ep.staged_store) {
+      prefetch_tensormap(&tma_c);
+      if (ep.gated_inter > 0) {
+        prefetch_tensormap(&tma_c_up);
+        prefetch_tensormap(&tma_c_h);
+      }
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, S::kTmemCols);
@@ -612,10 +620,21 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
           tmem_ld_32x32(tmem_d + lane_base + BN / 2 + c * 32, ru);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
-          if (!row_ok || col0 >= ep.gated_inter) continue;
+          const bool staged = ep.staged_store != 0;        // warp-uniform
+          if (staged ? (!warp_ok || m0 + q * 32 >= M || col0 >= ep.gated_inter)
+                     : (!row_ok || col0 >= ep.gated_inter))
+            continue;
+          // Staged: three 32 x 64-byte boxes (gate, up, product) in 64B-swizzled shared memory,
+          // one bulk group per chunk; the previous chunk's boxes were read while this chunk's
+          // values were computed above.
+          uint8_t* slot = store_stage + q * (S::kStoreBufs * 4096);
+          if (staged) {
+            if (lane == 0) bulk_wait_group_read<0>();
+            __syncwarp();
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
-            if (col0 + i >= ep.gated_inter) break;
+            if (!staged && col0 + i >= ep.gated_inter) break;
             uint4 pg, pu, ph;
             uint32_t* wg = &pg.x;
             uint32_t* wu = &pu.x;
@@ -631,9 +650,27 @@ __device__ __forceinline__ void gemm_bf16_tcgen05_body(const CUtensorMap& tma_a,
               const float sy = __bfloat162float(__float2bfloat16(g.y / (1.f + __expf(-g.y))));
               wh[j] = pack_bf16x2(sx * u.x, sy * u.y);
             }
-            *reinterpret_cast<uint4*>(gu_row + col0 + i) = pg;
-            *reinterpret_cast<uint4*>(gu_row + ep.gated_inter + col0 + i) = pu;
-            *reinterpret_cast<uint4*>(h_row + col0 + i) = ph;
+            if (staged) {
+              const int at = lane * 64 + (((i >> 3) ^ ((lane >> 1) & 3)) << 4);
+              *reinterpret_cast<uint4*>(slot + at) = pg;
+              *reinterpret_cast<uint4*>(slot + 2048 + at) = pu;
+              *reinterpret_cast<uint4*>(slot + 4096 + at) = ph;
+            } else {
+              *reinterpret_cast<uint4*>(gu_row + col0 + i) = pg;
+              *reinterpret_cast<uint4*>(gu_row + ep.gated_inter + col0 + i) = pu;
+              *reinterpret_cast<uint4*>(h_row + col0 + i) = ph;
+            }
+          }
+          if (staged) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              const int band_row = m0 + q * 32;
+              tma_store_2d(&tma_c, slot, col0, band_row);
+              tma_store_2d(&tma_c_up, slot + 2048, col0, band_row);
+              tma_store_2d(&tma_c_h, slot + 4096, col0, band_row);
+              bulk_commit_group();
+            }
           }
         }
         tc_fence_before_sync();
@@ -720,10 +757,12 @@ template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                          const __grid_constant__ CUtensorMap tma_b,
-                         const __grid_constant__ CUtensorMap tma_c, GemmEpilogue ep, GemmSplit sp,
+                         const __grid_constant__ CUtensorMap tma_c,
+                         const __grid_constant__ CUtensorMap tma_c_up,
+                         const __grid_constant__ CUtensorMap tma_c_h, GemmEpilogue ep, GemmSplit sp,
                          int M, int N, int K, int* __restrict__ status) {
-  gemm_bf16_tcgen05_body<BN, A_MN, B_MN, false>(tma_a, tma_b, tma_c, ep, sp, GemmPull{}, M, N, K,
-                                                status);
+  gemm_bf16_tcgen05_body<BN, A_MN, B_MN, false>(tma_a, tma_b, tma_c, tma_c_up, tma_c_h, ep, sp,
+                                                GemmPull{}, M, N, K, status);
 }
 
 // The same GEMM with four more warps that pull the A operand from its owners (see GemmPull).
@@ -731,10 +770,13 @@ template <int BN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads + kPullThreads, 1)
 gemm_pull_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                               const __grid_constant__ CUtensorMap tma_b,
-                              const __grid_constant__ CUtensorMap tma_c, GemmEpilogue ep,
+                              const __grid_constant__ CUtensorMap tma_c,
+                              const __grid_constant__ CUtensorMap tma_c_up,
+                              const __grid_constant__ CUtensorMap tma_c_h, GemmEpilogue ep,
                               GemmSplit sp, GemmPull pull, int M, int N, int K,
                               int* __restrict__ status) {
-  gemm_bf16_tcgen05_body<BN, false, B_MN, true>(tma_a, tma_b, tma_c, ep, sp, pull, M, N, K, status);
+  gemm_bf16_tcgen05_body<BN, false, B_MN, true>(tma_a, tma_b, tma_c, tma_c_up, tma_c_h, ep, sp, pull,
+                                                M, N, K, status);
 }
 
 }  // namespace stb

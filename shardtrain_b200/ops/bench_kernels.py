@@ -51,7 +51,7 @@ def timed(fn, warmup, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_scatter", "gemm_allgather", "gemm_seq_pull",
+    ap.add_argument("kernel", choices=["gemm", "gemm_swiglu", "gemm_scatter", "gemm_allgather", "gemm_seq_pull",
                                        "attention",
                                        "reduce_scatter_adamw", "gather_params", "gather_shadow",
                                        "rmsnorm"])
@@ -90,6 +90,23 @@ def main():
         out.update(shape=[a.m, a.n, a.k], a_mn=a.a_mn, b_mn=a.b_mn, out_fp32=a.out_fp32,
                    staged=a.staged, ms=ms, tflops=tflops, output_gbs=C.numel() * C.element_size() / ms / 1e6,
                    frac_of_burst_cublas=tflops / burst, frac_of_sustained_cublas=tflops / sustained)
+    elif a.kernel == "gemm_swiglu":
+        # gate|up projection: SwiGLU in the GEMM epilogue against GEMM + SwiGLU kernel (--n = 2 x inter)
+        inter = a.n // 2
+        A = torch.randn(a.m, a.k, device=dev).bfloat16()
+        W = (torch.randn(2 * inter, a.k, device=dev) * 0.05).bfloat16()
+        C = torch.empty(a.m, 2 * inter, device=dev, dtype=torch.bfloat16)
+        Hm = torch.empty(a.m, inter, device=dev, dtype=torch.bfloat16)
+
+        def two():
+            ops.gemm(A, W, C, False, False, None, None, False, 1.0, a.bn)
+            ops.swiglu_fwd(C, Hm)
+
+        ms_fused = timed(lambda: ops.gemm_swiglu(A, W, C, Hm), a.warmup, a.iters, flush=bool(a.flush))
+        ms_two = timed(two, a.warmup, a.iters, flush=bool(a.flush))
+        tflops = 2 * a.m * 2 * inter * a.k / ms_fused / 1e9
+        out.update(shape=[a.m, 2 * inter, a.k], fused_ms=ms_fused, gemm_then_swiglu_ms=ms_two,
+                   tflops=tflops, frac_of_sustained_cublas=tflops / sustained)
     elif a.kernel == "gemm_scatter":
         # row-parallel GEMM with the sequence-scatter epilogue; the owners' receive buffers are
         # local tensors here (the multi-GPU path passes peer pointers to the same kernel)

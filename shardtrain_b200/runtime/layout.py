@@ -97,11 +97,52 @@ def offsets(specs: Sequence[ParameterSpec]) -> tuple[list[int], int]:
     return starts, cursor
 
 
+_PACK_TABLES: dict[tuple, tuple[Tensor, list[int]]] = {}
+
+
+def _native_packing(buffer: Tensor, specs: Sequence[ParameterSpec]) -> bool:
+    """The single-launch pack / unpack kernels serve fp32 buffers on a GPU with the extension
+    built; everything else (CPU, other dtypes) takes the torch path below."""
+    if not buffer.is_cuda or buffer.dtype != torch.float32 or not specs:
+        return False
+    from shardtrain_b200 import ops
+
+    return ops.extension_path() is not None and all(s.dtype == torch.float32 for s in specs)
+
+
+def _pack_table(specs: Sequence[ParameterSpec], device) -> tuple[Tensor, list[int]]:
+    """Device table {start in slot, q, numel, offset in the flat output} per parameter, plus the
+    output offsets on the host; built once per unit and device."""
+    key = (tuple(s.param_id for s in specs), tuple(s.numel for s in specs), str(device))
+    hit = _PACK_TABLES.get(key)
+    if hit is None:
+        starts, _ = offsets(specs)
+        rows, cursor, outs = [], 0, []
+        for spec, start in zip(specs, starts):
+            rows.append([start, spec.fsdp_shard_numel, spec.numel, cursor])
+            outs.append(cursor)
+            cursor += _round_up(spec.numel, ALIGN)
+        outs.append(cursor)
+        hit = (torch.tensor(rows, dtype=torch.int64, device=device), outs)
+        _PACK_TABLES[key] = hit
+    return hit
+
+
 def copy_out(storage: Tensor, specs: Sequence[ParameterSpec], degree: int) -> dict[str, Tensor]:
-    """Rank-major packed gather buffer -> one independent tensor per parameter, padding dropped."""
+    """Rank-major packed gather buffer -> one independent tensor per parameter, padding dropped.
+    On a GPU one kernel launch writes all the unit's parameters into one flat buffer (the
+    returned tensors are views of it); elsewhere one copy per parameter."""
     starts, slot = offsets(specs)
     if storage.numel() != degree * slot:
         raise RuntimeError("Packed gather buffer has the wrong length")
+    if _native_packing(storage, specs):
+        from shardtrain_b200 import ops
+
+        table, outs = _pack_table(specs, storage.device)
+        flat = torch.empty(outs[-1], dtype=storage.dtype, device=storage.device)
+        ops.load().unpack_gathered(storage.reshape(-1), slot, table, max(s.numel for s in specs), flat)
+        return {spec.param_id: flat[off : off + spec.numel].view(spec.tp_local_shape)
+                for spec, off in zip(specs, outs)}
     by_rank = storage.view(degree, slot)
     result = {}
     for spec, start in zip(specs, starts):
@@ -115,10 +156,23 @@ def copy_out(storage: Tensor, specs: Sequence[ParameterSpec], degree: int) -> di
 def pack_gradients(grads: Sequence[Tensor], specs: Sequence[ParameterSpec], degree: int) -> Tensor:
     """Full per-parameter gradients -> destination-major, zero padded reduce-scatter input."""
     starts, slot = offsets(specs)
-    packed = grads[0].new_zeros(degree, slot)
-    for grad, spec, start in zip(grads, specs, starts):
+    for grad, spec in zip(grads, specs):
         if tuple(grad.shape) != spec.tp_local_shape or grad.dtype != spec.dtype:
             raise RuntimeError(f"Invalid full gradient: {spec.param_id}")
+    if _native_packing(grads[0], specs):
+        from shardtrain_b200 import ops
+
+        table, _ = _pack_table(specs, grads[0].device)
+        held = [g.contiguous() for g in grads]                  # alive until the launch is queued
+        pointers = torch.tensor([g.data_ptr() for g in held], dtype=torch.int64).to(grads[0].device)
+        packed = torch.empty(degree * slot, dtype=torch.float32, device=grads[0].device)
+        ops.load().pack_gradients(pointers, table, degree, slot, slot,
+                                  max(s.fsdp_shard_numel for s in specs), packed)
+        for g in held:
+            g.record_stream(torch.cuda.current_stream(g.device))
+        return packed
+    packed = grads[0].new_zeros(degree, slot)
+    for grad, spec, start in zip(grads, specs, starts):
         q = spec.fsdp_shard_numel
         flat = grad.reshape(-1)
         whole = spec.numel // q

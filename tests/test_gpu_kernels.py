@@ -706,3 +706,34 @@ def test_sequence_gather_fused_into_gemm_with_emulated_peers(ops, T, B, sl, K, N
     two = torch.empty_like(out)
     ops.gemm(gathered, w, two, False, b_mn, bias, None, False, 1.0, 0)
     assert torch.equal(out, two)      # same tiles, same accumulation order as the plain GEMM
+
+
+@pytest.mark.parametrize("degree", [1, 2, 4, 8])
+def test_packing_kernels_of_the_library_collective_path_match_the_torch_path(ops, degree):
+    """Single-launch unpack of the rank-major gather buffer and pack of the destination-major
+    gradient buffer (fp32, CUDA) against the per-parameter torch copies on the CPU: equal bits,
+    zero padding, odd sizes, a non-contiguous gradient."""
+    from shardtrain_b200.runtime.layout import ParameterSpec, copy_out, offsets, pack_gradients, shard_of
+
+    torch.manual_seed(degree)
+    shapes = [(3, 5), (7,), (2, 2, 3), (1,), (1031, 67), (8, 8)]
+    specs = [ParameterSpec.create(f"p{i}", 0, torch.empty(s), s, "column", degree)
+             for i, s in enumerate(shapes)]
+    tensors = [torch.randn(s) for s in shapes]
+    starts, slot = offsets(specs)
+    storage = torch.zeros(degree * slot)
+    for rank in range(degree):
+        for t, spec, start in zip(tensors, specs, starts):
+            storage[rank * slot + start: rank * slot + start + spec.fsdp_shard_numel] = shard_of(t, spec, rank)
+    before = int(ops.launch_count())
+    got = copy_out(storage.to(DEV), specs, degree)
+    assert int(ops.launch_count()) == before + 1              # one kernel for the whole unit
+    want = copy_out(storage, specs, degree)
+    for spec in specs:
+        assert got[spec.param_id].shape == want[spec.param_id].shape
+        assert torch.equal(got[spec.param_id].cpu(), want[spec.param_id])
+    grads_gpu = [t.to(DEV) for t in tensors]
+    grads_gpu[4] = tensors[4].t().contiguous().to(DEV).t()    # same values, column-major storage
+    assert not grads_gpu[4].is_contiguous()
+    packed = pack_gradients(grads_gpu, specs, degree)
+    assert torch.equal(packed.cpu(), pack_gradients(tensors, specs, degree))
