@@ -159,6 +159,7 @@ def _run(args) -> None:
     hybrid = bench.HYBRID.get(args.gpus) if args.model == "1.5b" else None
     if hybrid is not None and not args.strategy and not args.no_secondary:
         try:
+            bench.next_rendezvous()
             h = _measure(args, *hybrid)
             hv = labels * 1000.0 / h["ms"]
             line["secondary"] = {

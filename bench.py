@@ -165,6 +165,18 @@ def resolve_strategy(args):
 HYBRID = {2: (1, 2, True), 4: (2, 2, True), 8: (4, 2, True)}   # N -> (F, T, SP) second strategy
 
 
+def next_rendezvous():
+    """Call between two process-group sessions of the same processes.  Under torchrun the workers
+    rendezvous on the launcher's own store, which outlives a session: the first session's NCCL
+    ids stay posted there under the very keys the second session uses, and a rank that starts
+    its second session early reads a stale id and connects to a socket that is already closed
+    (the other ranks then wait for it until their timeout).  The second session therefore meets
+    on the next port, on a store that rank 0 creates for it."""
+    if "MASTER_PORT" in os.environ:
+        os.environ["MASTER_PORT"] = str(int(os.environ["MASTER_PORT"]) + 1)
+        os.environ["TORCHELASTIC_USE_AGENT_STORE"] = "False"
+
+
 def measure_ours(args, fsdp, tp, sp):
     """Warm up, then time exactly K steps of one strategy; returns the measurements of this rank
     group (times already reduced to the maximum over ranks)."""
@@ -322,6 +334,7 @@ def run_ours(args):
     hybrid = HYBRID.get(args.gpus) if args.model == "1.5b" else None
     if hybrid is not None and not args.strategy and not args.no_secondary:
         try:
+            next_rendezvous()
             h = measure_ours(args, *hybrid)
             hv = VALID_LABELS_PER_STEP * 1000.0 / h["ms"]
             line["secondary"] = {

@@ -113,7 +113,7 @@ def _native_packing(buffer: Tensor, specs: Sequence[ParameterSpec]) -> bool:
 def _pack_table(specs: Sequence[ParameterSpec], device) -> tuple[Tensor, list[int]]:
     """Device table {start in slot, q, numel, offset in the flat output} per parameter, plus the
     output offsets on the host; built once per unit and device."""
-    key = (tuple(s.param_id for s in specs), tuple(s.numel for s in specs), str(device))
+    key = (tuple((s.param_id, s.numel, s.fsdp_shard_numel) for s in specs), str(device))
     hit = _PACK_TABLES.get(key)
     if hit is None:
         starts, _ = offsets(specs)
