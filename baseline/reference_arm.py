@@ -47,7 +47,7 @@ def _measure(args, fsdp, tp, sp) -> dict:
 
     ours = bench.qwen15b_dict(args, fsdp, tp, sp)
     for key in ("communication_backend", "retain_parameters", "fused_allgather", "wire_dtype",
-                "fused_seq_gather", "nvls"):   # fields the reference lacks
+                "fused_seq_gather", "nvls", "cuda_graphs"):   # fields the reference lacks
         ours["runtime"].pop(key)
     ours["debug"]["output_dir"] = f"/tmp/shardtrain_ref_bench_{os.getpid()}_{fsdp}x{tp}"
     config = config_from_dict(ours)

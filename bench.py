@@ -57,6 +57,8 @@ def parse_args():
                     help="sequence parallel: the pulling GEMM instead of gather kernel + GEMM")
     ap.add_argument("--nvls", default="off", choices=["auto", "off"],
                     help="FSDP-only meshes: reduce gradients in the NVSwitch (multimem.ld_reduce)")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="launch every kernel of a decoder layer instead of replaying CUDA graphs")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the second (hybrid TP/SP) strategy that follows the F{N}T1 pass")
     return ap.parse_args()
@@ -137,7 +139,8 @@ def qwen15b_dict(args, fsdp, tp, sp, device_backend=("cuda", "nccl")):
                         communication_backend=args.backend, retain_parameters=bool(args.retain),
                         fused_allgather=args.fused_allgather,
                         wire_dtype="fp32" if args.fp32_wire else "bf16",
-                        fused_seq_gather=args.seq_pull, nvls=args.nvls),
+                        fused_seq_gather=args.seq_pull, nvls=args.nvls,
+                        cuda_graphs=not args.no_graphs),
         "training": dict(dtype="bf16", optimizer="adamw", lr=1e-5, steps=args.steps,
                          local_batch_size=args.global_batch // fsdp // 2, accumulation_steps=2,
                          seed=1234),
@@ -205,7 +208,7 @@ def measure_ours(args, fsdp, tp, sp):
             communication_backend=rc.communication_backend, retain_parameters=rc.retain_parameters,
             compute_dtype="bf16", device_wait_seconds=config.debug.distributed_timeout_seconds,
             wire_dtype=rc.wire_dtype, fused_allgather=rc.fused_allgather,
-            fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls,
+            fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls, cuda_graphs=rc.cuda_graphs,
         ).register(model, mesh if session.worker.launched else None, sp=sp)
         trainer = QwenTrainer(model, runtime, config.training.lr, dtype="bf16", optimizer="adamw",
                               accumulation_steps=config.training.accumulation_steps)

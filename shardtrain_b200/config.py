@@ -10,7 +10,9 @@ runtime fields are new and default to the reference behaviour: `communication_ba
 gate|up from the owning ranks' shards instead of gathering them first, `wire_dtype`
 ("bf16" | "fp32") picks what the parameter gather moves over NVLink, and `fused_seq_gather`
 lets the GEMM that consumes a sequence all-gather pull the peers' slices itself; `nvls`
-("auto" | "off") allows the gradient reduce-scatter of FSDP-only meshes to run inside the NVSwitch.
+("auto" | "off") allows the gradient reduce-scatter of FSDP-only meshes to run inside the NVSwitch;
+`cuda_graphs` lets the sm_100a executor replay a decoder layer's launch sequence as one CUDA graph
+once its arguments have repeated (FSDP-only meshes).
 
 This module never imports torch.
 """
@@ -81,6 +83,7 @@ class RuntimeConfig:
     wire_dtype: str = "bf16"
     fused_seq_gather: bool = False
     nvls: str = "off"
+    cuda_graphs: bool = True
 
 
 @dataclass(frozen=True)

@@ -14,6 +14,7 @@ int sm_count();
 // Every kernel launch site of this library counts itself: the number of kernels launched by this
 // process so far (benchmarks report the difference over their timed region).
 void count_launch();
+void count_launches(int64_t n);   // a replayed graph of n kernels
 int64_t launches_total();
 
 // ------------------------------------------------------------------ GEMM (gemm_sm100.cu)

@@ -110,6 +110,7 @@ namespace {
 std::atomic<int64_t> g_launches{0};
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+void count_launches(int64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launches_total() { return g_launches.load(std::memory_order_relaxed); }
 
 int sm_count() {

@@ -233,7 +233,8 @@ class ShardedRuntime:
                  backward_prefetch=False, async_grad_rs=False, communication_policy="conservative",
                  directory=None, diagnostics_enabled=True, communication_backend="auto",
                  retain_parameters=False, compute_dtype=None, device_wait_seconds=2.0,
-                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=False, nvls="off"):
+                 wire_dtype="bf16", fused_allgather="auto", fused_seq_gather=False, nvls="off",
+                 cuda_graphs=True):
         self.device = torch.device(device)
         self.reshard_after_forward = reshard_after_forward
         self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
@@ -262,6 +263,10 @@ class ShardedRuntime:
         # default: on two B200s the pulling GEMM was 7-9 % slower per training step than the
         # gather kernel followed by the plain GEMM (its producer has to poll arrival flags)
         self.fused_seq_gather = bool(fused_seq_gather)
+        # sm_100a, FSDP-only meshes: a decoder layer's forward / backward launch sequence is
+        # captured into a CUDA graph the second time it is called with identical arguments and
+        # replayed from then on (activations then live in buffers the executor owns)
+        self.cuda_graphs = bool(cuda_graphs)
         # sm_100a, FSDP-only meshes: reduce gradients inside the NVSwitch (`multimem.ld_reduce`
         # over multicast-bound gradient slots).  "auto": when the fabric grants multicast, else
         # plain peer loads; "off": never bind memory to a multicast object.
@@ -489,12 +494,18 @@ class ShardedRuntime:
         for unit in self.units:
             if unit.state != "GRAD_READY" or unit.reductions != 1:
                 raise RuntimeError(f"Missing gradient readiness U{unit.unit_id}")
+        # sm_100a, a micro-step that is not the last: nothing on the compute stream reads the
+        # gradient arena before the last micro-step's optimizer boundary, and the reductions of
+        # the next micro-step queue behind these on the reduce-scatter stream, so the compute
+        # stream does not have to stand still until the largest unit's reduction has finished
+        stream_waits = not (self.fused is not None and not self.last_microstep
+                            and getattr(self, "defer_gradient_check", False))
         waited = set()
         for name, handle in self.registry.items():
             if handle.grad_step != self.step_id:
                 raise RuntimeError(f"Missing shard Autograd commit {name}")
             event = handle.grad_ready_event
-            if event is not None and id(event) not in waited:
+            if stream_waits and event is not None and id(event) not in waited:
                 waited.add(id(event))
                 self.comm.wait_event(event, dependency_type="DATA_DEP", consumer="optimizer",
                                      param_id=name)

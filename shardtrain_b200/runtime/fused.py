@@ -221,6 +221,12 @@ class FusedExecutor:
         self._scratch = {}
         self.token_grad = torch.zeros(1, dtype=torch.float32, device=runtime.device)
         self.rows_hint = None     # rows of the layer GEMMs' activation, known after the first input
+        # Replay of a layer's launch sequence as a CUDA graph (FSDP-only meshes: the TP / SP
+        # sequences carry barrier epochs that change at every call).  `_forward_open` holds the
+        # layers whose forward has run and whose backward has not: their activations live in
+        # buffers the replay cache owns, so a second forward before the backward must not replay.
+        self.replay = bool(runtime.cuda_graphs) and self.tp_degree == 1
+        self._forward_open = set()
 
     # ------------------------------------------------------------------ fused all-gather -> GEMM
     # `auto` pulls only where one pass over the weights serves every row tile (four 128-row
@@ -578,7 +584,13 @@ class FusedEmbeddingFn(torch.autograd.Function):
         hidden = ex.cfg.hidden_size
         flat = ids.reshape(-1).contiguous()
         ex.rows_hint = flat.numel() * (ex.tp_degree if rt.sp else 1)
-        out = torch.empty((*ids.shape, hidden), dtype=torch.float32, device=rt.device)
+        ex._forward_open.clear()          # a new micro-step's forward begins here
+        if ex.replay:
+            # same address at every micro-step, so the first layer's replay key repeats
+            # (a fresh view each time: autograd attaches this call's node to the object it gets)
+            out = ex.scratch("embedding_out", (*ids.shape, hidden), torch.float32).view(*ids.shape, hidden)
+        else:
+            out = torch.empty((*ids.shape, hidden), dtype=torch.float32, device=rt.device)
         base = handle.arena_offset * 4
         ptrs = [p + base for p in ex.param_peer_ptrs]
         ex.ops.embedding_gather_sharded(ptrs, handle.spec.fsdp_shard_numel, flat, out)
@@ -635,7 +647,8 @@ class FusedNormFn(torch.autograd.Function):
         slot = ex.acquire_grad_slot(unit)
         side = ex.__dict__.pop("_head_dx", None)   # FP32 gradient handed over by the head node
         dy = side if side is not None else grad.reshape(x2.shape).float().contiguous()
-        dx = torch.empty_like(x2)
+        dx = (ex.scratch("final_norm_dx", x2.shape, x2.dtype) if ex.replay
+              else torch.empty_like(x2))      # a stable address for the last layer's replay key
         partial = ex.scratch("norm_partial", (592, x2.shape[1]), torch.float32)
         ex.ops.rmsnorm_bwd(dy, x2, weight, inv, None, dx, partial)
         dw = plan.grad_view(slot.local, name)
@@ -751,9 +764,13 @@ class FusedLayerFn(torch.autograd.Function):
             ctx.save_for_backward(x2, inv1, qkv, attn, lse, x_mid, inv2, gu, hm)
             return out.view(B, S, H)
         # the 10 launches of the forward run from C++ (csrc/layer_executor.cpp)
+        replay = ex.replay and index not in ex._forward_open
+        if ex.replay and torch.is_grad_enabled():
+            ex._forward_open.add(index)
+        ctx.replay = replay
         h1, inv1, qkv, attn, lse, x_mid, h2, inv2, gu, out, hm = ops.layer_forward(
             x2, w_qkv, b_qkv, w_o, w_gu, w_down, ln1, ln2, cos, sin, positions, mask, ex.status,
-            B, S, hq, hkv, cfg.rms_norm_eps, *ag)
+            B, S, hq, hkv, cfg.rms_norm_eps, *ag, replay)
 
         ctx.dims = (B, S, H, inter)
         ctx.save_for_backward(x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm)
@@ -799,7 +816,8 @@ class FusedLayerFn(torch.autograd.Function):
         dx = ops.layer_backward(
             d_out, x2, inv1, h1, qkv, attn, lse, x_mid, inv2, h2, gu, hm, w_qkv, w_o, w_gu, w_down, ln1,
             ln2, gv["down"], gv["gate_up"], gv["ln2"], gv["o"], gv["bias"], gv["qkv"], gv["ln1"], cos,
-            sin, positions, ctx.mask, ex.status, B, S, hq, hkv)
+            sin, positions, ctx.mask, ex.status, B, S, hq, hkv, ctx.replay)
+        ex._forward_open.discard(index)
         return (dx.view(B, S, H), None, None, None, None, None, *([ex.token_grad] * len(plan.names)))
 
     @staticmethod

@@ -37,7 +37,7 @@ def _runtime_rows(config, session):
         async_grad_rs=rc.async_grad_rs, communication_policy=rc.communication_policy,
         directory=session.directory, communication_backend=rc.communication_backend,
         retain_parameters=rc.retain_parameters, fused_allgather=rc.fused_allgather,
-        wire_dtype=rc.wire_dtype, fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls,
+        wire_dtype=rc.wire_dtype, fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls, cuda_graphs=rc.cuda_graphs,
     )
     runtime.register(model, mesh, sp=config.parallel.sp_enabled)
     trainer = ShardedTrainer(model, runtime, tc.lr)

@@ -335,7 +335,7 @@ def run(config: Config, *, warmup: int = 0, profile_mode: str = "off",
                 directory=session.directory, diagnostics_enabled=runtime_events,
                 communication_backend=rc.communication_backend,
                 retain_parameters=rc.retain_parameters, fused_allgather=rc.fused_allgather,
-                wire_dtype=rc.wire_dtype, fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls, compute_dtype=tc.dtype,
+                wire_dtype=rc.wire_dtype, fused_seq_gather=rc.fused_seq_gather, nvls=rc.nvls, cuda_graphs=rc.cuda_graphs, compute_dtype=tc.dtype,
                 device_wait_seconds=config.debug.distributed_timeout_seconds,
             ).register(model, mesh if session.worker.launched else None,
                        sp=config.parallel.sp_enabled)

@@ -7,7 +7,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def build(tied, accumulate=2, optimizer="sgd", lr=0.05, retain=False):
+def build(tied, accumulate=2, optimizer="sgd", lr=0.05, retain=False, graphs=True):
     from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
     from shardtrain_b200.runtime.engine import ShardedRuntime
     from shardtrain_b200.training.qwen2_trainer import QwenTrainer
@@ -19,7 +19,7 @@ def build(tied, accumulate=2, optimizer="sgd", lr=0.05, retain=False):
     model = copy.deepcopy(dense)
     rt = ShardedRuntime(device="cuda:0", reshard_after_forward=True, forward_prefetch=True,
                         backward_prefetch=True, async_grad_rs=True, communication_policy="stream_ordered",
-                        retain_parameters=retain)
+                        retain_parameters=retain, cuda_graphs=graphs)
     rt.register(model)
     assert rt.executor.name == "fused"
     tr = QwenTrainer(model, rt, lr=lr, dtype="bf16", optimizer=optimizer, accumulation_steps=accumulate)
@@ -53,6 +53,42 @@ def test_gradients_match_dense_bf16_autocast(tied):
         assert worst < 8e-2, (name, worst.item())
     assert all(p.ndim == 1 and p.dtype == torch.float32 for p in model.parameters())
     assert not rt.comm.live_buffers
+
+
+def test_replayed_layer_graphs_give_the_same_bits_as_kernel_by_kernel_launches():
+    """A layer's launch sequence is captured the second time its arguments repeat and replayed
+    afterwards: five AdamW steps must end in exactly the same shards and losses as with every
+    kernel launched by itself, graphs must actually have been built, and a changed input shape
+    (other keys) must keep working."""
+    from shardtrain_b200 import ops
+
+    stb = ops.load()
+    stb.replay_clear()
+    batches = [torch.randint(0, 2048, (4, 256), device="cuda") for _ in range(5)]   # new data each step
+    runs = {}
+    for graphs in (False, True):
+        dense, model, rt, tr = build(True, optimizer="adamw", lr=1e-3, graphs=graphs)
+        before = int(stb.launch_count())
+        losses = [tr.train_step(ids).loss for ids in batches]
+        torch.cuda.synchronize()
+        ops.check_status("replay")
+        runs[graphs] = (losses, [p.detach().clone() for p in model.parameters()],
+                        int(stb.launch_count()) - before)
+        if graphs:
+            # 2 layers x (forward + backward with 2 gradient-slot rotations) at least
+            assert int(stb.replay_graphs()) >= 4
+            shorter = torch.randint(0, 2048, (4, 128), device="cuda")
+            assert tr.train_step(shorter).loss > 0          # new shapes: new keys, no stale replay
+            torch.cuda.synchronize()
+            ops.check_status("replay, second shape")
+        else:
+            assert int(stb.replay_graphs()) == 0
+    # (the embedding's scatter-add uses atomics, so two runs agree to rounding, not to the bit)
+    assert runs[True][0] == pytest.approx(runs[False][0], rel=1e-5)
+    for a, b in zip(runs[True][1], runs[False][1]):
+        torch.testing.assert_close(a, b, atol=2e-5, rtol=0)
+    assert runs[True][2] == runs[False][2]                 # replayed kernels are counted too
+    stb.replay_clear()
 
 
 @pytest.mark.parametrize("retain", [False, True])
