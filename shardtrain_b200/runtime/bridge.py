@@ -26,7 +26,8 @@ class UnitMaterialize(torch.autograd.Function):
         # copy-out always runs on the compute stream, whichever stream owns this graph node
         with comm.stream_context("compute"):
             outputs = unit.runtime.materializer.finish(unit)
-        if comm.streams:
+        # (None: the materialiser left the wait to the first reader of the gathered parameters)
+        if comm.streams and unit.lease.copy_out_ready_event is not None:
             comm.wait_event(unit.lease.copy_out_ready_event, dependency_type="DATA_DEP",
                             consumer="materialize_outputs")
         return outputs

@@ -212,6 +212,19 @@ class TiedEmbeddingUnit(UnitState):
 
     tied = True
 
+    def pre_forward(self, *args):
+        runtime = self.runtime
+        materializer = runtime.materializer
+        if (self.lease is None and runtime.forward_prefetch and not runtime.defer_sp_prefetch
+                and len(runtime.units) > 1 and getattr(materializer, "kind", "") == "peer"
+                and materializer.degree > 1):
+            # On the sm_100a path the embedding lookup reads the shards and the gathered table is
+            # first read by the LM head at the end of the forward, while the first layer needs
+            # its weights at once: its (much smaller) gather goes first on the gather stream.
+            runtime.prefetch(1, "FWD")
+            self.annotate("FWD")
+        super().pre_forward(*args)
+
     def embedding_complete(self):
         self.annotate("FWD")
         if self.runtime.forward_prefetch and len(self.runtime.units) > 1:

@@ -214,6 +214,7 @@ class FusedExecutor:
         self._tp_buffers = {}
         self.exp_avg = self.exp_avg_sq = None
         self._shards_dirty = True
+        self.shards_clean_event = None
         self._flags = torch.zeros(2, dtype=torch.int32, device=runtime.device)
         self.check_flags = self._flags   # written by every reduce-scatter kernel
         self._rope_cache = {}
@@ -362,6 +363,9 @@ class FusedExecutor:
                 self._shadow_stale = False
             self.peer.barrier("fsdp_ag")
             self._shards_dirty = False
+            # readers of the peers' shards on OTHER streams (the embedding lookup) wait for this
+            self.shards_clean_event = torch.cuda.Event()
+            self.shards_clean_event.record(self.runtime.comm.current_stream())
 
     def acquire_grad_slot(self, unit):
         if getattr(unit, "grad_slot", None) is None:
@@ -563,6 +567,10 @@ class FusedExecutor:
 
     def head_loss(self, unit, hidden, labels, *, tied):
         name = "model.embed_tokens.weight" if tied else "lm_head.weight"
+        if tied:
+            # the embedding lookup did not wait for the gathered table (it reads the shards);
+            # the head is its first reader
+            self.runtime.materializer.await_deferred(unit)
         weight = unit.forward_weight(name, tied_second_use=tied)
         if labels is None:
             raise ValueError("The sm_100a executor fuses the LM head with the loss; pass labels")

@@ -297,7 +297,20 @@ class PeerMaterializer:
         if lease.weights:
             raise RuntimeError(f"Duplicate copy-out U{unit.unit_id}")
         comm = self.comm
-        comm.consume(lease.ag_ticket, consumer=f"copy_out/U{unit.unit_id}")
+        # A tied embedding unit is entered by the embedding lookup, which reads rows from the
+        # owners' FP32 shards and needs nothing of the gathered table; the LM head at the END of
+        # the forward is the table's first reader.  The wait for the (large) gather moves there,
+        # so the decoder layers run while it is still crossing the link; the lookup only needs
+        # the peers' shards to be final, which the barrier before the gather established.
+        defer = (getattr(unit, "tied", False) and lease.phase == "FWD" and self.degree > 1
+                 and comm.streams and getattr(self.arenas, "shards_clean_event", None) is not None)
+        if defer:
+            unit.runtime.wait_parameter_shards_ready()
+            comm.wait_event(self.arenas.shards_clean_event, dependency_type="DATA_DEP",
+                            consumer=f"embedding_lookup/U{unit.unit_id}")
+            lease.extras["deferred_gather"] = lease.ag_ticket
+        else:
+            comm.consume(lease.ag_ticket, consumer=f"copy_out/U{unit.unit_id}")
         plan = self.plans[unit.unit_id]
         if comm.diagnostics_enabled:
             comm.event("copy_out_start", unit_id=unit.unit_id, producer_ticket=lease.ag_ticket.op_id,
@@ -307,15 +320,25 @@ class PeerMaterializer:
         lease.weights = plan.weights
         lease.full_param_storages["bf16"] = lease.ag_storage
         lease.ag_storage = None
-        lease.copy_out_ready_event = lease.ag_ticket.ready_event
-        comm.event("copy_out_ready", unit_id=unit.unit_id)
+        lease.copy_out_ready_event = None if defer else lease.ag_ticket.ready_event
+        comm.event("copy_out_ready", unit_id=unit.unit_id, deferred=bool(defer))
         # The autograd edges of this executor carry one-element FP32 tokens, not the bf16
         # weights: autograd would cast an FP32 weight gradient to the dtype of a bf16 edge.  The
         # kernels read the weights from the lease and write gradients into the unit's slot.
         return plan.tokens
 
+    def await_deferred(self, unit):
+        """Make the calling stream wait for a gather whose wait `finish` left to the first real
+        reader of the gathered parameters (no-op when nothing was deferred)."""
+        lease = unit.lease
+        ticket = lease.extras.pop("deferred_gather", None) if lease is not None else None
+        if ticket is not None:
+            self.comm.consume(ticket, consumer=f"copy_out/U{unit.unit_id}")
+            lease.copy_out_ready_event = ticket.ready_event
+
     def released(self, unit, event):
         """Called when the unit's full parameters are given up; `event` marks the last reader."""
+        self.await_deferred(unit)      # a gather nobody waited for must not outlive its buffer
         self.plans[unit.unit_id].last_reader = event
 
     def reduce(self, unit, grads):
