@@ -36,9 +36,32 @@ from shardtrain_b200.runtime.materializer import Materializer
 
 MATERIALIZED_WAITING = {"RESHARDED", "FWD_RETAINED", "FWD_MATERIALIZING", "BWD_MATERIALIZING"}
 
+# The life of a unit inside one micro-step, as a table: state -> states it may be entered from.
+# ("SHARDED" enters FWD_ACTIVE directly when the lease was carried over from the previous
+# micro-step; FAILED is entered from anywhere by `ShardedRuntime.fail`.)
+# One edge is a quirk kept from the reference: with deferred sequence-parallel prefetch the tied LM
+# head (second consumer of unit 0's boundary handle) triggers "the next unit's forward gather"
+# once more at the end of the forward, so unit 1 goes RESHARDED -> FWD_MATERIALIZING and enters
+# its backward on that lease.
+ENTERED_FROM = {
+    "FWD_MATERIALIZING": {"SHARDED", "RESHARDED"},
+    "FWD_ACTIVE": {"FWD_MATERIALIZING", "SHARDED"},
+    "RESHARDED": {"FWD_ACTIVE"},
+    "FWD_RETAINED": {"FWD_ACTIVE"},
+    "BWD_MATERIALIZING": {"RESHARDED"},
+    "BWD_ACTIVE": {"BWD_MATERIALIZING", "FWD_RETAINED", "FWD_MATERIALIZING"},
+    "GRAD_REDUCING": {"BWD_ACTIVE"},
+    "GRAD_READY": {"GRAD_REDUCING"},
+}
+DIRECTION = {"FWD": +1, "BWD": -1}      # which neighbour a phase prefetches
+
 
 class UnitState:
-    """One FSDP unit: a group of parameters gathered, used, re-gathered and reduced together."""
+    """One FSDP unit: a group of parameters gathered, used, re-gathered and reduced together.
+
+    The unit is a small state machine (`ENTERED_FROM`) plus three counters that pin "exactly once
+    per micro-step" for forward, backward and reduction.  Who issues the neighbour's gather is
+    decided in one place, `_gather_neighbour`, from the runtime's prefetch switches."""
 
     tied = False
 
@@ -60,65 +83,95 @@ class UnitState:
     def handle(self, name) -> ShardedParameter:
         return self.runtime.registry[name]
 
+    def _enter(self, state):
+        if self.state not in ENTERED_FROM[state]:
+            raise RuntimeError(f"Illegal unit transition U{self.unit_id}: {self.state} -> {state}")
+        self.state = state
+
+    def _once(self, counter, what):
+        """`counter` (forward_calls, backward_calls, reductions) goes 0 -> 1 exactly once."""
+        if not self.runtime.active or getattr(self, counter):
+            raise RuntimeError(f"{what} U{self.unit_id}")
+        setattr(self, counter, 1)
+
+    # ------------------------------------------------------------------ materialisation
     def issue(self, phase):
         if self.lease is not None:
             raise RuntimeError(f"Duplicate materialization U{self.unit_id} {phase}")
         self.generation += 1
         self.annotate(phase)
-        self.state = f"{phase}_MATERIALIZING"
+        self._enter(f"{phase}_MATERIALIZING")
         self.lease = self.runtime.materializer.issue(self, phase)
         self.runtime.comm.event("materialize_issue")
 
     def release(self):
         if self.lease is None:
             raise RuntimeError(f"Missing lease U{self.unit_id}")
-        comm = self.runtime.comm
+        comm, lease = self.runtime.comm, self.lease
         if comm.streams:
-            self.lease.fullparam_last_consumer_event = torch.cuda.Event()
-            self.lease.fullparam_last_consumer_event.record(self.runtime.comm.current_stream())
+            lease.fullparam_last_consumer_event = torch.cuda.Event()
+            lease.fullparam_last_consumer_event.record(comm.current_stream())
         notify = getattr(self.runtime.materializer, "released", None)
         if notify is not None:
-            notify(self, self.lease.fullparam_last_consumer_event)
-        for lease in self.lease.full_param_storages.values():
-            comm.retire(lease)
-        self.lease.full_param_storages.clear()
-        self.lease.weights = {}
+            notify(self, lease.fullparam_last_consumer_event)
+        for storage in lease.full_param_storages.values():
+            comm.retire(storage)
+        lease.full_param_storages.clear()
+        lease.weights = {}
         self.lease = None
         comm.event("fullparams_retired", unit_id=self.unit_id)
 
     def weight(self, name):
         """Full parameter for a backward consumer, from the current step and generation only."""
-        if self.state != "BWD_ACTIVE" or self.lease is None:
+        lease = self.lease
+        if self.state != "BWD_ACTIVE" or lease is None:
             raise RuntimeError(f"Stale/early weight consumer {name} U{self.unit_id} {self.state}")
-        if self.lease.step_id != self.runtime.step_id or self.lease.generation != self.generation:
+        if (lease.step_id, lease.generation) != (self.runtime.step_id, self.generation):
             raise RuntimeError(f"Stale generation {name}")
-        return self.lease.weights[name]
+        return lease.weights[name]
 
-    # ------------------------------------------------------------------ prefetch boundary
-    def prefetch_after_input(self, handle, phase):
-        """Deferred prefetch: called by a consumer after it issued its sequence collective."""
+    # ------------------------------------------------------------------ who gathers the neighbour
+    def _gather_neighbour(self, phase, *, at, handle=None):
+        """Issue the gather of the unit this phase reaches next, if this is the place that owns
+        the decision.  `at` names the caller:
+
+        * "entry"  - the unit was just entered (`pre_forward` / `pre_backward`);
+        * "input"  - a consumer has issued its sequence collective (`prefetch_after_input`).
+
+        Plain prefetch decides at entry.  When sequence-parallel collectives are stream-ordered
+        the decision moves behind the consumer that owns the boundary handle ("input"), except
+        for an asynchronous backward, which keeps entry (or the gradient-dispatch tokens) as its
+        single scheduling source."""
         runtime = self.runtime
-        if not runtime.defer_sp_prefetch:
-            return
-        if phase == "BWD" and runtime.async_grad_rs:
-            return  # asynchronous backward has one fixed scheduling source (entry / dispatch)
-        boundary = self.forward_prefetch_handle if phase == "FWD" else self.backward_prefetch_handle
-        if handle is not boundary:
-            return
         enabled = runtime.forward_prefetch if phase == "FWD" else runtime.backward_prefetch
-        target = self.unit_id + (1 if phase == "FWD" else -1)
-        if enabled and 0 <= target < len(runtime.units):
+        target = self.unit_id + DIRECTION[phase]
+        if not enabled or not 0 <= target < len(runtime.units):
+            return
+        deferred = runtime.defer_sp_prefetch and not (phase == "BWD" and runtime.async_grad_rs)
+        if at == "input":
+            boundary = self.forward_prefetch_handle if phase == "FWD" else self.backward_prefetch_handle
+            if not deferred or handle is not boundary:
+                return
             self.annotate(phase)
             runtime.comm.event("prefetch_boundary", param_id=handle.spec.param_id, target_unit=target)
-            runtime.prefetch(target, phase)
-            self.annotate(phase)
+        else:
+            if deferred:
+                return
+            if phase == "BWD":
+                runtime.comm.event("prefetch_boundary", target_unit=target,
+                                   scheduling_boundary="backward_unit_entry")
+        runtime.prefetch(target, phase)
+        if at == "input" or phase == "BWD":
+            self.annotate(phase)       # (a forward entry leaves the log annotated with the target)
+
+    def prefetch_after_input(self, handle, phase):
+        """Deferred prefetch: called by a consumer after it issued its sequence collective."""
+        self._gather_neighbour(phase, at="input", handle=handle)
 
     # ------------------------------------------------------------------ forward
     def pre_forward(self, *_):
         runtime = self.runtime
-        if not runtime.active or self.forward_calls:
-            raise RuntimeError(f"Forward outside begin_step or repeated Unit U{self.unit_id}")
-        self.forward_calls += 1
+        self._once("forward_calls", "Forward outside begin_step or repeated Unit")
         if self.lease is None:
             self.issue("FWD")
         self.annotate("FWD")
@@ -130,11 +183,9 @@ class UnitState:
         if isinstance(weights, torch.Tensor):
             weights = (weights,)
         self.forward_weights = {h.spec.param_id: w for h, w in zip(self.handles, weights)}
-        self.state = "FWD_ACTIVE"
+        self._enter("FWD_ACTIVE")
         runtime.comm.event("unit_forward")
-        if (not runtime.defer_sp_prefetch and runtime.forward_prefetch
-                and self.unit_id + 1 < len(runtime.units)):
-            runtime.prefetch(self.unit_id + 1, "FWD")
+        self._gather_neighbour("FWD", at="entry")
 
     def forward_weight(self, name, *, tied_second_use=False):
         """Autograd-connected full parameter for a forward consumer (one use per parameter)."""
@@ -150,9 +201,9 @@ class UnitState:
         last = self.unit_id == len(runtime.units) - 1
         if runtime.reshard_after_forward and not last and not runtime.retain_parameters:
             self.release()
-            self.state = "RESHARDED"
+            self._enter("RESHARDED")
         else:
-            self.state = "FWD_RETAINED"
+            self._enter("FWD_RETAINED")
         runtime.comm.event(self.state)
         return PreBackward.apply(output, self)
 
@@ -170,23 +221,19 @@ class UnitState:
         self.annotate("BWD")
         if not self.lease.weights:
             runtime.materializer.finish(self)
-        self.state = "BWD_ACTIVE"
+        self._enter("BWD_ACTIVE")
         runtime.comm.event("unit_pre_backward")
         if dispatch:
             runtime.backward_prefetch_entered(self)
-        elif (runtime.backward_prefetch and self.unit_id
-              and (not runtime.defer_sp_prefetch or runtime.async_grad_rs)):
-            runtime.comm.event("prefetch_boundary", target_unit=self.unit_id - 1,
-                               scheduling_boundary="backward_unit_entry")
-            runtime.prefetch(self.unit_id - 1, "BWD")
-            self.annotate("BWD")
+        else:
+            self._gather_neighbour("BWD", at="entry")
 
     def reduce(self, grads):
         if self.reductions or self.state != "BWD_ACTIVE":
             raise RuntimeError(f"Duplicate/early gradient RS U{self.unit_id} {self.state}")
         self.reductions += 1
         self.annotate("BWD")
-        self.state = "GRAD_REDUCING"
+        self._enter("GRAD_REDUCING")
         comm = self.runtime.comm
         if comm.diagnostics_enabled:
             # the stream this node runs on: autograd replays the stream of the bridge's forward
@@ -199,7 +246,7 @@ class UnitState:
             self.lease = None
         else:
             self.release()
-        self.state = "GRAD_READY"
+        self._enter("GRAD_READY")
 
 
 class TiedEmbeddingUnit(UnitState):
@@ -236,7 +283,7 @@ class TiedEmbeddingUnit(UnitState):
             raise RuntimeError("Tied weight must have exactly embedding and head forward uses")
         self.forward_weights = {}
         self.annotate("FWD")
-        self.state = "FWD_RETAINED"
+        self._enter("FWD_RETAINED")
         self.runtime.comm.event("tied_weight_retained", unit_id=self.unit_id)
         return PreBackward.apply(output, self)
 
