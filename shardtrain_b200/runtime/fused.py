@@ -231,21 +231,27 @@ class FusedExecutor:
 
     # ------------------------------------------------------------------ fused all-gather -> GEMM
     # `auto` pulls only where one pass over the weights serves every row tile (four 128-row
-    # accumulators in TMEM).  Measured on B200: 63 us fused against 64 us gather kernel + gated
-    # GEMM at 512 rows, 111 us against 84 us at 1024 rows (gate|up of Qwen2.5-1.5B, 8 owners).
+    # accumulators in TMEM) AND nothing else would hide the gather.  Measured on B200, gate|up of
+    # Qwen2.5-1.5B with 8 owners: kernel against kernel the fused GEMM wins at 512 rows (62 us
+    # against 65 us gather kernel + gated GEMM on 8 GPUs) and loses at 1024 rows (111 / 84 us);
+    # inside the training step with forward prefetch the gather kernel runs on its own stream
+    # under the previous layer's compute, while the fused GEMM puts the pull on the compute
+    # stream: F8T1 on 8 GPUs 61.1 ms per step with the pull, 60.1 ms without.
     PULL_MAX_ROWS = 512
 
     def pulls_in_gemm(self, unit, phase) -> bool:
         """Should this materialisation leave q|k|v and gate|up to the consuming GEMMs?  Only in
         the forward of a decoder layer, with FSDP peers to pull from; `auto` also wants the
-        activation to fit the accumulators the kernel keeps in TMEM in one pass (<= 512 rows)."""
+        activation to fit the accumulators the kernel keeps in TMEM in one pass (<= 512 rows)
+        and forward prefetch to be off (with prefetch the gather is already hidden)."""
         mode = self.runtime.fused_allgather
         plan = self.runtime.materializer.plans[unit.unit_id]
         if mode == "off" or phase != "FWD" or self.peer.degree == 1 or plan.ag_segs_gu is None:
             return False
         if mode == "on":
             return True
-        return self.rows_hint is not None and self.rows_hint <= self.PULL_MAX_ROWS
+        return (not self.runtime.forward_prefetch and self.rows_hint is not None
+                and self.rows_hint <= self.PULL_MAX_ROWS)
 
     def ag_arguments(self, unit, plan):
         """The five trailing arguments of the layer-forward ops: empty unless this lease left
