@@ -336,6 +336,11 @@ class FusedExecutor:
         """Unmap and free the peer-visible buffers (arenas, gradient ring, activation slots).
         Tensors that alias them (`param`, `grad` views, shard leaves) must not be used
         afterwards.  With `failed` nothing is freed: a peer may still be reading."""
+        if self.replay and not failed:
+            # the replay cache keeps this executor's activations and graphs alive: give them back
+            # (the cache is per process; another executor's entries are simply rebuilt)
+            torch.cuda.synchronize(self.runtime.device)
+            self.ops.replay_clear()
         seen = set()
         for peer in (self.tp_peer, self.reduce_peer, self.peer):
             if peer is not None and id(peer) not in seen:

@@ -66,6 +66,16 @@ def test_strict_keys_types_and_overrides(tmp_path):
         load_config(None, ["--training.nope", "1"])
     with pytest.raises(ConfigError, match="WORLD_SIZE=3"):
         Config().validate(3)
+    # the sm_100a switches: defaults chosen by measurement, typed overrides, bad values refused
+    runtime = Config().runtime
+    assert (runtime.cuda_graphs, runtime.fused_allgather, runtime.fused_seq_gather, runtime.nvls,
+            runtime.wire_dtype) == (True, "auto", False, "off", "bf16")
+    assert load_config(None, ["--runtime.cuda_graphs", "false"]).runtime.cuda_graphs is False
+    with pytest.raises(ConfigError, match="must be bool"):
+        load_config(None, ["--runtime.cuda_graphs", "maybe"])
+    for field, value in (("nvls", "on"), ("fused_allgather", "always"), ("wire_dtype", "fp16")):
+        with pytest.raises(ConfigError, match=f"runtime.{field}"):
+            load_config(None, [f"--runtime.{field}", value]).validate()
 
 
 def test_strategy_names():
