@@ -140,3 +140,30 @@ def test_communicator_membership_formula():
     assert expected_members("tp_grad", 1, 2, 4) == [0, 1, 2, 3]
     assert expected_members("fsdp", 5, 2, 4) == [1, 5]
     assert expected_members("fsdp_grad", 2, 2, 4) == [2, 6]
+
+
+def test_step_profile_summary_groups_streams_kernels_and_gaps(tmp_path):
+    """`ops.profile_step.summarise` on a hand-written kineto trace: union of busy time, the
+    stream with the most launches is the compute stream, gaps are charged to the kernel after."""
+    import json
+
+    from shardtrain_b200.ops.profile_step import summarise
+
+    def kernel(name, ts, dur, stream):
+        return {"cat": "kernel", "name": name, "ts": ts, "dur": dur, "args": {"stream": stream}}
+
+    events = [kernel("void stb::(anonymous namespace)::rmsnorm_fwd_kernel<false>(float*)", 0, 10, 7),
+              kernel("void stb::gemm_bf16_tcgen05_kernel<256, false, false>(int)", 12, 50, 7),
+              kernel("void stb::gemm_bf16_tcgen05_kernel<256, false, false>(int)", 100, 50, 7),   # 38 us gap
+              kernel("stb::gather_params_kernel(int)", 20, 100, 9),
+              {"cat": "cpu_op", "name": "aten::add", "ts": 0, "dur": 5}]
+    path = tmp_path / "trace.json"
+    path.write_text(json.dumps({"traceEvents": events}))
+    got = summarise(str(path))
+    assert got["kernels"] == 4 and got["span_ms"] == pytest.approx(0.150)
+    assert got["busy_union_ms"] == pytest.approx(0.150 - 0.002)        # only 10..12 is idle everywhere
+    assert [s["launches"] for s in got["streams"]] == [3, 1]
+    assert got["top_kernels"][0]["name"] == "gemm_bf16_tcgen05_kernel<256, false, false>"
+    assert got["top_kernels"][0]["total_ms"] == pytest.approx(0.1)
+    gaps = got["compute_stream_gaps_over_15us"]
+    assert gaps["total_ms"] == pytest.approx(0.038) and gaps["before"][0]["count"] == 1
