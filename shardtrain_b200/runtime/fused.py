@@ -510,31 +510,31 @@ class FusedExecutor:
 
     def key_mask_bits(self, attention_mask):
         """Packed form of a [batch, sequence] key mask (one bit per key, int32 [B, pitch]) for
-        the attention kernels.  Every layer of every micro-step of a step presents the same mask
-        tensor: the packing runs once per (tensor, version) instead of three small kernels per
-        layer call."""
+        the attention kernels.  The bits live in ONE buffer per mask shape, refilled when another
+        mask tensor (or another version of it) arrives: every layer of a micro-step presents the
+        same mask, so the packing runs once per micro-step at most, and the buffer's address --
+        part of a layer's replay key -- stays the same from step to step even when the caller
+        builds a fresh mask tensor every step."""
         if attention_mask.ndim != 2:
             raise ValueError("The sm_100a attention kernel takes a [batch, sequence] key mask")
-        key = (attention_mask.data_ptr(), attention_mask._version, tuple(attention_mask.shape))
-        hit = self._mask_cache.get(key)
-        if hit is None:
-            if len(self._mask_cache) > 8:
-                self._mask_cache.clear()
-            batch, seq = attention_mask.shape
-            pitch = 4 * ((seq + 127) // 128)
-            bits = torch.empty((batch, pitch), dtype=torch.int32, device=self.runtime.device)
+        batch, seq = attention_mask.shape
+        source = (attention_mask.data_ptr(), attention_mask._version)
+        bits = self.scratch(("key_mask_bits", batch, seq), (batch, 4 * ((seq + 127) // 128)), torch.int32)
+        held = self._mask_cache.get((batch, seq))
+        if held is None or held[0] != source:
             as_bytes = attention_mask.to(self.runtime.device).ne(0).to(torch.uint8).contiguous()
             self.ops.pack_key_mask(as_bytes, bits)
             # the entry keeps the caller's tensor alive: its address cannot be reused meanwhile
-            hit = self._mask_cache[key] = (bits, attention_mask)
-        return hit[0]
+            self._mask_cache[(batch, seq)] = (source, attention_mask)
+        return bits
 
     def rotary(self, position_ids, default_positions):
         """cos/sin tables (FP32, [rows, D/2]) for the RoPE kernel and an optional int32 row index
         per (batch, token).  Default positions 0..S-1 and a caller-supplied [1, S] row share one
         table of S rows indexed by `token % S`; per-sample positions [B, S] get a table of B*S rows
         indexed by the token's row.  Tables of caller-supplied positions are cached on the
-        tensor's identity and version, so a batch that repeats them pays once."""
+        tensor's identity and version, so a batch that repeats them pays once; they are rebuilt
+        in place when fresh positions arrive."""
         seq = position_ids.shape[-1]
         inv_freq = self.runtime.inv_freq.float()
         if default_positions:
@@ -544,19 +544,26 @@ class FusedExecutor:
                 angle = pos[:, None] * inv_freq[None, :]
                 self._rope_cache[key] = (angle.cos().contiguous(), angle.sin().contiguous(), None)
         else:
-            key = (position_ids.data_ptr(), position_ids._version, tuple(position_ids.shape))
-            if key not in self._rope_cache:
-                for stale in [k for k in self._rope_cache if k[0] != "default"][8:]:
-                    del self._rope_cache[stale]
+            # One set of tables per shape of `position_ids`, at fixed addresses (they are part of
+            # a layer's replay key), recomputed when another tensor or version arrives.
+            shape = tuple(position_ids.shape)
+            key = ("given", shape)
+            source = (position_ids.data_ptr(), position_ids._version)
+            held = self._rope_cache.get(key)
+            if held is None or held[3] != source:
                 pos = position_ids.to(self.runtime.device, torch.float32).reshape(-1)
                 angle = pos[:, None] * inv_freq[None, :]
+                cos = self.scratch(("rope_cos", shape), tuple(angle.shape), torch.float32)
+                sin = self.scratch(("rope_sin", shape), tuple(angle.shape), torch.float32)
+                torch.cos(angle, out=cos)
+                torch.sin(angle, out=sin)
                 rows = None
                 if position_ids.shape[0] != 1:
-                    rows = torch.arange(pos.numel(), device=self.runtime.device, dtype=torch.int32)
+                    rows = self.scratch(("rope_rows", shape), (pos.numel(),), torch.int32)
+                    torch.arange(pos.numel(), out=rows)
                 # the entry keeps `position_ids` alive, so its address cannot be handed to another
-                # tensor while the key exists
-                self._rope_cache[key] = (angle.cos().contiguous(), angle.sin().contiguous(), rows,
-                                         position_ids)
+                # tensor while the entry is current
+                self._rope_cache[key] = (cos, sin, rows, source, position_ids)
         cos, sin, rows = self._rope_cache[key][:3]
         return cos, sin, rows, seq
 

@@ -91,6 +91,39 @@ def test_replayed_layer_graphs_give_the_same_bits_as_kernel_by_kernel_launches()
     stb.replay_clear()
 
 
+def test_fresh_mask_and_position_tensors_every_step_still_hit_the_replay_cache():
+    """A training loop builds new mask / position tensors every step.  Their packed bits and RoPE
+    tables live at fixed addresses, so the layers' replay keys repeat exactly as they do when one
+    mask tensor is reused: the same number of graphs (bounded by layers x gradient slots), and
+    the same masked result."""
+    from shardtrain_b200 import ops
+
+    stb = ops.load()
+    ids = torch.randint(0, 2048, (4, 256), device="cuda")
+
+    def inputs():
+        mask = torch.ones_like(ids)
+        mask[1, 200:] = 0                                     # one padded sample
+        return mask, torch.arange(256, device="cuda").unsqueeze(0).clone()
+
+    losses, graphs = {}, {}
+    for fresh in (True, False):
+        stb.replay_clear()
+        dense, model, rt, tr = build(True, optimizer="adamw", lr=1e-3)
+        kept = inputs()
+        run = []
+        for step in range(6):
+            mask, positions = inputs() if fresh else kept
+            run.append(tr.train_step(ids, ids, attention_mask=mask, position_ids=positions).loss)
+        torch.cuda.synchronize()
+        ops.check_status("fresh inputs")
+        losses[fresh], graphs[fresh] = run, int(stb.replay_graphs())
+    # 2 layers: one forward sequence each, one backward sequence per gradient slot (4) at most
+    assert 4 <= graphs[True] == graphs[False] <= 2 + 2 * 4
+    assert losses[True] == pytest.approx(losses[False], rel=1e-5)
+    stb.replay_clear()
+
+
 @pytest.mark.parametrize("retain", [False, True])
 def test_adamw_training_reduces_loss_and_fuses_the_update(retain):
     from shardtrain_b200 import ops
