@@ -158,3 +158,41 @@ def test_two_rank_save_reloads_on_one_and_four_ranks(tmp_path):
         for name in names:
             assert torch.equal(state.tensor(name), saved.tensor(name)), (mode, fsdp, name)
         assert loss == pytest.approx(saved_loss, rel=(0 if mode == "load_sharded" else 2e-6))
+
+
+def test_checkpoint_oracle_tool_compares_dense_and_runtime_and_changes_nothing(tmp_path, capsys):
+    """`utils.verify_checkpoint`: a tiny random HF-named checkpoint passes (loss and every
+    parameter gradient of the runtime equal the dense model's, shards untouched); a checkpoint
+    with one tensor missing is refused before anything runs."""
+    import json
+
+    import yaml
+
+    from shardtrain_b200.models.qwen2 import Qwen2CausalLM, Qwen2ModelConfig
+    from shardtrain_b200.utils import verify_checkpoint
+
+    torch.manual_seed(3)
+    cfg = Qwen2ModelConfig(vocab_size=96, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=True)
+    dense = Qwen2CausalLM(cfg)
+    tensors = {n: p.detach().clone() for n, p in dense.named_parameters()}
+    good = tmp_path / "good"
+    good.mkdir()
+    save_safetensors(good / "model.safetensors", tensors)
+    config_file = tmp_path / "config.yaml"
+    config_file.write_text(yaml.safe_dump(cfg.to_dict()))
+    code = verify_checkpoint.main(["--checkpoint", str(good), "--hf-config", str(config_file),
+                                   "--batch", "2", "--seq-len", "12"])
+    printed = capsys.readouterr().out
+    report = json.loads(printed[printed.index("{"):])
+    assert code == 0 and report["passed"] and not report["problems"]
+    assert report["parameters"] == sum(t.numel() for t in tensors.values())
+    assert report["loss_runtime"] == pytest.approx(report["loss_dense"], rel=1e-5)
+    assert report["worst_gradient"]["relative_to_max"] < 1e-4 and len(report["shard_sha256"]) == 64
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    fewer = dict(tensors)
+    fewer.pop("model.norm.weight")
+    save_safetensors(bad / "model.safetensors", fewer)
+    with pytest.raises(CheckpointError, match="Missing keys"):
+        verify_checkpoint.main(["--checkpoint", str(bad), "--hf-config", str(config_file)])
