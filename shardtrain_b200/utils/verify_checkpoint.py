@@ -39,17 +39,23 @@ def worst(actual: torch.Tensor, expected: torch.Tensor) -> tuple[float, float]:
     return float(diff.max()), float(diff.max() / scale)
 
 
-def dense_oracle(model_config, checkpoint, ids):
+def dense_oracle(model_config, checkpoint, batches):
+    """Loss and gradients of the dense FP32 model over ALL data-parallel replicas' batches (equal
+    sizes, so the global token mean is the mean of the per-batch means): what the runtime's
+    globally normalised loss and reduced gradients must equal on every rank."""
     from shardtrain_b200.models.qwen2 import Qwen2CausalLM
     from shardtrain_b200.models.qwen2_checkpoint import load_qwen_checkpoint
     from shardtrain_b200.models.qwen2_factory import qwen_config_from
 
     model = Qwen2CausalLM(qwen_config_from(model_config))
     report = load_qwen_checkpoint(model, checkpoint)
-    out = model(ids, labels=ids)
-    out.loss.backward()
+    total = 0.0
+    for ids in batches:
+        out = model(ids, labels=ids)
+        (out.loss / len(batches)).backward()
+        total += float(out.loss.detach()) / len(batches)
     grads = {n: p.grad.detach().clone() for n, p in model.named_parameters()}
-    return float(out.loss.detach()), grads, report
+    return total, grads, report
 
 
 def verify(config, checkpoint, *, batch: int, seed: int, atol: float, rtol: float) -> dict:
@@ -59,9 +65,11 @@ def verify(config, checkpoint, *, batch: int, seed: int, atol: float, rtol: floa
 
     with WorkerSession(config, "runtime") as session:
         mesh = session.context
-        generator = torch.Generator().manual_seed(seed + mesh.coordinate.fsdp)
-        ids = torch.randint(config.model.vocab_size, (batch, config.model.seq_len), generator=generator)
-        want_loss, want_grads, load_report = dense_oracle(config.model, checkpoint, ids)
+        batches = [torch.randint(config.model.vocab_size, (batch, config.model.seq_len),
+                                 generator=torch.Generator().manual_seed(seed + replica))
+                   for replica in range(config.parallel.fsdp_degree)]
+        ids = batches[mesh.coordinate.fsdp]
+        want_loss, want_grads, load_report = dense_oracle(config.model, checkpoint, batches)
 
         model = build_qwen_model(config.model, config.training.seed, checkpoint=checkpoint)
         runtime = ShardedRuntime(device=mesh.device, reshard_after_forward=True,
@@ -85,8 +93,8 @@ def verify(config, checkpoint, *, batch: int, seed: int, atol: float, rtol: floa
         if abs(got_loss - want_loss) > atol + rtol * abs(want_loss):
             problems.append(f"loss {got_loss!r} vs dense {want_loss!r}")
         worst_name, worst_abs, worst_rel = None, 0.0, 0.0
-        if config.parallel.fsdp_degree * config.parallel.tp_degree == 1:
-            # with one rank the dense gradient is the runtime's gradient of the same batch
+        if config.parallel.tp_degree == 1:
+            # the reduced shard gradients, put together again, are the dense model's gradients
             for name, grad in runtime.reconstruct_tp_local(gradients=True).items():
                 a, r = worst(grad.cpu(), want_grads[name])
                 if r > worst_rel:
