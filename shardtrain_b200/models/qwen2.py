@@ -154,27 +154,43 @@ def apply_rotary(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor
     return q * cos + rotate_half(q) * sin, k * cos + rotate_half(k) * sin
 
 
+def _with_key_padding(lower: Tensor, mask: Tensor, like: Tensor) -> Tensor:
+    """[B, S] key mask: a key is visible when it is causal AND not padding."""
+    batch, seq = like.shape[0], like.shape[2]
+    if mask.shape != (batch, seq):
+        raise ValueError("attention_mask must describe the full global [batch, sequence]")
+    return lower & mask.bool()[:, None, None, :]
+
+
+def _with_full_mask(lower: Tensor, mask: Tensor, like: Tensor) -> Tensor:
+    """[B or 1, 1, S, S] mask: boolean masks are intersected with the causal triangle, additive
+    floating-point masks get the triangle's complement filled with the dtype's minimum."""
+    batch, seq = like.shape[0], like.shape[2]
+    if mask.shape[-2:] != (seq, seq):
+        raise ValueError("attention_mask must have shape [B,S] or [B,1,S,S]")
+    if mask.shape[0] not in (1, batch):
+        raise ValueError("attention_mask batch size is incompatible")
+    if mask.dtype == torch.bool:
+        return lower & mask
+    if not mask.is_floating_point():
+        raise ValueError("A 4-D attention mask must be boolean or additive floating point")
+    return mask.to(like.dtype).masked_fill(~lower, torch.finfo(like.dtype).min)
+
+
+_MASK_FORMS = {2: _with_key_padding, 4: _with_full_mask}      # by number of dimensions
+
+
 def causal_attention_mask(x: Tensor, attention_mask: Tensor | None) -> Tensor:
     """Boolean (or additive, for a float 4-D input) mask for [B, H, S, D] queries."""
     batch, _, seq, _ = x.shape
-    allowed = torch.ones((seq, seq), dtype=torch.bool, device=x.device).tril()
-    allowed = allowed[None, None].expand(batch, 1, seq, seq)
+    lower = torch.ones((seq, seq), dtype=torch.bool, device=x.device).tril()
+    lower = lower[None, None].expand(batch, 1, seq, seq)
     if attention_mask is None:
-        return allowed
-    attention_mask = attention_mask.to(x.device)
-    if attention_mask.ndim == 2:
-        if attention_mask.shape != (batch, seq):
-            raise ValueError("attention_mask must describe the full global [batch, sequence]")
-        return allowed & attention_mask[:, None, None, :].bool()
-    if attention_mask.ndim != 4 or attention_mask.shape[-2:] != (seq, seq):
+        return lower
+    combine = _MASK_FORMS.get(attention_mask.ndim)
+    if combine is None:
         raise ValueError("attention_mask must have shape [B,S] or [B,1,S,S]")
-    if attention_mask.shape[0] not in (1, batch):
-        raise ValueError("attention_mask batch size is incompatible")
-    if attention_mask.dtype == torch.bool:
-        return allowed & attention_mask
-    if not attention_mask.is_floating_point():
-        raise ValueError("A 4-D attention mask must be boolean or additive floating point")
-    return attention_mask.to(x.dtype).masked_fill(~allowed, torch.finfo(x.dtype).min)
+    return combine(lower, attention_mask.to(x.device), x)
 
 
 def causal_attention(q: Tensor, k: Tensor, v: Tensor, attention_mask: Tensor | None) -> Tensor:
