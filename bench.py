@@ -294,7 +294,7 @@ def run_ours(args):
     if fsdp * tp != args.gpus:
         raise SystemExit(f"strategy F{fsdp}T{tp} does not match --gpus {args.gpus}")
     m = measure_ours(args, fsdp, tp, sp)
-    VALID_LABELS_PER_STEP = valid_labels(args)
+    VALID_LABELS_PER_STEP = valid_labels(args)      # of THIS run (model, batch), not the default
     value = VALID_LABELS_PER_STEP * 1000.0 / m["ms"]
     published = PUBLISHED.get(args.gpus, {}).get(m["strategy"])
     wire = ("fp32 parameter shards" if args.fp32_wire else
@@ -319,7 +319,8 @@ def run_ours(args):
                    "inputs": "token ids + all-ones attention_mask + position_ids, as the "
                              "reference benchmark passes them",
                    "runtime": {**m["switches"], "executor": m["executor"],
-                               "fused_allgather": args.fused_allgather, "nvls": m["nvls"]},
+                               "fused_allgather": args.fused_allgather, "nvls": m["nvls"],
+                               "cuda_graphs": not args.no_graphs and tp == 1},
                    "l2": "no explicit flush: each step streams >6 GB of parameters, "
                          "gradients and optimizer state per GPU group, far above the 126 MB L2"},
         "clocks": m["clocks"],
