@@ -236,6 +236,69 @@ def audit_event_logs(directory, *, fsdp: int, tp: int, layers: int, tied: bool =
 
 
 # ---------------------------------------------------------------------------- benchmark artefacts
+# kinds the event log uses for each role (gloo computes a reduce-scatter as all-reduce + slice)
+VOLUME_KINDS = {"fsdp_ag": {"fsdp_ag"}, "fsdp_rs": {"fsdp_rs", "fsdp_rs_math_allreduce"},
+                "sp_ag": {"sp_ag"}, "sp_rs": {"sp_rs", "sp_rs_math_allreduce"},
+                "tp_replicated_allreduce": {"tp_norm_allreduce"}}
+
+
+def audit_volume(directory, model: dict, *, fsdp: int, tp: int, sp: bool, local_batch: int) -> list[str]:
+    """Measured payload against the model: in every micro-step of every rank, the collectives of
+    each role are as many, and carry as many elements, as `comm_volume.microstep_payload` predicts
+    from the configuration alone (the reference's "predicted vs. measured payload" table,
+    reports/fsdp_interview_sections/04_communication_volume.md:84-95)."""
+    from shardtrain_b200.utils.comm_volume import microstep_payload
+
+    want = microstep_payload(model, fsdp=fsdp, tp=tp, sp=sp, local_batch=local_batch)
+    if fsdp == 1:
+        want.pop("fsdp_ag"), want.pop("fsdp_rs")        # a singleton group issues nothing
+    problems = []
+    for rank, rows in read_events(directory).items():
+        seen: dict[tuple[int, str], list[int]] = defaultdict(lambda: [0, 0])
+        for r in rows:
+            if r["event_type"] != "collective_issue" or r.get("step_id", -1) < 0:
+                continue
+            if r.get("phase") not in ("FWD", "BWD"):
+                continue
+            for role, kinds in VOLUME_KINDS.items():
+                if r.get("kind") in kinds:
+                    shape = r.get("output_shape") if role.endswith("_ag") else r.get("input_shape")
+                    elements = 1
+                    for extent in shape or [r.get("numel", 0)]:
+                        elements *= extent
+                    entry = seen[(r["step_id"], role)]
+                    entry[0] += 1
+                    entry[1] += elements
+        steps = sorted({step for step, _ in seen})
+        for step in steps:
+            for role, expect in want.items():
+                count, elements = seen.get((step, role), (0, 0))
+                low = expect.get("count", expect.get("count_min"))
+                high = expect.get("count", expect.get("count_max"))
+                if not low <= count <= high:
+                    problems.append(f"rank {rank} step {step}: {count} {role} collectives, "
+                                    f"expected {low}" + ("" if low == high else f"..{high}"))
+                if elements != expect["elements"]:
+                    problems.append(f"rank {rank} step {step}: {role} carried {elements} elements, "
+                                    f"the model predicts {expect['elements']}")
+        if not steps:
+            problems.append(f"rank {rank}: no micro-step with collectives found")
+    return problems
+
+
+def volume_arguments(config_path) -> dict:
+    """`audit_volume`'s arguments from a run's configuration file."""
+    from shardtrain_b200.config import load_config
+
+    c = load_config(config_path)
+    m = c.model
+    model = dict(hidden_size=m.hidden_size, mlp_hidden_size=m.mlp_hidden_size, num_heads=m.num_heads,
+                 num_key_value_heads=m.num_key_value_heads or m.num_heads, layers=m.layers,
+                 vocab_size=m.vocab_size, seq_len=m.seq_len, tie_word_embeddings=m.tie_word_embeddings)
+    return dict(model=model, fsdp=c.parallel.fsdp_degree, tp=c.parallel.tp_degree,
+                sp=c.parallel.sp_enabled, local_batch=c.training.local_batch_size)
+
+
 def audit_benchmark(directory, *, layers: int | None = None, tied: bool | None = None) -> list[str]:
     paths = sorted(Path(directory).glob("benchmark.rank*.json"))
     if not paths:
@@ -334,10 +397,17 @@ def main(argv=None) -> int:
     be = sub.add_parser("benchmark")
     be.add_argument("directory")
     be.add_argument("--layers", type=int, default=None)
+    vo = sub.add_parser("volume", help="measured payload of every micro-step against the volume model")
+    vo.add_argument("directory")
+    vo.add_argument("--config", default=None,
+                    help="the run's configuration (default: resolved_config.rank0.yaml in the directory)")
     a = ap.parse_args(argv)
     if a.what == "events":
         problems = audit_event_logs(a.directory, fsdp=a.fsdp, tp=a.tp, layers=a.layers,
                                     tied=not a.untied, policy=a.policy)
+    elif a.what == "volume":
+        problems = audit_volume(a.directory, **volume_arguments(
+            a.config or Path(a.directory) / "resolved_config.rank0.yaml"))
     else:
         problems = audit_benchmark(a.directory, layers=a.layers)
     for line in problems:

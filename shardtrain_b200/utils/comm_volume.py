@@ -55,6 +55,67 @@ def qwen_units(m, tp: int) -> list[Unit]:
     return units
 
 
+def qwen_parameters(m, tp: int) -> list[tuple[int, str, int, bool]]:
+    """(unit index, name, TP-local element count, replicated over TP) of every parameter, in the
+    runtime's unit order."""
+    h, inter, heads = m["hidden_size"], m["mlp_hidden_size"], m["num_heads"]
+    kv = m.get("num_key_value_heads", heads) * (h // heads)
+    table = m["vocab_size"] * h
+    rows = [(0, "embed_tokens.weight", table, True)]
+    for layer in range(m["layers"]):
+        unit = layer + 1
+        rows += [(unit, "q_proj.weight", h * h // tp, False), (unit, "q_proj.bias", h // tp, False),
+                 (unit, "k_proj.weight", kv * h // tp, False), (unit, "k_proj.bias", kv // tp, False),
+                 (unit, "v_proj.weight", kv * h // tp, False), (unit, "v_proj.bias", kv // tp, False),
+                 (unit, "o_proj.weight", h * h // tp, False),
+                 (unit, "gate_proj.weight", inter * h // tp, False),
+                 (unit, "up_proj.weight", inter * h // tp, False),
+                 (unit, "down_proj.weight", inter * h // tp, False),
+                 (unit, "input_layernorm.weight", h, True),
+                 (unit, "post_attention_layernorm.weight", h, True)]
+    rows.append((m["layers"] + 1, "norm.weight", h, True))
+    if not m.get("tie_word_embeddings", True):
+        rows.append((m["layers"] + 2, "lm_head.weight", table, True))
+    return rows
+
+
+def microstep_payload(model: dict, *, fsdp: int, tp: int, sp: bool, local_batch: int) -> dict:
+    """What the collectives of ONE micro-step carry on the library-collective path, in elements
+    (shards are padded to ceil(n / F), so a gathered parameter is F * ceil(n / F) elements):
+
+    * `fsdp_ag`: gathers issued and the elements they deliver (all units for the forward, the
+      resharded ones again for the backward);
+    * `fsdp_rs`: elements entering the gradient reductions (every parameter once); the number of
+      reductions lies between one per unit and one per bucket (asynchronous reduction puts a
+      unit's norm weights in a bucket of their own);
+    * `sp_ag` / `sp_rs`: six gathers and four reduce-scatters of a full [batch, sequence, hidden]
+      activation per layer;
+    * `tp_replicated_allreduce`: one all-reduce per TP-replicated parameter (each norm weight,
+      the embedding, an untied head), over its FSDP shard.
+    """
+    params = qwen_parameters(model, tp)
+    tied = model.get("tie_word_embeddings", True)
+    last_unit = max(unit for unit, *_ in params)
+    padded = lambda n: fsdp * -(-n // fsdp)          # noqa: E731
+    regathered = {unit for unit, *_ in params
+                  if unit != last_unit and not (tied and unit == 0)}
+    units = {unit for unit, *_ in params}
+    out = {"fsdp_ag": {"count": len(units) + len(regathered),
+                       "elements": sum(padded(n) * (2 if unit in regathered else 1)
+                                       for unit, _, n, _ in params)},
+           "fsdp_rs": {"count_min": len(units),
+                       "count_max": len({(unit, rep) for unit, _, _, rep in params}),
+                       "elements": sum(padded(n) for _, _, n, _ in params)}}
+    if tp > 1:
+        shards = [-(-n // fsdp) for _, _, n, rep in params if rep]
+        out["tp_replicated_allreduce"] = {"count": len(shards), "elements": sum(shards)}
+        if sp:
+            tokens = local_batch * model["seq_len"] * model["hidden_size"]
+            out["sp_ag"] = {"count": 6 * model["layers"], "elements": 6 * model["layers"] * tokens}
+            out["sp_rs"] = {"count": 4 * model["layers"], "elements": 4 * model["layers"] * tokens}
+    return out
+
+
 def predict(model: dict, *, fsdp: int, tp: int, sp: bool, local_batch: int, accumulation: int,
             compute_bytes: int = 2, wire: str = "reference") -> dict:
     """Counts and bytes per rank per optimizer step, by role."""

@@ -13,7 +13,8 @@ and a run only counts as passed when its artifacts pass the gates:
 * `groups`     `shardtrain --smoke-groups` on every mesh that fits (one collective per group)
 * `flags`      the tiny Qwen2 model through the shard runtime on one mesh, all eight combinations
                of forward prefetch / backward prefetch / asynchronous reduce-scatter; gates:
-               the event-log audit and the benchmark-record audit of `utils/audit.py`
+               the event-log audit, the benchmark-record audit and the measured-payload audit
+               of `utils/audit.py`
 * `meshes`     the same run with all switches on, on every mesh that fits
 * `policies`   conservative against stream_ordered on the largest hybrid mesh that fits; gate: the
                two policies report the same losses
@@ -37,7 +38,8 @@ from pathlib import Path
 
 import yaml
 
-from shardtrain_b200.utils.audit import audit_benchmark, audit_event_logs
+from shardtrain_b200.utils.audit import (audit_benchmark, audit_event_logs, audit_volume,
+                                         volume_arguments)
 
 ROOT = Path(__file__).resolve().parents[2]
 MESHES = [(1, 1), (2, 1), (1, 2), (2, 2), (4, 1), (4, 2), (2, 4), (8, 1)]       # (F, T)
@@ -161,7 +163,11 @@ def gate(case: Case, status: int, layers: int, tied: bool) -> list[str]:
         return [f"no smoke record of ranks {missing}"] if missing else []
     problems = audit_event_logs(directory, fsdp=case.fsdp, tp=case.tp, layers=layers, tied=tied,
                                 policy=case.policy)
-    return problems + audit_benchmark(directory, layers=layers, tied=tied)
+    problems += audit_benchmark(directory, layers=layers, tied=tied)
+    if case.fsdp * case.tp > 1:
+        # every micro-step carried what the volume model predicts from this configuration
+        problems += audit_volume(directory, **volume_arguments(directory / "config.yaml"))
+    return problems
 
 
 def main(argv=None) -> int:

@@ -167,3 +167,27 @@ def test_step_profile_summary_groups_streams_kernels_and_gaps(tmp_path):
     assert got["top_kernels"][0]["total_ms"] == pytest.approx(0.1)
     gaps = got["compute_stream_gaps_over_15us"]
     assert gaps["total_ms"] == pytest.approx(0.038) and gaps["before"][0]["count"] == 1
+
+
+WORKER_TINY = dict(hidden_size=64, mlp_hidden_size=128, num_heads=4, num_key_value_heads=2, layers=2,
+                   vocab_size=1024, seq_len=64, tie_word_embeddings=True)
+
+
+@pytest.mark.distributed
+def test_measured_payload_equals_the_volume_model_on_a_mesh(mesh_run):
+    """Every micro-step of the 2 x 2 run carries exactly the collectives and elements that the
+    volume model predicts from the configuration; a wrong batch or mesh does not."""
+    from shardtrain_b200.utils.audit import audit_volume
+
+    assert audit_volume(mesh_run, WORKER_TINY, fsdp=2, tp=2, sp=True, local_batch=2) == []
+    wrong_batch = audit_volume(mesh_run, WORKER_TINY, fsdp=2, tp=2, sp=True, local_batch=4)
+    assert wrong_batch and all("sp_" in p for p in wrong_batch)
+    assert audit_volume(mesh_run, dict(WORKER_TINY, layers=3), fsdp=2, tp=2, sp=True, local_batch=2)
+
+
+def test_measured_payload_of_a_single_rank_run_has_nothing_to_carry(run_dir):
+    from shardtrain_b200.utils.audit import audit_volume
+
+    out, config = run_dir
+    problems = audit_volume(out, WORKER_TINY, fsdp=1, tp=1, sp=False, local_batch=2)
+    assert problems == ["rank 0: no micro-step with collectives found"]
