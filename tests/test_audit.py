@@ -191,3 +191,21 @@ def test_measured_payload_of_a_single_rank_run_has_nothing_to_carry(run_dir):
     out, config = run_dir
     problems = audit_volume(out, WORKER_TINY, fsdp=1, tp=1, sp=False, local_batch=2)
     assert problems == ["rank 0: no micro-step with collectives found"]
+
+
+def test_event_logs_become_a_chrome_trace(run_dir, tmp_path):
+    """`utils.trace_events`: one process per rank, collectives and unit phases as slices with
+    non-negative durations in log order, step boundaries as markers."""
+    from shardtrain_b200.utils import trace_events
+
+    out, _ = run_dir
+    target = tmp_path / "timeline.json"
+    assert trace_events.main([str(out), "-o", str(target)]) == 0
+    events = json.loads(target.read_text())["traceEvents"]
+    slices = [e for e in events if e["ph"] == "X"]
+    assert slices and all(e["dur"] > 0 and e["ts"] >= 0 and e["pid"] == 0 for e in slices)
+    assert {e["cat"] for e in slices} >= {"unit"}
+    names = {e["args"]["name"] for e in events if e["ph"] == "M" and e["name"] == "thread_name"}
+    assert "units" in names and "markers" in names
+    assert any(e["ph"] == "i" and e["name"] == "step_end" for e in events)
+    assert trace_events.main([str(tmp_path / "empty")]) == 1
