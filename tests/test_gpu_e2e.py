@@ -67,7 +67,10 @@ def test_replayed_layer_graphs_give_the_same_bits_as_kernel_by_kernel_launches()
     batches = [torch.randint(0, 2048, (4, 256), device="cuda") for _ in range(5)]   # new data each step
     runs = {}
     for graphs in (False, True):
-        dense, model, rt, tr = build(True, optimizer="adamw", lr=1e-3, graphs=graphs)
+        # SGD: a parameter moves in proportion to its gradient, so the run-to-run rounding noise of
+        # the embedding's atomic scatter-add stays rounding noise (AdamW's g / sqrt(v) would turn
+        # it into whole steps for elements whose gradient is nearly zero)
+        dense, model, rt, tr = build(True, optimizer="sgd", lr=0.05, graphs=graphs)
         before = int(stb.launch_count())
         losses = [tr.train_step(ids).loss for ids in batches]
         torch.cuda.synchronize()
@@ -84,9 +87,9 @@ def test_replayed_layer_graphs_give_the_same_bits_as_kernel_by_kernel_launches()
         else:
             assert int(stb.replay_graphs()) == 0
     # (the embedding's scatter-add uses atomics, so two runs agree to rounding, not to the bit)
-    assert runs[True][0] == pytest.approx(runs[False][0], rel=1e-5)
+    assert runs[True][0] == pytest.approx(runs[False][0], rel=1e-4)
     for a, b in zip(runs[True][1], runs[False][1]):
-        torch.testing.assert_close(a, b, atol=2e-5, rtol=0)
+        torch.testing.assert_close(a, b, atol=2e-5, rtol=1e-4)
     assert runs[True][2] == runs[False][2]                 # replayed kernels are counted too
     stb.replay_clear()
 
@@ -109,7 +112,7 @@ def test_fresh_mask_and_position_tensors_every_step_still_hit_the_replay_cache()
     losses, graphs = {}, {}
     for fresh in (True, False):
         stb.replay_clear()
-        dense, model, rt, tr = build(True, optimizer="adamw", lr=1e-3)
+        dense, model, rt, tr = build(True, optimizer="sgd", lr=0.05)
         kept = inputs()
         run = []
         for step in range(6):
@@ -120,7 +123,9 @@ def test_fresh_mask_and_position_tensors_every_step_still_hit_the_replay_cache()
         losses[fresh], graphs[fresh] = run, int(stb.replay_graphs())
     # 2 layers: one forward sequence each, one backward sequence per gradient slot (4) at most
     assert 4 <= graphs[True] == graphs[False] <= 2 + 2 * 4
-    assert losses[True] == pytest.approx(losses[False], rel=1e-5)
+    # (a wrong or stale mask moves the loss by percents; atomics in the embedding's scatter-add
+    # move it by rounding noise)
+    assert losses[True] == pytest.approx(losses[False], rel=1e-3)
     stb.replay_clear()
 
 
